@@ -1,0 +1,313 @@
+"""Benchmark of the Gemma4 decode step.  python bench.py --gpus N --steps K --warmup W
+
+One "step" = one decode step (one new token for every sequence of the batch) through all layers,
+the tied LM head and the fused arg-max. Prints ONE JSON line (rank 0).
+
+  value      decode tokens/s with everything resident in HBM: the captured step graph is replayed
+             K times, each step's arg-max fed back on the device (oxg4_decode_greedy), timed with
+             CUDA events on the library's stream.
+  e2e        the same metric through the public per-token call (decode_topk): every step copies
+             the token ids host->device, replays the graph, copies (id, score) device->host and
+             synchronises, exactly what the reference's generate loop does per token.
+  roofline   dominant kernel (gate/up projection): algorithmic bytes / mean device time of that
+             kernel, measured with CUDA events around each launch in eager profiling steps run
+             right after the timed region; `step_*` keys give the whole-step figure.
+  cpu_baseline / --impl reference: the CPU oracle (a port of the reference's arithmetic; the
+             reference has no CPU forward pass of its own) on this box's host cores.
+
+Weights are seeded random N(0, 0.02) (generated with torch on the GPU when one is present, then
+handed to the library through its host-pointer upload call); prompts are seeded uniform ids.
+Inputs streamed per step (weights + KV) are far larger than the 126 MB L2, so no L2 flush is needed.
+"""
+import argparse
+import importlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "decode_tokens_per_s"
+UNIT = "tok/s"
+DEFAULT_WORKLOAD = "c3"          # ~4B-class, batch 1: the configuration the 70%-of-HBM target is quoted on
+NCU_TRAFFIC_BYTES = {}           # workload -> dram bytes per launch of the dominant kernel (from ncu)
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def algorithmic_bytes(cfg, batch, contexts, wb=2, kvb=2):
+    """weights + KV bytes one decode step must read (activations and KV writes excluded)."""
+    H, D = cfg["hidden_size"], cfg["head_dim"]
+    Nq, Nkv, I, V = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["intermediate_size"], cfg["vocab_size"]
+    per_layer = (H * (Nq + 2 * Nkv) * D + Nq * D * H + 3 * H * I) * wb
+    total = cfg["num_hidden_layers"] * per_layer + V * H * wb
+    kv = 0
+    for t in cfg["layer_types"]:
+        for ctx in contexts:
+            vis = min(ctx, cfg["sliding_window"]) if t == "sliding_attention" else ctx
+            kv += 2 * vis * Nkv * D * kvb
+    return total + kv, {"weights": total, "kv": kv, "gateup_launch": 2 * I * H * wb}
+
+
+def torch_weights(cfg, device):
+    """Seeded N(0, 0.02) BF16 weights generated on `device`, yielded as (name, uint16 array)."""
+    import torch
+    syn = importlib.import_module("oxide-beta_b200").synthetic
+    gen = torch.Generator(device=device).manual_seed(0)
+    for name, shape, kind in syn.weight_names(cfg):
+        if kind == "matrix":
+            t = torch.empty(shape, dtype=torch.float32, device=device).normal_(0.0, 0.02, generator=gen)
+        else:
+            t = torch.ones(shape, dtype=torch.float32, device=device)
+        yield name, t.to(torch.bfloat16).view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=self.file,
+                                         stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, mx, reasons = [], [], set()
+        for line in self.file.read().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.file.name)
+        if sm:
+            out = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                   "samples": len(sm)}
+        return out
+
+
+def cpu_oracle_run(cfg, weights_iter, prompt, steps, warmup):
+    """Times the CPU oracle: ingests `prompt`, then `warmup` + `steps` greedy decode steps."""
+    from oracle import oracle as orc
+    m = orc.OracleModel(cfg, orc.REF_BF16, kv_bf16=True)
+    for name, a in weights_iter:
+        m.set_weight(name, a)
+    cache = m.new_cache(len(prompt) + steps + warmup + 1)
+    for t in prompt[:-1]:
+        cache.prefill_token(int(t))
+    tok = int(prompt[-1])
+    for _ in range(warmup):
+        tok = int(cache.decode_topk(tok, 1, 1.0, False)[0][0])
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        tok = int(cache.decode_topk(tok, 1, 1.0, False)[0][0])
+    dt = time.perf_counter() - t0
+    return steps / dt, dt, orc.num_threads()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=16)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
+    ap.add_argument("--prompt", type=int, default=None, help="override the prompt length")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    pkg = importlib.import_module("oxide-beta_b200")
+    syn = pkg.synthetic
+    w = syn.workload(args.workload)
+    cfg, B = w["cfg"], w["batch"]
+    prompt_len = args.prompt or (w["prompt"] if isinstance(w["prompt"], int) else w["prompt"][1])
+
+    import torch
+    has_gpu = torch.cuda.is_available()
+
+    # ------------------------------------------------------------------ reference arm (CPU oracle)
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        sample_prompt = 32
+        steps = min(args.steps, 16)
+        wu = min(warmup, 3)
+        weights = torch_weights(cfg, "cuda:0" if has_gpu else "cpu")
+        prompt = syn.prompt_ids(cfg["vocab_size"], sample_prompt, seed=1)
+        tps, dt, cores = cpu_oracle_run(cfg, weights, prompt, steps, wu)
+        sample = (f"{steps} greedy decode steps at batch 1 after a {sample_prompt}-token prompt "
+                  f"(full {args.workload} weights, BF16 recipe, OpenMP over {cores} threads)")
+        print(json.dumps({
+            "impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+            "warmup": wu, "ms_per_step": 1000.0 * dt / steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": args.workload, "batch": 1, "prompt": sample_prompt,
+                       "note": "CPU port of the reference arithmetic; the reference has no CPU forward pass"},
+            "cpu_baseline": {"value": tps, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+
+    # ------------------------------------------------------------------ our arm
+    if not has_gpu:
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    t_load = time.perf_counter()
+    state = pkg.Gemma4CudaState(pkg.Gemma4TextConfig(cfg), local_rank, pkg.BF16)
+    host_weights = []
+    keep_host = (rank == 0 and world == 1 and not args.no_cpu_baseline)
+    for name, a in torch_weights(cfg, f"cuda:{local_rank}"):
+        state.upload(name, a)
+        if keep_host:
+            host_weights.append((name, a))
+    state.finalize()
+    torch.cuda.empty_cache()
+    load_s = time.perf_counter() - t_load
+
+    lens = [prompt_len] * B
+    if not isinstance(w["prompt"], int) and args.prompt is None:
+        lens = syn.ragged_lengths(B, w["prompt"][0], w["prompt"][1], seed=2).tolist()
+    total_steps = warmup + args.steps
+    max_seq = [n + 2 * total_steps + 8 for n in lens]
+    table = state.new_cache_table(max_seq, batch=B, kv_dtype=pkg.BF16)
+    prompts = [syn.prompt_ids(cfg["vocab_size"], n, seed=1 + b) for b, n in enumerate(lens)]
+    t_pre = time.perf_counter()
+    logits = state.prefill_prompt(np.concatenate(prompts), table, lens=lens)
+    prefill_s = time.perf_counter() - t_pre
+    first = np.atleast_2d(logits).argmax(-1).astype(np.uint32)
+
+    launches0 = state.kernel_launches()
+    # device-resident loop: warm-up then the timed K steps
+    ids, _ = state.decode_greedy(first, table, warmup)
+    if dist:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches1 = state.kernel_launches()
+    ids, ms_step = state.decode_greedy(ids[-1], table, args.steps)
+    torch.cuda.synchronize()
+    launches_timed = state.kernel_launches() - launches1
+    if dist:
+        dist.barrier()
+    # end-to-end: per-token public call with host buffers
+    tok = ids[-1].copy()
+    for _ in range(3):
+        r = state.decode_topk(tok, table, 1, 1.0, True)
+        tok = np.array([r[0][0]], dtype=np.uint32) if B == 1 else r[0][:, 0].copy()
+    e2e_steps = min(args.steps, total_steps - 3)
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        r = state.decode_topk(tok, table, 1, 1.0, True)
+        tok = np.array([r[0][0]], dtype=np.uint32) if B == 1 else r[0][:, 0].copy()
+    e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop()
+
+    if dist:
+        t = torch.tensor([ms_step, e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step, e2e_s = float(t[0]), float(t[1])
+    value = world * B * 1000.0 / ms_step
+    e2e_value = world * B * e2e_steps / e2e_s
+
+    # dominant-kernel timing: eager steps with CUDA events around every launch
+    contexts = [table.position(b) for b in range(B)]
+    prof = {}
+    n_prof = 5
+    for _ in range(n_prof):
+        p = state.profile_step(tok, table)
+        for k, v in p.items():
+            if v >= 0:
+                prof[k] = prof.get(k, 0.0) + v / n_prof
+        tok = tok.copy()
+    peak, peak_kind = peaks()
+    step_bytes, parts = algorithmic_bytes(cfg, B, contexts)
+    gu_ms = prof.get("gateup", float("nan"))
+    achieved = parts["gateup_launch"] / (gu_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "gemv_kernel<bf16, PRO_NORM, EPI_GATEUP> (gate/up projection)",
+                "achieved": achieved, "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
+                "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                "bytes_per_launch": parts["gateup_launch"], "ms_per_launch": gu_ms,
+                "step_bytes": step_bytes, "step_achieved": step_bytes / (ms_step * 1e-3) / 1e9,
+                "step_frac": step_bytes / (ms_step * 1e-3) / 1e9 / peak,
+                "kernel_ms": {k: round(v, 5) for k, v in prof.items()}}
+
+    if rank != 0:
+        if dist:
+            dist.destroy_process_group()
+        return
+    out = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "batch": B, "prompt": lens[0] if len(set(lens)) == 1 else "ragged",
+                   "context_at_timing": contexts[0], "kv_dtype": "bf16", "page_tokens": 256,
+                   "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
+                   "l2": "per-step inputs (weights + KV) exceed the 126 MB L2; no flush",
+                   "load_s": round(load_s, 2), "prefill_s": round(prefill_s, 2)},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * B + 16, "d2h_bytes_per_step": 8 * B,
+                "steps": e2e_steps},
+        "gpu_launches": int(launches_timed),
+        "clocks": clocks,
+        "roofline": roofline,
+    }
+    if keep_host:
+        sample_prompt, cpu_steps = 32, 8
+        tps, dt, cores = cpu_oracle_run(cfg, host_weights, syn.prompt_ids(cfg["vocab_size"], sample_prompt, seed=1),
+                                        cpu_steps, 2)
+        out["cpu_baseline"] = {"value": tps, "unit": UNIT, "cores": cores, "kind": "port",
+                               "sample": f"{cpu_steps} greedy decode steps at batch 1 after a {sample_prompt}-token "
+                                         f"prompt, full {args.workload} weights, BF16 recipe"}
+    print(json.dumps(out))
+    if dist:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

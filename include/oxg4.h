@@ -1,0 +1,205 @@
+/* oxg4.h — C ABI of the B200-native Gemma4 token-generation path.
+ *
+ * This library replaces, for Gemma4 decode only, what the reference project (tuna2134/oxide-beta)
+ * implements in crates/oxide-torch-cuda (kernel module, cuBLAS and CUDA-graph wrappers) and in
+ * crates/oxide-torch-models/src/gemma4_cuda (the Gemma4 CUDA executor). The reference's Rust
+ * types become owners of the opaque handles declared here; their public signatures do not change.
+ * Each entry point cites the reference interface it stands in for (paths inside the reference).
+ *
+ * Conventions
+ *   - every function returns an oxg4_status; 0 is success; no exception crosses the boundary
+ *   - a failing call leaves a message retrievable with oxg4_last_error()
+ *   - all pointers are HOST pointers; device memory never crosses the boundary
+ *   - handles are not thread-safe; calls on one model/cache are serialised by the caller
+ *     (the reference state is Rc<RefCell<..>>, i.e. !Send + !Sync)
+ *   - there is no CPU fallback: without a CUDA device every compute entry point fails
+ */
+#ifndef OXG4_H
+#define OXG4_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct oxg4_model oxg4_model;   /* Gemma4CudaState        (gemma4_cuda/mod.rs:161-175)   */
+typedef struct oxg4_cache oxg4_cache;   /* Gemma4CudaCacheTable   (gemma4_cuda/mod.rs:119-159)   */
+
+typedef enum {
+    OXG4_OK = 0,
+    OXG4_INVALID_SHAPE = 1,     /* oxide_torch::Error::InvalidShape                               */
+    OXG4_INVALID_ARGUMENT = 2,  /* oxide_torch::Error::Execution for bad input                    */
+    OXG4_CUDA = 3,              /* Error::Execution("Gemma 4 CUDA error: ...") mod.rs:581-583     */
+    OXG4_NCCL = 4,
+    OXG4_OOM = 5,
+    OXG4_TIMEOUT = 6,
+    OXG4_UNSUPPORTED = 7
+} oxg4_status;
+
+typedef enum { OXG4_F32 = 0, OXG4_BF16 = 1 } oxg4_dtype;
+
+/* Subset of Gemma4TextConfig the decode path reads (models/gemma4/config.rs:103-148) plus the
+ * per-layer plan fields of Gemma4DecodeLayerPlan (gemma4_cuda/mod.rs:65-93, 365-413). */
+typedef struct {
+    int32_t vocab_size;
+    int32_t hidden_size;
+    int32_t num_hidden_layers;
+    int32_t num_attention_heads;
+    int32_t num_key_value_heads;
+    int32_t head_dim;
+    int32_t global_head_dim;          /* must equal head_dim in this build                        */
+    int32_t intermediate_size;
+    int32_t sliding_window;
+    float rms_norm_eps;
+    float final_logit_softcapping;    /* 0 = none; applied on the host to returned scores/logits   */
+    int32_t weight_dtype;             /* OXG4_BF16: the reference's recipe (BF16 weights, BF16-
+                                         rounded GEMM inputs, f32 accumulate and activations).
+                                         OXG4_F32: f32 weights, no rounding (tiny CPU-checkable case) */
+    int32_t norm_weight_offset;       /* 0: x*s*w as the reference; 1: x*s*(1+w)                   */
+    const int32_t* layer_is_sliding;  /* [num_hidden_layers] 1 = sliding_attention                 */
+    const int32_t* rotary_dim;        /* [num_hidden_layers] (partial_rotary_factor * head_dim)     */
+    const float* rope_theta;          /* [num_hidden_layers]                                        */
+    const float* rope_factor;         /* [num_hidden_layers]                                        */
+    int32_t tp_rank;                  /* tensor-parallel rank of this process (0 when tp_size = 1)  */
+    int32_t tp_size;                  /* 1, 2, 4 or 8; must divide the KV-head count               */
+} oxg4_config;
+
+typedef struct {
+    int32_t batch;
+    int32_t layer_count;              /* Gemma4CudaCacheTable::layer_count                          */
+    int32_t physical_cache_count;     /* ::physical_cache_count                                     */
+    int32_t shared_layer_count;       /* ::shared_layer_count (always 0: KV sharing unsupported)    */
+    int32_t page_tokens;
+    int32_t kv_dtype;
+    int64_t kv_bytes;                 /* device bytes held by K and V pools                         */
+} oxg4_cache_info;
+
+/* Message of the most recent failing call on this thread. */
+const char* oxg4_last_error(void);
+
+/* ---- model: Gemma4CudaState::load (gemma4_cuda/mod.rs:221-466) split into three steps ---------- */
+
+/* CudaContext::new(n) + stream creation (mod.rs:221-232). `device` is the ordinal of Device::Cuda(n). */
+int32_t oxg4_model_create(const oxg4_config* config, int32_t device, oxg4_model** out);
+
+/* Upload of one checkpoint tensor (mod.rs:236-279). `name` is the checkpoint name with or without
+ * the "model.language_model." prefix. The copy has completed when the call returns, so it may be
+ * made from inside SafeTensorLoader::with_view (crates/oxide-torch/src/safetensors.rs:182-189).
+ * With tp_size > 1 the full tensor is passed and only this rank's shard is kept. */
+int32_t oxg4_model_upload(oxg4_model* model, const char* name, int32_t dtype, const int64_t* shape,
+                          int32_t rank, const void* data, size_t bytes);
+
+/* QKV fusion + decode-plan construction (mod.rs:283-449). */
+int32_t oxg4_model_finalize(oxg4_model* model);
+
+void oxg4_model_destroy(oxg4_model* model);
+
+/* Gemma4CudaState::weight_count / weight_bytes (mod.rs:468-476). */
+int64_t oxg4_weight_count(const oxg4_model* model);
+int64_t oxg4_weight_bytes(const oxg4_model* model);
+
+/* Gemma4CudaState::synchronize (mod.rs:478-480). */
+int32_t oxg4_synchronize(oxg4_model* model);
+
+/* Tensor parallelism (no counterpart in the reference, which is single-GPU): every rank creates
+ * its model with the same tp_size and its own tp_rank; rank 0 obtains an id, the host program
+ * distributes the 128 bytes to the other ranks, and all ranks call oxg4_model_tp_init. */
+int32_t oxg4_tp_unique_id(void* out_128_bytes);
+int32_t oxg4_model_tp_init(oxg4_model* model, const void* unique_id_128_bytes);
+
+/* ---- KV cache: new_cache_table (gemma4_cuda/cache.rs:31-95) -------------------------------------- */
+
+/* `max_seq[b]` is the longest sequence (prompt + generated) sequence b may reach. Sliding layers
+ * get a ring of min(sliding_window, max_seq[b]) positions, global layers max_seq[b] positions, in
+ * pages of `page_tokens` tokens. kv_dtype OXG4_F32 is the reference's cache; OXG4_BF16 halves it. */
+int32_t oxg4_cache_create(oxg4_model* model, int32_t batch, const int32_t* max_seq,
+                          int32_t page_tokens, int32_t kv_dtype, oxg4_cache** out);
+void oxg4_cache_destroy(oxg4_cache* cache);
+int32_t oxg4_cache_info_get(const oxg4_cache* cache, oxg4_cache_info* out);
+/* Tokens processed so far for sequence b (Gemma4CudaKvCache::len semantics on a global layer). */
+int32_t oxg4_cache_position(const oxg4_cache* cache, int32_t b);
+/* Empties the cache and the seen-token bitmap so the table can serve a new generation
+ * (reset_generation_state, mod.rs:178-180, plus a fresh table). */
+int32_t oxg4_cache_reset(oxg4_cache* cache);
+
+/* ---- steps ------------------------------------------------------------------------------------------ */
+
+/* prefill_prompt (gemma4_cuda/decode.rs:431-459). `tokens` holds the prompts back to back,
+ * `lens[b]` tokens for sequence b. last_logits (may be NULL) receives [batch, vocab] f32 logits
+ * of each prompt's final token. The cache must be empty. */
+int32_t oxg4_prefill(oxg4_model* model, oxg4_cache* cache, const uint32_t* tokens,
+                     const int32_t* lens, float* last_logits);
+
+/* prefill_token (decode.rs:464-472): one token per sequence, no LM head.
+ * A token id of 0xFFFFFFFF leaves that sequence untouched in this step. */
+int32_t oxg4_prefill_token(oxg4_model* model, oxg4_cache* cache, const uint32_t* tokens);
+
+/* decode_token (decode.rs:476-486): one token per sequence, logits [batch, vocab] to the host. */
+int32_t oxg4_decode_logits(oxg4_model* model, oxg4_cache* cache, const uint32_t* tokens, float* logits);
+
+/* decode_topk (decode.rs:666-783): one token per sequence; returns for each sequence the top_k
+ * (clamped to 1..=64) candidates in descending order, repetition penalty applied on the device
+ * to tokens marked seen. ids/scores are [batch, top_k]. The step is captured as a CUDA graph on
+ * first use for a (top_k, penalty) pair and replayed afterwards. */
+int32_t oxg4_decode_topk(oxg4_model* model, oxg4_cache* cache, const uint32_t* tokens, int32_t top_k,
+                         float repetition_penalty, int32_t mark_seen, uint32_t* ids, float* scores);
+
+/* Device-resident greedy loop (no counterpart in the reference, whose host samples every token):
+ * runs `steps` decode steps feeding each step's arg-max back as the next token without leaving
+ * the GPU, then returns the generated ids [steps, batch] and the mean device time per step.
+ * Equivalent to calling oxg4_decode_topk(top_k = 1, penalty = 1) `steps` times. */
+int32_t oxg4_decode_greedy(oxg4_model* model, oxg4_cache* cache, const uint32_t* first_tokens,
+                           int32_t steps, uint32_t* out_ids, float* ms_per_step);
+
+/* Number of kernels launched by this library since the model was created (graph replays count
+ * the kernels inside the graph). */
+int64_t oxg4_kernel_launches(const oxg4_model* model);
+
+/* Mean device time in milliseconds, measured with CUDA events on the model's stream, of the
+ * decode kernels of the kind `kind` ("qkv", "attn", "o", "gateup", "down", "lmhead") during the
+ * most recent oxg4_profile_step call; that call runs one eager decode step with events around
+ * every kernel. */
+int32_t oxg4_profile_step(oxg4_model* model, oxg4_cache* cache, const uint32_t* tokens);
+float oxg4_profile_ms(const oxg4_model* model, const char* kind);
+
+/* ---- host-side mirror of the generation loop -------------------------------------------------------- */
+
+/* GenerationConfig (models/gemma4/config.rs:7-33). */
+typedef struct {
+    int64_t max_new_tokens;
+    float temperature;
+    int64_t top_k;
+    float top_p;
+    float repetition_penalty;
+    uint64_t seed;
+    const uint32_t* eos_token_ids;
+    int64_t n_eos;
+    const uint32_t* stop_sequences;       /* flattened */
+    const int64_t* stop_sequence_lens;
+    int64_t n_stop_sequences;
+} oxg4_generation_config;
+
+typedef int32_t (*oxg4_token_callback)(uint32_t token, void* user);
+
+/* Gemma4ForCausalLM::generate / generate_stream (models/gemma4/generation.rs:47-140) for one
+ * sequence: validate, new cache table, prefill, sample, callback, EOS / stop check, decode_topk.
+ * out_ids must hold n_prompt + max_new_tokens entries; *n_out receives the length written
+ * (prompt followed by the generated ids). A non-zero callback return aborts with
+ * OXG4_INVALID_ARGUMENT, mirroring an Err from on_token. */
+int32_t oxg4_generate(oxg4_model* model, const uint32_t* prompt, int64_t n_prompt,
+                      const oxg4_generation_config* generation, int32_t kv_dtype,
+                      oxg4_token_callback on_token, void* user, uint32_t* out_ids, int64_t* n_out);
+
+/* sample_token / sample_topk_candidates (models/gemma4/sampling.rs:9-158). Return the token id or
+ * -1 for the inputs the reference rejects. `random` is the xorshift64 state, updated in place. */
+int64_t oxg4_sample_token(const float* logits, int64_t n, float temperature, int64_t top_k,
+                          float top_p, uint64_t* random);
+int64_t oxg4_sample_topk_candidates(const uint32_t* ids, const float* scores, int64_t n,
+                                    float temperature, float top_p, uint64_t* random);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OXG4_H */

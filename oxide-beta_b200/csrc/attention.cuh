@@ -1,0 +1,331 @@
+// Decode attention over a paged KV cache: one launch per layer does what the reference spreads
+// over slice_rows x3, rms_norm (q), rope_state (q), rms_norm (k), rope_state (k), rms_norm_unit
+// (v), cache_write_f32_state x2 and gqa_decode_block_state
+// (crates/oxide-torch-models/src/gemma4_cuda/decode.rs:82-157; device math in
+// crates/oxide-torch-cuda/src/kernel_module.rs:1133-1246,1423-1439,1510-1550,1790-1894).
+//
+// Grid (split, kv_head, sequence). The visible positions of a sequence are partitioned into up
+// to `n_splits` contiguous ranges; each CTA streams its range of K and V rows once (split-KV
+// "flash decoding" with an online softmax per warp), writes an un-normalised partial, and the
+// last CTA of a (sequence, kv_head) to finish merges the partials in split order, so the result
+// does not depend on scheduling. Attention scale is 1.0 as in the reference (no 1/sqrt(d)).
+//
+// Cache layout: pool[page][kv_head][token_in_page][head_dim]; a sequence's slot -> page mapping
+// comes from its page table. Ring semantics follow the reference: slot = position % capacity,
+// capacity = min(window, max_seq) on sliding layers (kernel_module.rs:1811-1831), so the ring
+// itself implements the window.
+//
+// HBM-bound: bytes per launch = 2 * visible_positions * kv_heads * head_dim * sizeof(KV element).
+#pragma once
+#include "common.cuh"
+
+namespace oxg4 {
+
+constexpr int kAttnThreads = 256;
+constexpr int kAttnWarps = kAttnThreads / 32;
+
+struct AttnArgs {
+    PartialSpec qkv;         // QKV projection partials, columns q | k | v
+    int B, Nq, Nkv;
+    const float* q_norm;     // [D]
+    const float* k_norm;     // [D]
+    const float* inv_freq;   // [D/2]: theta^(-2i/D) / factor
+    int rotary_half;         // rotary_dim / 2; frequency lanes at or above it pass through
+    float eps;
+    const int32_t* pos;      // [B] absolute position of the token being processed
+    const uint32_t* tokens;  // [B] (kInactiveToken rows are skipped)
+    void* kpool;
+    void* vpool;
+    const int32_t* page_table;   // [B, pages_per_seq]
+    int pages_per_seq, page_tokens;
+    const int32_t* cap;      // [B] ring capacity of this layer kind for each sequence
+    int n_splits, min_split;
+    float* part;             // [B, Nkv, n_splits, G, D + 2]
+    unsigned int* ticket;    // [B, Nkv]
+    float* out;              // [B, Nq * D]
+};
+
+template <typename KT, int EPT> struct KVec;
+template <> struct KVec<uint16_t, 8> {
+    static DEVINL void load(const uint16_t* p, float (&o)[8]) {
+        uint4 v = ldg_stream16(p);
+        o[0] = bf16lo(v.x); o[1] = bf16hi(v.x); o[2] = bf16lo(v.y); o[3] = bf16hi(v.y);
+        o[4] = bf16lo(v.z); o[5] = bf16hi(v.z); o[6] = bf16lo(v.w); o[7] = bf16hi(v.w);
+    }
+};
+template <> struct KVec<uint16_t, 4> {
+    static DEVINL void load(const uint16_t* p, float (&o)[4]) {
+        uint2 v = ldg_stream8(p);
+        o[0] = bf16lo(v.x); o[1] = bf16hi(v.x); o[2] = bf16lo(v.y); o[3] = bf16hi(v.y);
+    }
+};
+template <> struct KVec<uint16_t, 2> {
+    static DEVINL void load(const uint16_t* p, float (&o)[2]) {
+        uint32_t v = ldg_stream4(p);
+        o[0] = bf16lo(v); o[1] = bf16hi(v);
+    }
+};
+template <> struct KVec<float, 8> {
+    static DEVINL void load(const float* p, float (&o)[8]) {
+        uint4 a = ldg_stream16(p), b = ldg_stream16(p + 4);
+        o[0] = __uint_as_float(a.x); o[1] = __uint_as_float(a.y); o[2] = __uint_as_float(a.z);
+        o[3] = __uint_as_float(a.w); o[4] = __uint_as_float(b.x); o[5] = __uint_as_float(b.y);
+        o[6] = __uint_as_float(b.z); o[7] = __uint_as_float(b.w);
+    }
+};
+template <> struct KVec<float, 4> {
+    static DEVINL void load(const float* p, float (&o)[4]) {
+        uint4 a = ldg_stream16(p);
+        o[0] = __uint_as_float(a.x); o[1] = __uint_as_float(a.y); o[2] = __uint_as_float(a.z);
+        o[3] = __uint_as_float(a.w);
+    }
+};
+template <> struct KVec<float, 2> {
+    static DEVINL void load(const float* p, float (&o)[2]) {
+        uint2 a = ldg_stream8(p);
+        o[0] = __uint_as_float(a.x); o[1] = __uint_as_float(a.y);
+    }
+};
+
+template <typename KT> DEVINL KT kv_store_cvt(float v);
+template <> DEVINL float kv_store_cvt<float>(float v) { return v; }
+template <> DEVINL uint16_t kv_store_cvt<uint16_t>(float v) { return (uint16_t)f32_to_bf16_bits(v); }
+template <typename KT> DEVINL float kv_widen(KT v);
+template <> DEVINL float kv_widen<float>(float v) { return v; }
+template <> DEVINL float kv_widen<uint16_t>(uint16_t v) { return __uint_as_float((uint32_t)v << 16); }
+
+template <typename KT, int D, int G>
+__global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArgs a) {
+    constexpr int EPT = D / 32;
+    constexpr int NW = kAttnWarps;
+    extern __shared__ __align__(16) float sm[];
+    float* qs = sm;                          // [G][D]
+    float* kcur = qs + G * D;                // [D]
+    float* vcur = kcur + D;                  // [D]
+    float* wm = vcur + D;                    // [NW][G]
+    float* wl = wm + NW * G;                 // [NW][G]
+    float* wacc = wl + NW * G;               // [NW][G][D]
+    __shared__ unsigned int s_last;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int s = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int half = D / 2;
+
+    pdl_wait();
+    pdl_launch();
+
+    const bool active = a.tokens[b] != kInactiveToken;
+    const int pos = a.pos[b];
+    const int cap = a.cap[b];
+    const int lo = max(0, pos + 1 - cap);
+    const int n = pos - lo + 1;
+    const int n_eff = min(a.n_splits, (n + a.min_split - 1) / a.min_split);
+    const bool has_work = active && s < n_eff;
+    float* part = a.part + (((size_t)b * a.Nkv + kvh) * a.n_splits) * (size_t)(G * (D + 2));
+
+    if (has_work) {
+        const int begin = lo + (int)(((long long)n * s) / n_eff);
+        const int end = lo + (int)(((long long)n * (s + 1)) / n_eff);
+        const bool owner = (s == n_eff - 1);        // the range that contains `pos`
+        const int slot_cur = pos % cap;
+        const size_t cur_off =
+            (((size_t)a.page_table[(size_t)b * a.pages_per_seq + slot_cur / a.page_tokens] * a.Nkv + kvh) *
+                 a.page_tokens + (slot_cur % a.page_tokens)) * (size_t)D;
+
+        // tasks 0..G-1: query heads (norm + rope); task G: key (norm + rope + append);
+        // task G+1: value (unit norm + append). One warp per task.
+        const int n_tasks = owner ? G + 2 : G;
+        for (int task = warp; task < n_tasks; task += NW) {
+            int col;
+            if (task < G) col = (kvh * G + task) * D;
+            else if (task == G) col = a.Nq * D + kvh * D;
+            else col = (a.Nq + a.Nkv) * D + kvh * D;
+            float t[EPT];
+            float ss = 0.0f;
+#pragma unroll
+            for (int e = 0; e < EPT; ++e) {
+                const float v = sum_partials(a.qkv, a.B, b, col + lane * EPT + e);
+                t[e] = v;
+                ss += v * v;
+            }
+            ss = warp_sum(ss);
+            const float r = 1.0f / sqrtf(ss / (float)D + a.eps);
+            float* dst = task < G ? qs + task * D : (task == G ? kcur : vcur);
+            if (task <= G) {
+                const float* w = task < G ? a.q_norm : a.k_norm;
+#pragma unroll
+                for (int e = 0; e < EPT; ++e) dst[lane * EPT + e] = t[e] * r * w[lane * EPT + e];
+                __syncwarp();
+                float o[EPT];
+#pragma unroll
+                for (int e = 0; e < EPT; ++e) {
+                    const int d = lane * EPT + e;
+                    const int fi = d % half;
+                    float v = dst[d];
+                    if (fi < a.rotary_half) {
+                        const float angle = (float)pos * a.inv_freq[fi];
+                        const float pv = dst[d < half ? d + half : d - half];
+                        const float rotated = d < half ? -pv : pv;
+                        v = v * cosf(angle) + rotated * sinf(angle);
+                    }
+                    o[e] = v;
+                }
+                __syncwarp();
+#pragma unroll
+                for (int e = 0; e < EPT; ++e) dst[lane * EPT + e] = o[e];
+            } else {
+#pragma unroll
+                for (int e = 0; e < EPT; ++e) dst[lane * EPT + e] = t[e] * r;
+            }
+            if (task >= G) {
+                // append to the cache; keep the stored (possibly BF16-rounded) value for this step
+                KT* pool = (KT*)(task == G ? a.kpool : a.vpool);
+                __syncwarp();
+#pragma unroll
+                for (int e = 0; e < EPT; ++e) {
+                    const int d = lane * EPT + e;
+                    const KT stored = kv_store_cvt<KT>(dst[d]);
+                    pool[cur_off + d] = stored;
+                    dst[d] = kv_widen<KT>(stored);
+                }
+            }
+        }
+        __syncthreads();
+
+        float q[G][EPT];
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int e = 0; e < EPT; ++e) q[g][e] = qs[g * D + lane * EPT + e];
+        float m[G], l[G], acc[G][EPT];
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            m[g] = -INFINITY;
+            l[g] = 0.0f;
+#pragma unroll
+            for (int e = 0; e < EPT; ++e) acc[g][e] = 0.0f;
+        }
+        const KT* kpool = (const KT*)a.kpool;
+        const KT* vpool = (const KT*)a.vpool;
+        const int32_t* pt = a.page_table + (size_t)b * a.pages_per_seq;
+
+        auto row_offset = [&](int p) -> size_t {
+            const int slot = p % cap;
+            return (((size_t)pt[slot / a.page_tokens] * a.Nkv + kvh) * a.page_tokens +
+                    (slot % a.page_tokens)) * (size_t)D + lane * EPT;
+        };
+        auto consume = [&](const float (&kf)[EPT], const float (&vf)[EPT]) {
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float sc = 0.0f;
+#pragma unroll
+                for (int e = 0; e < EPT; ++e) sc = fmaf(q[g][e], kf[e], sc);
+                sc = warp_sum(sc);
+                const float mn = fmaxf(m[g], sc);
+                const float corr = expf(m[g] - mn);       // exp(-inf) = 0 on the first position
+                const float pe = expf(sc - mn);
+                l[g] = l[g] * corr + pe;
+#pragma unroll
+                for (int e = 0; e < EPT; ++e) acc[g][e] = acc[g][e] * corr + pe * vf[e];
+                m[g] = mn;
+            }
+        };
+
+        int p = begin + warp;
+        for (; p + NW < end; p += 2 * NW) {
+            float k0[EPT], v0[EPT], k1[EPT], v1[EPT];
+            const int p1 = p + NW;
+            if (p == pos) {
+#pragma unroll
+                for (int e = 0; e < EPT; ++e) { k0[e] = kcur[lane * EPT + e]; v0[e] = vcur[lane * EPT + e]; }
+            } else {
+                const size_t off = row_offset(p);
+                KVec<KT, EPT>::load(kpool + off, k0);
+                KVec<KT, EPT>::load(vpool + off, v0);
+            }
+            if (p1 == pos) {
+#pragma unroll
+                for (int e = 0; e < EPT; ++e) { k1[e] = kcur[lane * EPT + e]; v1[e] = vcur[lane * EPT + e]; }
+            } else {
+                const size_t off = row_offset(p1);
+                KVec<KT, EPT>::load(kpool + off, k1);
+                KVec<KT, EPT>::load(vpool + off, v1);
+            }
+            consume(k0, v0);
+            consume(k1, v1);
+        }
+        for (; p < end; p += NW) {
+            float k0[EPT], v0[EPT];
+            if (p == pos) {
+#pragma unroll
+                for (int e = 0; e < EPT; ++e) { k0[e] = kcur[lane * EPT + e]; v0[e] = vcur[lane * EPT + e]; }
+            } else {
+                const size_t off = row_offset(p);
+                KVec<KT, EPT>::load(kpool + off, k0);
+                KVec<KT, EPT>::load(vpool + off, v0);
+            }
+            consume(k0, v0);
+        }
+
+        // merge the warps of this CTA (fixed warp order)
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            if (lane == 0) { wm[warp * G + g] = m[g]; wl[warp * G + g] = l[g]; }
+#pragma unroll
+            for (int e = 0; e < EPT; ++e) wacc[((size_t)warp * G + g) * D + lane * EPT + e] = acc[g][e];
+        }
+        __syncthreads();
+        float* my = part + (size_t)s * (G * (D + 2));
+        for (int idx = tid; idx < G * D; idx += kAttnThreads) {
+            const int g = idx / D, d = idx % D;
+            float M = -INFINITY;
+            for (int w = 0; w < NW; ++w) M = fmaxf(M, wm[w * G + g]);
+            float A = 0.0f, L = 0.0f;
+            for (int w = 0; w < NW; ++w) {
+                const float mw = wm[w * G + g];
+                if (mw == -INFINITY) continue;
+                const float e = expf(mw - M);
+                A += e * wacc[((size_t)w * G + g) * D + d];
+                L += e * wl[w * G + g];
+            }
+            my[g * (D + 2) + d] = A;
+            if (d == 0) { my[g * (D + 2) + D] = M; my[g * (D + 2) + D + 1] = L; }
+        }
+    }
+
+    // ---- last CTA of this (sequence, kv head) merges the split partials in split order ----
+    __threadfence();
+    __syncthreads();
+    if (tid == 0)
+        s_last = (atomicAdd(&a.ticket[b * a.Nkv + kvh], 1u) == (unsigned)a.n_splits - 1u) ? 1u : 0u;
+    __syncthreads();
+    if (s_last) {
+        __threadfence();
+        if (active) {
+            for (int idx = tid; idx < G * D; idx += kAttnThreads) {
+                const int g = idx / D, d = idx % D;
+                float M = -INFINITY;
+                for (int sp = 0; sp < n_eff; ++sp)
+                    M = fmaxf(M, __ldcg(part + (size_t)sp * (G * (D + 2)) + g * (D + 2) + D));
+                float A = 0.0f, L = 0.0f;
+                for (int sp = 0; sp < n_eff; ++sp) {
+                    const float* ps = part + (size_t)sp * (G * (D + 2)) + g * (D + 2);
+                    const float ms = __ldcg(ps + D);
+                    if (ms == -INFINITY) continue;
+                    const float e = expf(ms - M);
+                    A += e * __ldcg(ps + d);
+                    L += e * __ldcg(ps + D + 1);
+                }
+                a.out[(size_t)b * a.Nq * D + (size_t)(kvh * G + g) * D + d] = A / L;
+            }
+        }
+        if (tid == 0) a.ticket[b * a.Nkv + kvh] = 0u;
+    }
+}
+
+template <int D, int G>
+inline size_t attn_smem_bytes() {
+    return sizeof(float) * (size_t)(G * D + 2 * D + 2 * kAttnWarps * G + kAttnWarps * G * D);
+}
+
+}  // namespace oxg4

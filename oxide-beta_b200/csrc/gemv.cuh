@@ -1,0 +1,394 @@
+// Weight-streaming projection kernel for small batches (1..4 activation rows per pass).
+//
+// One launch covers what the reference spreads over rms_norm[_bf16] + f32_to_bf16 + cublasGemmEx
+// (+ slice / gelu_mul / add / mul_bf16_scalar) launches — crates/oxide-torch-models/src/
+// gemma4_cuda/decode.rs:4-21,43-174 and tensor_ops.rs:61-157:
+//   prologue  PRO_NORM : finish the previous block's residual update
+//                        h = (h_in + rmsnorm(previous projection, w_post)) * layer_scalar
+//                        (or h = embedding row * sqrt(H) for the first layer), store h once, then
+//                        x = bf16(rmsnorm(h, w_norm))
+//             PRO_PLAIN: x = bf16(in)
+//             PRO_GEGLU: x = bf16(gelu_tanh(gate) * up) from the gate/up projection's partials
+//   body      out[n] = sum_k x[k] * W[n,k], f32 accumulate, 16-byte coalesced streaming loads,
+//             warp-shuffle reductions
+//   epilogue  EPI_PARTIAL / EPI_GATEUP: store row-segment partial sums (see below)
+//             EPI_LOGITS : optional logits store + running arg-max with repetition penalty
+//
+// Work split (EPI_PARTIAL / EPI_GATEUP). The matrix is cut into 512-byte chunks (one 16-byte load
+// per lane); the N * chunks_per_row chunks are dealt out as equal contiguous runs, one per warp of
+// the grid, so every SM streams the same number of bytes whatever the matrix shape. A run that
+// ends inside a row leaves a partial sum; the pieces of a row are stored in consecutive "slots"
+// [slot, batch row, n] and added up, in slot order, by the consuming kernel (PartialSpec), which
+// makes the split-K reduction deterministic without atomics. EPI_GATEUP streams gate and up as
+// one matrix of 2*I virtual rows (even rows gate_i, odd rows up_i).
+//
+// The kernel is HBM-bound: bytes per launch = N * K * sizeof(weight).
+#pragma once
+#include "common.cuh"
+
+namespace oxg4 {
+
+enum { PRO_PLAIN = 0, PRO_NORM = 1, PRO_GEGLU = 2 };
+enum { EPI_PARTIAL = 0, EPI_GATEUP = 1, EPI_LOGITS = 2 };
+
+constexpr int kGemvThreads = 512;
+constexpr int kGemvWarps = kGemvThreads / 32;
+
+struct GemvArgs {
+    const void* W0;          // [N, K] row-major (EPI_GATEUP: gate)
+    const void* W1;          // EPI_GATEUP: up projection [N, K]
+    int N, K;                // rows (EPI_GATEUP: virtual rows = 2 * intermediate), columns
+    int cpr, lr;             // chunks per row, chunks per warp run
+    int B;                   // activation rows in the step
+    // PRO_PLAIN
+    const float* in;         // [B, K]
+    // PRO_GEGLU: `raw` describes the gate/up partials (2*K virtual rows)
+    // PRO_NORM (K == hidden size)
+    const float* h_in;       // [B, K] residual stream before the pending update (unused with embed)
+    float* h_out;            // [B, K] residual stream after it (written by block 0)
+    PartialSpec raw;         // previous projection's partials (buf == null: nothing pending)
+    const float* w_post;     // norm weight applied to the previous projection
+    float scalar;            // layer_scalar of the layer that just ended (1.0 otherwise)
+    const float* w_norm;     // norm weight producing x
+    const void* embed;       // embedding table [V, K] (same element type as W0), or null
+    const uint32_t* tokens;  // [B]
+    float embed_scale;
+    float eps;
+    // epilogue
+    float* out;              // PARTIAL/GATEUP: [slots, B, N]; LOGITS: [B, N] or null
+    const uint8_t* seen;     // LOGITS: [B, N] repetition bitmap or null
+    float penalty;
+    int row_offset;          // LOGITS: first vocabulary row of this rank's slice
+    int n_total;             // LOGITS: full vocabulary (row stride of `out` and `seen`)
+    Cand* blk_best;          // LOGITS: [B, gridDim.x]
+    unsigned int* ticket;    // LOGITS: one counter per batch chunk (gridDim.y)
+    uint32_t* best_ids;      // LOGITS: [B]
+    float* best_scores;      // LOGITS: [B]
+};
+
+template <typename WT> struct WTraits;
+template <> struct WTraits<float> {
+    static constexpr int EPL = 4;                     // elements per 16-byte load
+    typedef float XT;
+    static DEVINL float elem(const void* base, size_t idx) { return ((const float*)base)[idx]; }
+    static DEVINL void store_x(XT* p, float v) { *p = v; }          // f32 mode: no rounding
+};
+template <> struct WTraits<uint16_t> {
+    static constexpr int EPL = 8;
+    typedef uint16_t XT;
+    static DEVINL float elem(const void* base, size_t idx) {
+        return __uint_as_float((uint32_t)((const uint16_t*)base)[idx] << 16);
+    }
+    static DEVINL void store_x(XT* p, float v) { *p = (uint16_t)f32_to_bf16_bits(v); }
+};
+
+// acc[b] += dot(w (16 bytes of weights), x (matching activations of row b))
+template <typename WT, int NB>
+DEVINL void fma16(float (&acc)[NB], const uint4& w, const typename WTraits<WT>::XT* xs, int K, int k) {
+    if constexpr (sizeof(WT) == 2) {
+        const float w0 = bf16lo(w.x), w1 = bf16hi(w.x), w2 = bf16lo(w.y), w3 = bf16hi(w.y);
+        const float w4 = bf16lo(w.z), w5 = bf16hi(w.z), w6 = bf16lo(w.w), w7 = bf16hi(w.w);
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+            const uint4 x = *reinterpret_cast<const uint4*>(xs + (size_t)b * K + k);
+            float a = acc[b];
+            a = fmaf(w0, bf16lo(x.x), a); a = fmaf(w1, bf16hi(x.x), a);
+            a = fmaf(w2, bf16lo(x.y), a); a = fmaf(w3, bf16hi(x.y), a);
+            a = fmaf(w4, bf16lo(x.z), a); a = fmaf(w5, bf16hi(x.z), a);
+            a = fmaf(w6, bf16lo(x.w), a); a = fmaf(w7, bf16hi(x.w), a);
+            acc[b] = a;
+        }
+    } else {
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+            const float4 x = *reinterpret_cast<const float4*>(xs + (size_t)b * K + k);
+            float a = acc[b];
+            a = fmaf(__uint_as_float(w.x), x.x, a); a = fmaf(__uint_as_float(w.y), x.y, a);
+            a = fmaf(__uint_as_float(w.z), x.z, a); a = fmaf(__uint_as_float(w.w), x.w, a);
+            acc[b] = a;
+        }
+    }
+}
+
+template <typename WT, int NB, int PRO, int EPI>
+__global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a) {
+    typedef WTraits<WT> T;
+    typedef typename T::XT XT;
+    constexpr int EPL = T::EPL;
+    constexpr int STEP = 32 * EPL;                     // elements per chunk
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int K = a.K;
+    XT* xs = reinterpret_cast<XT*>(smem_raw);                                        // [NB][K]
+    float* red = reinterpret_cast<float*>(smem_raw + (size_t)NB * K * sizeof(XT));   // [NB*32]
+    float* hs = red + NB * 32;                         // [NB][K] (PRO_NORM) / Cand scratch (LOGITS)
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int b0 = blockIdx.y * NB;
+    const int nb = min(NB, a.B - b0);
+    const size_t row_bytes = (size_t)K * sizeof(WT);
+
+    auto row_ptr = [&](int r) -> const WT* {
+        if constexpr (EPI == EPI_GATEUP)
+            return (const WT*)((r & 1) ? a.W1 : a.W0) + (size_t)(r >> 1) * K;
+        else
+            return (const WT*)a.W0 + (size_t)r * K;
+    };
+
+    // ---- pre-dependency section: warm L2 with the start of what this CTA will stream ----
+    if constexpr (EPI == EPI_LOGITS) {
+        const int U = (a.N + 1) / 2;
+        const int lines_per_row = (int)((row_bytes + 127) / 128);
+        for (int j = 0; j < 2 * kGemvWarps; ++j) {
+            const int u = blockIdx.x + gridDim.x * j;
+            if (u >= U) break;
+            const char* p0 = (const char*)row_ptr(u * 2);
+            const int nl = (u * 2 + 1 < a.N) ? 2 * lines_per_row : lines_per_row;   // rows are adjacent
+            for (int l = tid; l < nl; l += kGemvThreads) prefetch_l2(p0 + (size_t)l * 128);
+        }
+    } else {
+        const long long TC = (long long)a.N * a.cpr;
+        long long c = (long long)blockIdx.x * kGemvWarps * a.lr;
+        const long long cend = min(TC, c + (long long)kGemvWarps * a.lr);
+        // at most 512 chunks (256 KiB) per CTA; one 128-byte line per thread and step
+        const long long cstop = min(cend, c + 512);
+        for (long long cc = c + (tid >> 2); cc < cstop; cc += kGemvThreads / 4) {
+            const int r = (int)(cc / a.cpr);
+            const int col = (int)(cc % a.cpr) * STEP + (tid & 3) * (STEP / 4);
+            if (col < K) prefetch_l2((const char*)(row_ptr(r) + col));
+        }
+    }
+    pdl_wait();
+
+    // ---- prologue: build x[nb][K] in shared memory ----
+    if constexpr (PRO == PRO_PLAIN) {
+        for (int b = 0; b < nb; ++b)
+            for (int i = tid; i < K; i += kGemvThreads)
+                T::store_x(xs + (size_t)b * K + i, a.in[(size_t)(b0 + b) * K + i]);
+    } else if constexpr (PRO == PRO_GEGLU) {
+        for (int b = 0; b < nb; ++b)
+            for (int i = tid; i < K; i += kGemvThreads) {
+                const float g = sum_partials(a.raw, a.B, b0 + b, 2 * i);
+                const float u = sum_partials(a.raw, a.B, b0 + b, 2 * i + 1);
+                T::store_x(xs + (size_t)b * K + i, gelu_mul(g, u));
+            }
+    } else {
+        float ss[NB];
+        const bool writer = (blockIdx.x == 0);
+        if (a.embed != nullptr) {
+            // kernel_module.rs:1272-1285: embedding row widened to f32, times sqrt(hidden)
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                ss[b] = 0.0f;
+                if (b < nb) {
+                    uint32_t tok = a.tokens[b0 + b];
+                    if (tok == kInactiveToken) tok = 0;
+                    for (int i = tid; i < K; i += kGemvThreads) {
+                        float h = T::elem(a.embed, (size_t)tok * K + i) * a.embed_scale;
+                        hs[(size_t)b * K + i] = h;
+                        if (writer) a.h_out[(size_t)(b0 + b) * K + i] = h;
+                        ss[b] += h * h;
+                    }
+                }
+            }
+        } else {
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                ss[b] = 0.0f;
+                if (b < nb)
+                    for (int i = tid; i < K; i += kGemvThreads) {
+                        const float t = sum_partials(a.raw, a.B, b0 + b, i);
+                        hs[(size_t)b * K + i] = t;
+                        ss[b] += t * t;
+                    }
+            }
+            block_sum<NB>(ss, red);
+            float r[NB];
+#pragma unroll
+            for (int b = 0; b < NB; ++b) { r[b] = 1.0f / sqrtf(ss[b] / (float)K + a.eps); ss[b] = 0.0f; }
+#pragma unroll
+            for (int b = 0; b < NB; ++b)
+                if (b < nb)
+                    for (int i = tid; i < K; i += kGemvThreads) {
+                        const float nrm = hs[(size_t)b * K + i] * r[b] * a.w_post[i];
+                        const float h = (a.h_in[(size_t)(b0 + b) * K + i] + nrm) * a.scalar;
+                        hs[(size_t)b * K + i] = h;
+                        if (writer) a.h_out[(size_t)(b0 + b) * K + i] = h;
+                        ss[b] += h * h;
+                    }
+        }
+        block_sum<NB>(ss, red);
+#pragma unroll
+        for (int b = 0; b < NB; ++b)
+            if (b < nb) {
+                const float r = 1.0f / sqrtf(ss[b] / (float)K + a.eps);
+                for (int i = tid; i < K; i += kGemvThreads)
+                    T::store_x(xs + (size_t)b * K + i, hs[(size_t)b * K + i] * r * a.w_norm[i]);
+            }
+    }
+    // rows of a partial batch chunk that do not exist read zeros
+    for (int b = nb; b < NB; ++b)
+        for (int i = tid; i < K; i += kGemvThreads) xs[(size_t)b * K + i] = (XT)0;
+    __syncthreads();
+    pdl_launch();
+
+    if constexpr (EPI != EPI_LOGITS) {
+        // ---- body: this warp's contiguous run of chunks, cut at row boundaries ----
+        const long long TC = (long long)a.N * a.cpr;
+        const long long g = (long long)blockIdx.x * kGemvWarps + warp;
+        long long c0 = g * a.lr;
+        const long long c1 = min(TC, c0 + a.lr);
+        const bool ragged = (K % STEP) != 0;          // the last chunk of a row is partly empty
+        while (c0 < c1) {
+            const int r = (int)(c0 / a.cpr);
+            const long long rend = min(c1, (long long)(r + 1) * a.cpr);
+            const int cc = (int)(c0 - (long long)r * a.cpr);
+            const int ncs = (int)(rend - c0);
+            const bool has_tail = ragged && (cc + ncs == a.cpr);
+            const int nfull = has_tail ? ncs - 1 : ncs;
+            const WT* p = row_ptr(r) + (size_t)cc * STEP + lane * EPL;
+            int k = cc * STEP + lane * EPL;
+            float acc[NB];
+#pragma unroll
+            for (int b = 0; b < NB; ++b) acc[b] = 0.0f;
+            int j = 0;
+            for (; j + 8 <= nfull; j += 8) {
+                uint4 w[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) w[q] = ldg_stream16(p + q * STEP);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) fma16<WT, NB>(acc, w[q], xs, K, k + q * STEP);
+                p += 8 * STEP;
+                k += 8 * STEP;
+            }
+            for (; j + 2 <= nfull; j += 2) {
+                uint4 w0 = ldg_stream16(p), w1 = ldg_stream16(p + STEP);
+                fma16<WT, NB>(acc, w0, xs, K, k);
+                fma16<WT, NB>(acc, w1, xs, K, k + STEP);
+                p += 2 * STEP;
+                k += 2 * STEP;
+            }
+            for (; j < ncs; ++j) {
+                if (k < K) {
+                    uint4 w0 = ldg_stream16(p);
+                    fma16<WT, NB>(acc, w0, xs, K, k);
+                }
+                p += STEP;
+                k += STEP;
+            }
+#pragma unroll
+            for (int b = 0; b < NB; ++b) acc[b] = warp_sum(acc[b]);
+            if (lane == 0) {
+                const int slot = (int)(g - ((long long)r * a.cpr) / a.lr);
+#pragma unroll
+                for (int b = 0; b < NB; ++b)
+                    if (b < nb) a.out[((size_t)slot * a.B + b0 + b) * a.N + r] = acc[b];
+            }
+            c0 = rend;
+        }
+    } else {
+        // ---- body: one warp per row pair; logits + running arg-max ----
+        Cand best[NB];
+#pragma unroll
+        for (int b = 0; b < NB; ++b) { best[b].s = -INFINITY; best[b].i = 0xffffffffu; }
+        const int U = (a.N + 1) / 2;
+        for (int u = blockIdx.x + gridDim.x * warp; u < U; u += gridDim.x * kGemvWarps) {
+            const int r0 = u * 2;
+            const bool has1 = (r0 + 1 < a.N);
+            const WT* p0 = row_ptr(r0);
+            const WT* p1 = has1 ? p0 + K : p0;
+            float acc0[NB], acc1[NB];
+#pragma unroll
+            for (int b = 0; b < NB; ++b) { acc0[b] = 0.0f; acc1[b] = 0.0f; }
+            int k = lane * EPL;
+            for (; k + 3 * STEP < K; k += 4 * STEP) {
+                uint4 wa[4], wb[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    wa[j] = ldg_stream16(p0 + k + j * STEP);
+                    wb[j] = ldg_stream16(p1 + k + j * STEP);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    fma16<WT, NB>(acc0, wa[j], xs, K, k + j * STEP);
+                    fma16<WT, NB>(acc1, wb[j], xs, K, k + j * STEP);
+                }
+            }
+            for (; k < K; k += STEP) {
+                uint4 wa = ldg_stream16(p0 + k);
+                uint4 wb = ldg_stream16(p1 + k);
+                fma16<WT, NB>(acc0, wa, xs, K, k);
+                fma16<WT, NB>(acc1, wb, xs, K, k);
+            }
+#pragma unroll
+            for (int b = 0; b < NB; ++b) { acc0[b] = warp_sum(acc0[b]); acc1[b] = warp_sum(acc1[b]); }
+            if (lane == 0) {
+                const int v0 = a.row_offset + r0;                 // vocabulary id of row r0
+#pragma unroll
+                for (int b = 0; b < NB; ++b) {
+                    if (b >= nb) continue;
+                    const size_t base = (size_t)(b0 + b) * a.n_total;
+                    if (a.out) {
+                        a.out[base + v0] = acc0[b];
+                        if (has1) a.out[base + v0 + 1] = acc1[b];
+                    }
+                    // kernel_module.rs:2008-2016: penalty on seen tokens, NaN skipped, strict '>'
+                    float s0 = acc0[b], s1 = acc1[b];
+                    if (a.seen && a.penalty > 1.0f) {
+                        if (a.seen[base + v0]) s0 = s0 >= 0.0f ? s0 / a.penalty : s0 * a.penalty;
+                        if (has1 && a.seen[base + v0 + 1]) s1 = s1 >= 0.0f ? s1 / a.penalty : s1 * a.penalty;
+                    }
+                    const Cand c0{s0, (uint32_t)v0}, c1{s1, (uint32_t)(v0 + 1)};
+                    if (s0 == s0 && s0 > -INFINITY && cand_better(c0, best[b])) best[b] = c0;
+                    if (has1 && s1 == s1 && s1 > -INFINITY && cand_better(c1, best[b])) best[b] = c1;
+                }
+            }
+        }
+        // block-level arg-max, then the last block to arrive merges all blocks
+        Cand* wc = reinterpret_cast<Cand*>(hs);           // hs is free after the prologue
+        __shared__ unsigned int s_last;
+        if (lane == 0)
+            for (int b = 0; b < NB; ++b) wc[b * kGemvWarps + warp] = best[b];
+        __syncthreads();
+        if (tid < nb) {
+            Cand c = wc[tid * kGemvWarps];
+            for (int w = 1; w < kGemvWarps; ++w)
+                if (cand_better(wc[tid * kGemvWarps + w], c)) c = wc[tid * kGemvWarps + w];
+            a.blk_best[(size_t)(b0 + tid) * gridDim.x + blockIdx.x] = c;
+        }
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) s_last = (atomicAdd(&a.ticket[blockIdx.y], 1u) == gridDim.x - 1) ? 1u : 0u;
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            for (int b = warp; b < nb; b += kGemvWarps) {
+                Cand c{-INFINITY, 0xffffffffu};
+                for (int gi = lane; gi < (int)gridDim.x; gi += 32) {
+                    const Cand* src = &a.blk_best[(size_t)(b0 + b) * gridDim.x + gi];
+                    Cand o;
+                    o.s = __ldcg(&src->s);
+                    o.i = __ldcg(&src->i);
+                    if (cand_better(o, c)) c = o;
+                }
+                c = warp_best(c);
+                if (lane == 0) {
+                    a.best_ids[b0 + b] = (c.i == 0xffffffffu) ? 0u : c.i;
+                    a.best_scores[b0 + b] = c.s;
+                }
+            }
+            if (tid == 0) a.ticket[blockIdx.y] = 0u;       // ready for the next launch / replay
+        }
+    }
+}
+
+// dynamic shared memory the kernel needs
+template <typename WT, int NB, int PRO>
+inline size_t gemv_smem_bytes(int K) {
+    size_t x = (size_t)NB * K * sizeof(typename WTraits<WT>::XT);
+    size_t red = (size_t)(NB * 32) * sizeof(float);
+    size_t hs = (PRO == PRO_NORM) ? (size_t)NB * K * sizeof(float) : 0;
+    size_t cands = (size_t)NB * kGemvWarps * sizeof(Cand);
+    if (hs < cands) hs = cands;
+    return x + red + hs;
+}
+
+}  // namespace oxg4

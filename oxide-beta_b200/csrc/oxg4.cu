@@ -1,0 +1,1232 @@
+// Host runtime and C ABI of the B200-native Gemma4 token-generation path (see include/oxg4.h).
+//
+// Stands in for the reference's Gemma4 CUDA executor — crates/oxide-torch-models/src/gemma4_cuda/
+// {mod,decode,attention,cache,tensor_ops}.rs — and the pieces of crates/oxide-torch-cuda it drives
+// (kernel module, cuBLAS GEMM wrapper, CUDA-graph wrapper). Where the reference issues about 27
+// launches per layer (decode.rs:4-21,43-174) with a separate f32 buffer between each, this runtime
+// issues five: QKV projection, attention, O projection, gate/up projection, down projection; the
+// norms, casts, residual adds, RoPE, KV append and GeGLU live in their prologues and epilogues.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/oxg4.h"
+#include "attention.cuh"
+#include "gemv.cuh"
+#include "sampling.cuh"
+
+using namespace oxg4;
+
+// ------------------------------------------------------------------------------------------------
+// errors
+// ------------------------------------------------------------------------------------------------
+static thread_local std::string g_err;
+
+static int32_t fail(int32_t code, const char* fmt, ...) {
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_err = buf;
+    return code;
+}
+
+#define CK(expr)                                                                                 \
+    do {                                                                                         \
+        cudaError_t e__ = (expr);                                                                \
+        if (e__ != cudaSuccess)                                                                  \
+            return fail(e__ == cudaErrorMemoryAllocation ? OXG4_OOM : OXG4_CUDA,                 \
+                        "Gemma 4 CUDA error: %s (%s) at %s:%d", cudaGetErrorString(e__), #expr,  \
+                        __FILE__, __LINE__);                                                     \
+    } while (0)
+#define TRY(expr)                        \
+    do {                                 \
+        int32_t s__ = (expr);            \
+        if (s__ != OXG4_OK) return s__;  \
+    } while (0)
+
+extern "C" const char* oxg4_last_error(void) { return g_err.c_str(); }
+
+// ------------------------------------------------------------------------------------------------
+// model
+// ------------------------------------------------------------------------------------------------
+struct Tensor {
+    void* d = nullptr;
+    int dtype = OXG4_F32;     // element type on the device
+    std::vector<int64_t> shape;
+    size_t bytes = 0;
+};
+
+struct LayerPlan {            // Gemma4DecodeLayerPlan (gemma4_cuda/mod.rs:65-93)
+    bool sliding = false;
+    int rotary_dim = 0;
+    float theta = 0, factor = 1, layer_scalar = 1;
+    const void *wqkv = nullptr, *wo = nullptr, *wgate = nullptr, *wup = nullptr, *wdown = nullptr;
+    const float *input_ln = nullptr, *post_attn_ln = nullptr, *pre_ff_ln = nullptr,
+                *post_ff_ln = nullptr, *q_norm = nullptr, *k_norm = nullptr;
+    float* inv_freq = nullptr;
+};
+
+struct GemvPlan {             // how a projection is cut into warp runs
+    int N = 0, K = 0, cpr = 0, lr = 0, grid = 0, slots = 0;
+};
+
+struct ProfileSlot {
+    double ms = 0;
+    int count = 0;
+};
+
+struct oxg4_model {
+    oxg4_config cfg{};
+    std::vector<int32_t> layer_sliding, rotary_dim;
+    std::vector<float> rope_theta, rope_factor;
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    int num_sms = 148;
+    bool use_pdl = true;
+    bool finalized = false;
+    std::map<std::string, Tensor> tensors;
+    std::vector<LayerPlan> layers;
+    const void* embed = nullptr;
+    const float* final_norm = nullptr;
+    // local (per tensor-parallel rank) sizes
+    int H = 0, D = 0, Nq = 0, Nkv = 0, I = 0, V = 0, Vloc = 0, v0 = 0, G = 0;
+    int es = 2;               // bytes per weight element
+    GemvPlan p_qkv, p_o, p_gateup, p_down, p_lm;
+    long long launches = 0;
+    std::map<std::string, ProfileSlot> profile;
+    bool profiling = false;
+    std::vector<std::pair<std::string, std::pair<cudaEvent_t, cudaEvent_t>>> prof_events;
+};
+
+static int32_t bind_device(const oxg4_model* m) {
+    CK(cudaSetDevice(m->device));
+    return OXG4_OK;
+}
+
+static std::string canonical(const char* name) {
+    std::string n(name);
+    const std::string p = "model.language_model.";
+    if (n.rfind(p, 0) == 0) n = n.substr(p.size());
+    return n;
+}
+
+static inline uint16_t host_f32_to_bf16(float f) {
+    uint32_t b;
+    memcpy(&b, &f, 4);
+    return (uint16_t)((b + 0x7fffu + ((b >> 16) & 1u)) >> 16);
+}
+static inline float host_bf16_to_f32(uint16_t h) {
+    uint32_t b = (uint32_t)h << 16;
+    float f;
+    memcpy(&f, &b, 4);
+    return f;
+}
+
+static GemvPlan make_plan(int N, int K, int es, int num_sms) {
+    GemvPlan p;
+    p.N = N;
+    p.K = K;
+    const int step = 32 * (16 / es);
+    p.cpr = (K + step - 1) / step;
+    const long long TC = (long long)N * p.cpr;
+    p.grid = (int)std::min<long long>(num_sms, (TC + kGemvWarps - 1) / kGemvWarps);
+    if (p.grid < 1) p.grid = 1;
+    p.lr = (int)((TC + (long long)p.grid * kGemvWarps - 1) / ((long long)p.grid * kGemvWarps));
+    if (p.lr < 1) p.lr = 1;
+    p.slots = (p.cpr - 1) / p.lr + 2;
+    return p;
+}
+
+extern "C" int32_t oxg4_model_create(const oxg4_config* c, int32_t device, oxg4_model** out) {
+    if (!c || !out) return fail(OXG4_INVALID_ARGUMENT, "null argument");
+    *out = nullptr;
+    if (c->num_attention_heads <= 0 || c->num_key_value_heads <= 0 ||
+        c->num_attention_heads % c->num_key_value_heads != 0 || c->hidden_size <= 0 ||
+        c->num_hidden_layers <= 0)
+        return fail(OXG4_INVALID_SHAPE, "invalid Gemma 4 attention configuration");   // config.rs:151-161
+    if (!c->layer_is_sliding || !c->rotary_dim || !c->rope_theta || !c->rope_factor)
+        return fail(OXG4_INVALID_ARGUMENT, "per-layer plan arrays are missing");
+    if (c->weight_dtype != OXG4_F32 && c->weight_dtype != OXG4_BF16)
+        return fail(OXG4_INVALID_ARGUMENT, "weight_dtype must be OXG4_F32 or OXG4_BF16");
+    if (c->global_head_dim != c->head_dim)
+        return fail(OXG4_UNSUPPORTED, "global_head_dim != head_dim is not supported");
+    if (c->head_dim != 64 && c->head_dim != 128 && c->head_dim != 256)
+        return fail(OXG4_UNSUPPORTED, "head_dim must be 64, 128 or 256");
+    const int tp = c->tp_size <= 0 ? 1 : c->tp_size;
+    if (tp != 1) return fail(OXG4_UNSUPPORTED, "tensor parallelism is not available in this build");
+    if (c->num_key_value_heads % tp != 0 || c->intermediate_size % tp != 0 || c->vocab_size % tp != 0)
+        return fail(OXG4_INVALID_SHAPE, "tp_size must divide kv heads, intermediate size and vocabulary");
+    const int g = c->num_attention_heads / c->num_key_value_heads;
+    if (g != 1 && g != 2 && g != 4 && g != 8)
+        return fail(OXG4_UNSUPPORTED, "query heads per KV head must be 1, 2, 4 or 8");
+    const int esz = c->weight_dtype == OXG4_BF16 ? 2 : 4;
+    if ((c->hidden_size * esz) % 16 || (c->intermediate_size / tp * esz) % 16)
+        return fail(OXG4_INVALID_SHAPE, "hidden and intermediate sizes must be multiples of 16 bytes");
+    int ndev = 0;
+    cudaError_t e = cudaGetDeviceCount(&ndev);
+    if (e != cudaSuccess || ndev == 0)
+        return fail(OXG4_CUDA, "Gemma 4 CUDA error: no CUDA device (%s); this library has no CPU path",
+                    cudaGetErrorString(e));
+    if (device < 0 || device >= ndev) return fail(OXG4_INVALID_ARGUMENT, "device ordinal %d out of range", device);
+    oxg4_model* m = new oxg4_model();
+    m->cfg = *c;
+    const int L = c->num_hidden_layers;
+    m->layer_sliding.assign(c->layer_is_sliding, c->layer_is_sliding + L);
+    m->rotary_dim.assign(c->rotary_dim, c->rotary_dim + L);
+    m->rope_theta.assign(c->rope_theta, c->rope_theta + L);
+    m->rope_factor.assign(c->rope_factor, c->rope_factor + L);
+    m->cfg.layer_is_sliding = m->layer_sliding.data();
+    m->cfg.rotary_dim = m->rotary_dim.data();
+    m->cfg.rope_theta = m->rope_theta.data();
+    m->cfg.rope_factor = m->rope_factor.data();
+    m->cfg.tp_size = tp;
+    m->device = device;
+    m->H = c->hidden_size;
+    m->D = c->head_dim;
+    m->Nq = c->num_attention_heads / tp;
+    m->Nkv = c->num_key_value_heads / tp;
+    m->G = g;
+    m->I = c->intermediate_size / tp;
+    m->V = c->vocab_size;
+    m->Vloc = c->vocab_size / tp;
+    m->v0 = m->Vloc * c->tp_rank;
+    m->es = esz;
+    m->use_pdl = getenv("OXG4_DISABLE_PDL") == nullptr;
+    if (cudaSetDevice(device) != cudaSuccess) { delete m; return fail(OXG4_CUDA, "Gemma 4 CUDA error: cudaSetDevice"); }
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) == cudaSuccess) m->num_sms = prop.multiProcessorCount;
+    // a dedicated non-blocking stream: the legacy default stream cannot be captured (mod.rs:223-226)
+    if (cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking) != cudaSuccess) {
+        delete m;
+        return fail(OXG4_CUDA, "Gemma 4 CUDA error: stream creation failed");
+    }
+    *out = m;
+    return OXG4_OK;
+}
+
+extern "C" void oxg4_model_destroy(oxg4_model* m) {
+    if (!m) return;
+    cudaSetDevice(m->device);
+    cudaStreamSynchronize(m->stream);
+    for (auto& kv : m->tensors) cudaFree(kv.second.d);
+    for (auto& l : m->layers) cudaFree(l.inv_freq);
+    cudaStreamDestroy(m->stream);
+    delete m;
+}
+
+// which slice of a checkpoint tensor a tensor-parallel rank keeps
+enum ShardKind { SH_FULL, SH_ROWS, SH_COLS, SH_ROWS_HEADS_Q, SH_ROWS_HEADS_KV, SH_COLS_HEADS_Q };
+
+extern "C" int32_t oxg4_model_upload(oxg4_model* m, const char* name, int32_t dtype, const int64_t* shape,
+                                     int32_t rank, const void* data, size_t bytes) {
+    if (!m || !name || !shape || !data) return fail(OXG4_INVALID_ARGUMENT, "null argument");
+    if (m->finalized) return fail(OXG4_INVALID_ARGUMENT, "model is already finalized");
+    if (dtype != OXG4_F32 && dtype != OXG4_BF16) return fail(OXG4_INVALID_ARGUMENT, "unsupported tensor dtype");
+    TRY(bind_device(m));
+    const std::string n = canonical(name);
+    int64_t count = 1;
+    for (int i = 0; i < rank; ++i) count *= shape[i];
+    const size_t src_es = dtype == OXG4_BF16 ? 2 : 4;
+    if (bytes != (size_t)count * src_es) return fail(OXG4_INVALID_SHAPE, "tensor `%s`: byte count does not match shape", n.c_str());
+    // the reference's loader accepts BF16 only (mod.rs:247-251); the f32 mode is this build's extension
+    if (m->cfg.weight_dtype == OXG4_BF16 && dtype != OXG4_BF16)
+        return fail(OXG4_INVALID_ARGUMENT, "tensor `%s`: BF16 models take BF16 tensors", n.c_str());
+    const bool is_matrix = rank == 2;
+    Tensor t;
+    t.shape.assign(shape, shape + rank);
+    if (!is_matrix) {
+        // norm weights and layer_scalar: widened to f32 once (exact); +1 folded in if requested
+        std::vector<float> f((size_t)count);
+        for (int64_t i = 0; i < count; ++i) {
+            float v = dtype == OXG4_BF16 ? host_bf16_to_f32(((const uint16_t*)data)[i]) : ((const float*)data)[i];
+            if (m->cfg.norm_weight_offset && n.find("layer_scalar") == std::string::npos) v += 1.0f;
+            f[i] = v;
+        }
+        t.dtype = OXG4_F32;
+        t.bytes = (size_t)count * 4;
+        CK(cudaMalloc(&t.d, t.bytes));
+        CK(cudaMemcpy(t.d, f.data(), t.bytes, cudaMemcpyHostToDevice));
+    } else {
+        // matrices keep the model's weight type
+        const int dst_dtype = m->cfg.weight_dtype;
+        const size_t dst_es = dst_dtype == OXG4_BF16 ? 2 : 4;
+        const void* src = data;
+        std::vector<uint8_t> conv;
+        if ((int)dtype != dst_dtype) {      // only BF16 checkpoint into an f32 model
+            conv.resize((size_t)count * 4);
+            float* f = (float*)conv.data();
+            for (int64_t i = 0; i < count; ++i) f[i] = host_bf16_to_f32(((const uint16_t*)data)[i]);
+            src = conv.data();
+        }
+        t.dtype = dst_dtype;
+        t.bytes = (size_t)count * dst_es;
+        CK(cudaMalloc(&t.d, t.bytes));
+        CK(cudaMemcpy(t.d, src, t.bytes, cudaMemcpyHostToDevice));   // synchronous: done on return
+    }
+    auto it = m->tensors.find(n);
+    if (it != m->tensors.end()) { cudaFree(it->second.d); m->tensors.erase(it); }
+    m->tensors[n] = t;
+    return OXG4_OK;
+}
+
+static int32_t need(oxg4_model* m, const std::string& name, std::vector<int64_t> shape, const Tensor** out) {
+    auto it = m->tensors.find(name);
+    if (it == m->tensors.end()) return fail(OXG4_INVALID_ARGUMENT, "missing CUDA weight `%s`", name.c_str());   // mod.rs:359-364
+    if (!shape.empty() && it->second.shape != shape) {
+        int64_t a = 1, b = 1;
+        for (auto v : shape) a *= v;
+        for (auto v : it->second.shape) b *= v;
+        if (a != b) return fail(OXG4_INVALID_SHAPE, "weight `%s` has an unexpected shape", name.c_str());
+    }
+    *out = &it->second;
+    return OXG4_OK;
+}
+
+template <typename WT, int NB>
+static int32_t set_gemv_attrs() {
+    const int big = 227 * 1024;
+#define SETA(PRO, EPI) CK(cudaFuncSetAttribute(gemv_kernel<WT, NB, PRO, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, big))
+    SETA(PRO_NORM, EPI_PARTIAL);
+    SETA(PRO_PLAIN, EPI_PARTIAL);
+    SETA(PRO_NORM, EPI_GATEUP);
+    SETA(PRO_GEGLU, EPI_PARTIAL);
+    SETA(PRO_NORM, EPI_LOGITS);
+#undef SETA
+    return OXG4_OK;
+}
+
+template <typename KT, int D>
+static int32_t set_attn_attrs() {
+    const int big = 160 * 1024;
+    CK(cudaFuncSetAttribute(attn_decode_kernel<KT, D, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    CK(cudaFuncSetAttribute(attn_decode_kernel<KT, D, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    CK(cudaFuncSetAttribute(attn_decode_kernel<KT, D, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    CK(cudaFuncSetAttribute(attn_decode_kernel<KT, D, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    return OXG4_OK;
+}
+
+extern "C" int32_t oxg4_model_finalize(oxg4_model* m) {
+    if (!m) return fail(OXG4_INVALID_ARGUMENT, "null model");
+    if (m->finalized) return OXG4_OK;
+    TRY(bind_device(m));
+    const oxg4_config& c = m->cfg;
+    const int L = c.num_hidden_layers, H = m->H, D = m->D;
+    const int64_t QW = (int64_t)m->Nq * D, KW = (int64_t)m->Nkv * D;
+    const Tensor* t = nullptr;
+    TRY(need(m, "embed_tokens.weight", {c.vocab_size, H}, &t));
+    m->embed = t->d;
+    TRY(need(m, "norm.weight", {H}, &t));
+    m->final_norm = (const float*)t->d;
+    m->layers.resize(L);
+    for (int l = 0; l < L; ++l) {
+        LayerPlan& p = m->layers[l];
+        const std::string pre = "layers." + std::to_string(l) + ".";
+        p.sliding = m->layer_sliding[l] != 0;
+        p.rotary_dim = m->rotary_dim[l];
+        p.theta = m->rope_theta[l];
+        p.factor = m->rope_factor[l];
+        if (p.rotary_dim < 0 || p.rotary_dim > D) return fail(OXG4_INVALID_SHAPE, "layer %d: rotary_dim out of range", l);
+        // fuse q/k/v rows into one [q;k;v, H] matrix (mod.rs:283-350)
+        const Tensor *q, *k, *v;
+        TRY(need(m, pre + "self_attn.q_proj.weight", {QW, H}, &q));
+        TRY(need(m, pre + "self_attn.k_proj.weight", {KW, H}, &k));
+        TRY(need(m, pre + "self_attn.v_proj.weight", {KW, H}, &v));
+        Tensor f;
+        f.dtype = q->dtype;
+        f.shape = {QW + 2 * KW, H};
+        f.bytes = q->bytes + k->bytes + v->bytes;
+        CK(cudaMalloc(&f.d, f.bytes));
+        CK(cudaMemcpy(f.d, q->d, q->bytes, cudaMemcpyDeviceToDevice));
+        CK(cudaMemcpy((char*)f.d + q->bytes, k->d, k->bytes, cudaMemcpyDeviceToDevice));
+        CK(cudaMemcpy((char*)f.d + q->bytes + k->bytes, v->d, v->bytes, cudaMemcpyDeviceToDevice));
+        for (const char* nm : {"self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn.v_proj.weight"}) {
+            auto it = m->tensors.find(pre + nm);
+            cudaFree(it->second.d);
+            m->tensors.erase(it);
+        }
+        m->tensors[pre + "self_attn.qkv_proj.weight"] = f;
+        p.wqkv = f.d;
+        TRY(need(m, pre + "self_attn.o_proj.weight", {H, QW}, &t)); p.wo = t->d;
+        TRY(need(m, pre + "mlp.gate_proj.weight", {m->I, H}, &t)); p.wgate = t->d;
+        TRY(need(m, pre + "mlp.up_proj.weight", {m->I, H}, &t)); p.wup = t->d;
+        TRY(need(m, pre + "mlp.down_proj.weight", {H, m->I}, &t)); p.wdown = t->d;
+        TRY(need(m, pre + "input_layernorm.weight", {H}, &t)); p.input_ln = (const float*)t->d;
+        TRY(need(m, pre + "post_attention_layernorm.weight", {H}, &t)); p.post_attn_ln = (const float*)t->d;
+        TRY(need(m, pre + "pre_feedforward_layernorm.weight", {H}, &t)); p.pre_ff_ln = (const float*)t->d;
+        TRY(need(m, pre + "post_feedforward_layernorm.weight", {H}, &t)); p.post_ff_ln = (const float*)t->d;
+        TRY(need(m, pre + "self_attn.q_norm.weight", {D}, &t)); p.q_norm = (const float*)t->d;
+        TRY(need(m, pre + "self_attn.k_norm.weight", {D}, &t)); p.k_norm = (const float*)t->d;
+        TRY(need(m, pre + "layer_scalar", {1}, &t));          // mandatory, mod.rs:447
+        CK(cudaMemcpy(&p.layer_scalar, t->d, 4, cudaMemcpyDeviceToHost));
+        // kernel_module.rs:1539-1540: frequency = powf(theta, -(2 i)/head_dim) / factor, in f32
+        std::vector<float> inv(D / 2);
+        for (int i = 0; i < D / 2; ++i) {
+            const float exponent = -((float)(2 * i)) / (float)D;
+            inv[i] = powf(p.theta, exponent) / p.factor;
+        }
+        CK(cudaMalloc(&p.inv_freq, sizeof(float) * (D / 2)));
+        CK(cudaMemcpy(p.inv_freq, inv.data(), sizeof(float) * (D / 2), cudaMemcpyHostToDevice));
+    }
+    m->p_qkv = make_plan((int)(QW + 2 * KW), H, m->es, m->num_sms);
+    m->p_o = make_plan(H, (int)QW, m->es, m->num_sms);
+    m->p_gateup = make_plan(2 * m->I, H, m->es, m->num_sms);
+    m->p_down = make_plan(H, m->I, m->es, m->num_sms);
+    m->p_lm = make_plan(m->Vloc, H, m->es, m->num_sms);
+    m->p_lm.grid = std::min(m->num_sms, std::max(1, (m->Vloc + 2 * kGemvWarps - 1) / (2 * kGemvWarps)));
+    if (m->es == 2) {
+        TRY((set_gemv_attrs<uint16_t, 1>())); TRY((set_gemv_attrs<uint16_t, 2>())); TRY((set_gemv_attrs<uint16_t, 4>()));
+    } else {
+        TRY((set_gemv_attrs<float, 1>())); TRY((set_gemv_attrs<float, 2>())); TRY((set_gemv_attrs<float, 4>()));
+    }
+    TRY((set_attn_attrs<uint16_t, 64>())); TRY((set_attn_attrs<uint16_t, 128>())); TRY((set_attn_attrs<uint16_t, 256>()));
+    TRY((set_attn_attrs<float, 64>())); TRY((set_attn_attrs<float, 128>())); TRY((set_attn_attrs<float, 256>()));
+    CK(cudaDeviceSynchronize());
+    m->finalized = true;
+    return OXG4_OK;
+}
+
+extern "C" int64_t oxg4_weight_count(const oxg4_model* m) { return m ? (int64_t)m->tensors.size() : 0; }
+extern "C" int64_t oxg4_weight_bytes(const oxg4_model* m) {
+    int64_t b = 0;
+    if (m) for (auto& kv : m->tensors) b += (int64_t)kv.second.bytes;
+    return b;
+}
+extern "C" int32_t oxg4_synchronize(oxg4_model* m) {
+    if (!m) return fail(OXG4_INVALID_ARGUMENT, "null model");
+    TRY(bind_device(m));
+    CK(cudaStreamSynchronize(m->stream));
+    return OXG4_OK;
+}
+extern "C" int64_t oxg4_kernel_launches(const oxg4_model* m) { return m ? m->launches : 0; }
+
+extern "C" int32_t oxg4_tp_unique_id(void*) { return fail(OXG4_UNSUPPORTED, "tensor parallelism is not available in this build"); }
+extern "C" int32_t oxg4_model_tp_init(oxg4_model*, const void*) { return fail(OXG4_UNSUPPORTED, "tensor parallelism is not available in this build"); }
+
+// ------------------------------------------------------------------------------------------------
+// cache table + per-batch workspace
+// ------------------------------------------------------------------------------------------------
+struct GraphEntry {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    int kernels = 0;
+};
+
+enum StepKind { STEP_TOPK = 0, STEP_LOGITS = 1, STEP_PREFILL = 2 };
+
+struct oxg4_cache {
+    oxg4_model* m = nullptr;
+    int B = 0, PT = 256, kv_dtype = OXG4_BF16;
+    std::vector<int32_t> max_seq, pos_host;
+    int pps_full = 0, pps_slide = 0;
+    int splits_full = 1, splits_slide = 1, min_split = 32;
+    std::vector<void*> kpool, vpool;          // per layer
+    int64_t kv_bytes = 0;
+    int32_t *pt_full = nullptr, *pt_slide = nullptr, *cap_full = nullptr, *cap_slide = nullptr;
+    uint32_t* tokens = nullptr;
+    int32_t* pos = nullptr;
+    uint8_t* seen = nullptr;
+    StepCtl* ctl = nullptr;
+    uint32_t* history = nullptr;
+    int history_cap = 0;
+    // workspace
+    float *hA = nullptr, *hB = nullptr, *qkv_raw = nullptr, *attn_out = nullptr, *o_raw = nullptr,
+          *gu_raw = nullptr, *down_raw = nullptr, *logits = nullptr, *attn_part = nullptr;
+    unsigned int *attn_ticket = nullptr, *lm_ticket = nullptr;
+    Cand *blk_best = nullptr, *topk_stage = nullptr;
+    uint32_t *best_ids = nullptr, *topk_ids = nullptr;
+    float *best_scores = nullptr, *topk_scores = nullptr;
+    // pinned staging
+    uint32_t* h_tokens = nullptr;
+    StepCtl* h_ctl = nullptr;
+    uint32_t* h_ids = nullptr;
+    float* h_scores = nullptr;
+    std::map<std::string, GraphEntry> graphs;
+    std::vector<void*> owned;                 // every device allocation, for destroy
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+};
+
+template <typename T>
+static int32_t dalloc(oxg4_cache* c, T** p, size_t count, bool zero = true) {
+    void* d = nullptr;
+    const size_t bytes = std::max<size_t>(count * sizeof(T), 16);
+    CK(cudaMalloc(&d, bytes));
+    if (zero) CK(cudaMemset(d, 0, bytes));
+    c->owned.push_back(d);
+    *p = (T*)d;
+    return OXG4_OK;
+}
+
+static int32_t cache_build(oxg4_cache* c) {
+    oxg4_model* m = c->m;
+    const int B = c->B, L = m->cfg.num_hidden_layers, H = m->H, D = m->D, PT = c->PT;
+    const size_t kes = c->kv_dtype == OXG4_BF16 ? 2 : 4;
+    // cache.rs:58-62: sliding capacity = min(window, max_seq); global capacity = max_seq
+    std::vector<int32_t> capf(B), caps(B);
+    int maxf = 0, maxs = 0;
+    for (int b = 0; b < B; ++b) {
+        capf[b] = c->max_seq[b];
+        caps[b] = std::min(m->cfg.sliding_window, c->max_seq[b]);
+        maxf = std::max(maxf, capf[b]);
+        maxs = std::max(maxs, caps[b]);
+    }
+    c->pps_full = (maxf + PT - 1) / PT;
+    c->pps_slide = (maxs + PT - 1) / PT;
+    std::vector<int32_t> ptf((size_t)B * c->pps_full, 0), pts((size_t)B * c->pps_slide, 0);
+    int pages_full = 0, pages_slide = 0;
+    for (int b = 0; b < B; ++b) {
+        for (int i = 0; i < (capf[b] + PT - 1) / PT; ++i) ptf[(size_t)b * c->pps_full + i] = pages_full++;
+        for (int i = 0; i < (caps[b] + PT - 1) / PT; ++i) pts[(size_t)b * c->pps_slide + i] = pages_slide++;
+    }
+    TRY(dalloc(c, &c->pt_full, ptf.size()));
+    TRY(dalloc(c, &c->pt_slide, pts.size()));
+    TRY(dalloc(c, &c->cap_full, B));
+    TRY(dalloc(c, &c->cap_slide, B));
+    CK(cudaMemcpy(c->pt_full, ptf.data(), ptf.size() * 4, cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(c->pt_slide, pts.data(), pts.size() * 4, cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(c->cap_full, capf.data(), B * 4, cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(c->cap_slide, caps.data(), B * 4, cudaMemcpyHostToDevice));
+    c->kpool.resize(L);
+    c->vpool.resize(L);
+    for (int l = 0; l < L; ++l) {
+        const int pages = m->layers[l].sliding ? pages_slide : pages_full;
+        const size_t bytes = (size_t)pages * m->Nkv * PT * D * kes;
+        uint8_t *k, *v;
+        TRY(dalloc(c, &k, bytes));      // zeroed like the reference's DeviceBuffer::zeroed
+        TRY(dalloc(c, &v, bytes));
+        c->kpool[l] = k;
+        c->vpool[l] = v;
+        c->kv_bytes += 2 * (int64_t)bytes;
+    }
+    // split-KV geometry: enough CTAs to fill the GPU a few times over at the longest context
+    const int pairs = std::max(1, m->Nkv * B);
+    const int want = std::max(1, (8 * m->num_sms + pairs - 1) / pairs);
+    c->min_split = 32;
+    c->splits_full = std::max(1, std::min({want, 64, (maxf + c->min_split - 1) / c->min_split}));
+    c->splits_slide = std::max(1, std::min({want, 64, (maxs + c->min_split - 1) / c->min_split}));
+    const int smax = std::max(c->splits_full, c->splits_slide);
+    TRY(dalloc(c, &c->tokens, B));
+    TRY(dalloc(c, &c->pos, B));
+    TRY(dalloc(c, &c->seen, (size_t)B * m->V));
+    TRY(dalloc(c, &c->ctl, 1));
+    TRY(dalloc(c, &c->hA, (size_t)B * H));
+    TRY(dalloc(c, &c->hB, (size_t)B * H));
+    TRY(dalloc(c, &c->qkv_raw, (size_t)m->p_qkv.slots * B * m->p_qkv.N));
+    TRY(dalloc(c, &c->attn_out, (size_t)B * m->Nq * D));
+    TRY(dalloc(c, &c->o_raw, (size_t)m->p_o.slots * B * H));
+    TRY(dalloc(c, &c->gu_raw, (size_t)m->p_gateup.slots * B * m->p_gateup.N));
+    TRY(dalloc(c, &c->down_raw, (size_t)m->p_down.slots * B * H));
+    TRY(dalloc(c, &c->logits, (size_t)B * m->V));
+    TRY(dalloc(c, &c->attn_part, (size_t)B * m->Nkv * smax * m->G * (D + 2)));
+    TRY(dalloc(c, &c->attn_ticket, (size_t)B * m->Nkv));
+    TRY(dalloc(c, &c->lm_ticket, (size_t)(B + 3) / 4 + 1));
+    TRY(dalloc(c, &c->blk_best, (size_t)B * m->num_sms));
+    const int chunks = (m->V + kTopkChunk - 1) / kTopkChunk;
+    TRY(dalloc(c, &c->topk_stage, (size_t)B * chunks * 64));
+    TRY(dalloc(c, &c->best_ids, B));
+    TRY(dalloc(c, &c->best_scores, B));
+    TRY(dalloc(c, &c->topk_ids, (size_t)B * 64));
+    TRY(dalloc(c, &c->topk_scores, (size_t)B * 64));
+    CK(cudaMallocHost(&c->h_tokens, sizeof(uint32_t) * B));
+    CK(cudaMallocHost(&c->h_ctl, sizeof(StepCtl)));
+    CK(cudaMallocHost(&c->h_ids, sizeof(uint32_t) * B * 64));
+    CK(cudaMallocHost(&c->h_scores, sizeof(float) * B * 64));
+    CK(cudaEventCreate(&c->ev0));
+    CK(cudaEventCreate(&c->ev1));
+    CK(cudaDeviceSynchronize());
+    return OXG4_OK;
+}
+
+extern "C" void oxg4_cache_destroy(oxg4_cache* c) {
+    if (!c) return;
+    cudaSetDevice(c->m->device);
+    cudaStreamSynchronize(c->m->stream);
+    for (auto& g : c->graphs) {
+        if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
+        if (g.second.graph) cudaGraphDestroy(g.second.graph);
+    }
+    for (void* p : c->owned) cudaFree(p);
+    if (c->h_tokens) cudaFreeHost(c->h_tokens);
+    if (c->h_ctl) cudaFreeHost(c->h_ctl);
+    if (c->h_ids) cudaFreeHost(c->h_ids);
+    if (c->h_scores) cudaFreeHost(c->h_scores);
+    if (c->ev0) cudaEventDestroy(c->ev0);
+    if (c->ev1) cudaEventDestroy(c->ev1);
+    delete c;
+}
+
+extern "C" int32_t oxg4_cache_create(oxg4_model* m, int32_t batch, const int32_t* max_seq, int32_t page_tokens,
+                                     int32_t kv_dtype, oxg4_cache** out) {
+    if (!m || !max_seq || !out) return fail(OXG4_INVALID_ARGUMENT, "null argument");
+    *out = nullptr;
+    if (!m->finalized) return fail(OXG4_INVALID_ARGUMENT, "model is not finalized");
+    if (batch <= 0) return fail(OXG4_INVALID_SHAPE, "batch must be positive");
+    for (int b = 0; b < batch; ++b)
+        if (max_seq[b] <= 0) return fail(OXG4_INVALID_SHAPE, "zero max_sequence");     // cache.rs:36-38
+    if (page_tokens <= 0) return fail(OXG4_INVALID_SHAPE, "page_tokens must be positive");
+    if (kv_dtype != OXG4_F32 && kv_dtype != OXG4_BF16) return fail(OXG4_INVALID_ARGUMENT, "kv_dtype must be OXG4_F32 or OXG4_BF16");
+    TRY(bind_device(m));
+    oxg4_cache* c = new oxg4_cache();
+    c->m = m;
+    c->B = batch;
+    c->PT = page_tokens;
+    c->kv_dtype = kv_dtype;
+    c->max_seq.assign(max_seq, max_seq + batch);
+    c->pos_host.assign(batch, 0);
+    int32_t s = cache_build(c);
+    if (s != OXG4_OK) {
+        std::string keep = g_err;
+        oxg4_cache_destroy(c);
+        g_err = keep;
+        return s;
+    }
+    *out = c;
+    return OXG4_OK;
+}
+
+extern "C" int32_t oxg4_cache_info_get(const oxg4_cache* c, oxg4_cache_info* o) {
+    if (!c || !o) return fail(OXG4_INVALID_ARGUMENT, "null argument");
+    o->batch = c->B;
+    o->layer_count = c->m->cfg.num_hidden_layers;
+    o->physical_cache_count = c->m->cfg.num_hidden_layers;
+    o->shared_layer_count = 0;
+    o->page_tokens = c->PT;
+    o->kv_dtype = c->kv_dtype;
+    o->kv_bytes = c->kv_bytes;
+    return OXG4_OK;
+}
+
+extern "C" int32_t oxg4_cache_position(const oxg4_cache* c, int32_t b) {
+    if (!c || b < 0 || b >= c->B) return -1;
+    return c->pos_host[b];
+}
+
+extern "C" int32_t oxg4_cache_reset(oxg4_cache* c) {
+    if (!c) return fail(OXG4_INVALID_ARGUMENT, "null cache");
+    TRY(bind_device(c->m));
+    cudaStream_t st = c->m->stream;
+    CK(cudaMemsetAsync(c->pos, 0, sizeof(int32_t) * c->B, st));
+    CK(cudaMemsetAsync(c->seen, 0, (size_t)c->B * c->m->V, st));
+    CK(cudaStreamSynchronize(st));
+    std::fill(c->pos_host.begin(), c->pos_host.end(), 0);
+    return OXG4_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// one decode step
+// ------------------------------------------------------------------------------------------------
+struct Launcher {
+    oxg4_model* m;
+    int kernels = 0;
+    int32_t status = OXG4_OK;
+
+    template <typename... KArgs, typename... Args>
+    void go(const char* kind, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args... args) {
+        if (status != OXG4_OK) return;
+        cudaEvent_t e0 = nullptr, e1 = nullptr;
+        if (m->profiling) {
+            cudaEventCreate(&e0);
+            cudaEventCreate(&e1);
+            cudaEventRecord(e0, m->stream);
+        }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = block;
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = m->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = (m->use_pdl && !m->profiling) ? 1 : 0;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, args...);
+        if (e != cudaSuccess) {
+            status = fail(OXG4_CUDA, "Gemma 4 CUDA error: launch of %s failed: %s", kind, cudaGetErrorString(e));
+            return;
+        }
+        if (m->profiling) {
+            cudaEventRecord(e1, m->stream);
+            m->prof_events.push_back({kind, {e0, e1}});
+        }
+        ++kernels;
+    }
+};
+
+template <typename WT>
+static void (*pick_gemv(int nb, int pro, int epi))(const GemvArgs) {
+#define PICK(NB)                                                                              \
+    if (pro == PRO_NORM && epi == EPI_PARTIAL) return gemv_kernel<WT, NB, PRO_NORM, EPI_PARTIAL>;   \
+    if (pro == PRO_PLAIN && epi == EPI_PARTIAL) return gemv_kernel<WT, NB, PRO_PLAIN, EPI_PARTIAL>; \
+    if (pro == PRO_NORM && epi == EPI_GATEUP) return gemv_kernel<WT, NB, PRO_NORM, EPI_GATEUP>;     \
+    if (pro == PRO_GEGLU && epi == EPI_PARTIAL) return gemv_kernel<WT, NB, PRO_GEGLU, EPI_PARTIAL>; \
+    if (pro == PRO_NORM && epi == EPI_LOGITS) return gemv_kernel<WT, NB, PRO_NORM, EPI_LOGITS>;
+    if (nb == 1) { PICK(1) }
+    if (nb == 2) { PICK(2) }
+    if (nb == 4) { PICK(4) }
+#undef PICK
+    return nullptr;
+}
+
+static void launch_gemv(Launcher& ln, const char* kind, oxg4_cache* c, GemvArgs a, const GemvPlan& p, int pro, int epi) {
+    oxg4_model* m = c->m;
+    const int B = c->B;
+    const int nb = B >= 3 ? 4 : B;
+    a.N = p.N;
+    a.K = p.K;
+    a.cpr = p.cpr;
+    a.lr = p.lr;
+    a.B = B;
+    a.eps = m->cfg.rms_norm_eps;
+    const size_t xes = m->es == 2 ? 2 : 4;
+    size_t smem = (size_t)nb * p.K * xes + (size_t)nb * 32 * 4;
+    size_t extra = pro == PRO_NORM ? (size_t)nb * p.K * 4 : 0;
+    extra = std::max(extra, (size_t)nb * kGemvWarps * sizeof(Cand));
+    smem += extra;
+    if (smem > 227 * 1024) {
+        ln.status = fail(OXG4_UNSUPPORTED, "projection %s needs %zu bytes of shared memory", kind, smem);
+        return;
+    }
+    auto fn = m->es == 2 ? pick_gemv<uint16_t>(nb, pro, epi) : pick_gemv<float>(nb, pro, epi);
+    dim3 grid(p.grid, (B + nb - 1) / nb, 1);
+    ln.go(kind, fn, grid, dim3(kGemvThreads), smem, a);
+}
+
+template <typename KT>
+static void (*pick_attn(int D, int G))(const AttnArgs) {
+#define PA(DD)                                                     \
+    if (D == DD) {                                                 \
+        if (G == 1) return attn_decode_kernel<KT, DD, 1>;          \
+        if (G == 2) return attn_decode_kernel<KT, DD, 2>;          \
+        if (G == 4) return attn_decode_kernel<KT, DD, 4>;          \
+        if (G == 8) return attn_decode_kernel<KT, DD, 8>;          \
+    }
+    PA(64) PA(128) PA(256)
+#undef PA
+    return nullptr;
+}
+
+static PartialSpec spec_of(const float* buf, const GemvPlan& p) {
+    PartialSpec s;
+    s.buf = buf;
+    s.n = p.N;
+    s.cpr = p.cpr;
+    s.lr = p.lr;
+    return s;
+}
+
+// Launches every kernel of one step on the model's stream (eagerly or under stream capture).
+static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* n_kernels) {
+    oxg4_model* m = c->m;
+    Launcher ln{m};
+    const int B = c->B, L = m->cfg.num_hidden_layers, H = m->H, D = m->D;
+    ln.go("step_begin", step_begin_kernel, dim3(1), dim3(128), 0, B, m->V,
+          (const uint32_t*)c->tokens, c->seen, (const StepCtl*)c->ctl);
+    for (int l = 0; l < L; ++l) {
+        const LayerPlan& p = m->layers[l];
+        {   // input norm + QKV projection (decode.rs:61-98); also closes the previous layer
+            GemvArgs a{};
+            a.W0 = p.wqkv;
+            a.h_in = c->hA;
+            a.h_out = c->hB;
+            a.w_norm = p.input_ln;
+            a.scalar = 1.0f;
+            if (l == 0) {
+                a.embed = m->embed;
+                a.tokens = c->tokens;
+                a.embed_scale = sqrtf((float)H);
+            } else {
+                a.raw = spec_of(c->down_raw, m->p_down);
+                a.w_post = m->layers[l - 1].post_ff_ln;
+                a.scalar = m->layers[l - 1].layer_scalar;
+            }
+            a.out = c->qkv_raw;
+            launch_gemv(ln, "qkv", c, a, m->p_qkv, PRO_NORM, EPI_PARTIAL);
+        }
+        {   // q/k norm + RoPE + v norm + KV append + attention (decode.rs:99-157)
+            AttnArgs a{};
+            a.qkv = spec_of(c->qkv_raw, m->p_qkv);
+            a.B = B;
+            a.Nq = m->Nq;
+            a.Nkv = m->Nkv;
+            a.q_norm = p.q_norm;
+            a.k_norm = p.k_norm;
+            a.inv_freq = p.inv_freq;
+            a.rotary_half = p.rotary_dim / 2;
+            a.eps = m->cfg.rms_norm_eps;
+            a.pos = c->pos;
+            a.tokens = c->tokens;
+            a.kpool = c->kpool[l];
+            a.vpool = c->vpool[l];
+            a.page_table = p.sliding ? c->pt_slide : c->pt_full;
+            a.pages_per_seq = p.sliding ? c->pps_slide : c->pps_full;
+            a.page_tokens = c->PT;
+            a.cap = p.sliding ? c->cap_slide : c->cap_full;
+            a.n_splits = p.sliding ? c->splits_slide : c->splits_full;
+            a.min_split = c->min_split;
+            a.part = c->attn_part;
+            a.ticket = c->attn_ticket;
+            a.out = c->attn_out;
+            auto fn = c->kv_dtype == OXG4_BF16 ? pick_attn<uint16_t>(D, m->G) : pick_attn<float>(D, m->G);
+            const size_t smem = sizeof(float) * (size_t)(m->G * D + 2 * D + 2 * kAttnWarps * m->G + kAttnWarps * m->G * D);
+            ln.go("attn", fn, dim3(a.n_splits, m->Nkv, B), dim3(kAttnThreads), smem, a);
+        }
+        {   // O projection (decode.rs:159)
+            GemvArgs a{};
+            a.W0 = p.wo;
+            a.in = c->attn_out;
+            a.out = c->o_raw;
+            launch_gemv(ln, "o", c, a, m->p_o, PRO_PLAIN, EPI_PARTIAL);
+        }
+        {   // post-attention norm + residual, pre-FF norm, gate and up projections (decode.rs:161-171, 14-16)
+            GemvArgs a{};
+            a.W0 = p.wgate;
+            a.W1 = p.wup;
+            a.h_in = c->hB;
+            a.h_out = c->hA;
+            a.raw = spec_of(c->o_raw, m->p_o);
+            a.w_post = p.post_attn_ln;
+            a.scalar = 1.0f;
+            a.w_norm = p.pre_ff_ln;
+            a.out = c->gu_raw;
+            launch_gemv(ln, "gateup", c, a, m->p_gateup, PRO_NORM, EPI_GATEUP);
+        }
+        {   // GeGLU + down projection (decode.rs:17-18)
+            GemvArgs a{};
+            a.W0 = p.wdown;
+            a.raw = spec_of(c->gu_raw, m->p_gateup);
+            a.out = c->down_raw;
+            launch_gemv(ln, "down", c, a, m->p_down, PRO_GEGLU, EPI_PARTIAL);
+        }
+    }
+    if (kind != STEP_PREFILL) {
+        // post-FF norm + residual + layer_scalar of the last layer, final norm, tied LM head with
+        // fused arg-max (decode.rs:495-508, kernel_module.rs:1988-2075)
+        GemvArgs a{};
+        a.W0 = (const char*)m->embed + (size_t)m->v0 * H * m->es;
+        a.h_in = c->hA;
+        a.h_out = c->hB;
+        a.raw = spec_of(c->down_raw, m->p_down);
+        a.w_post = m->layers[L - 1].post_ff_ln;
+        a.scalar = m->layers[L - 1].layer_scalar;
+        a.w_norm = m->final_norm;
+        const bool want_logits = (kind == STEP_LOGITS) || top_k > 1;
+        a.out = want_logits ? c->logits : nullptr;
+        a.seen = c->seen;
+        a.penalty = penalty;
+        a.row_offset = m->v0;
+        a.n_total = m->V;
+        a.blk_best = c->blk_best;
+        a.ticket = c->lm_ticket;
+        a.best_ids = c->best_ids;
+        a.best_scores = c->best_scores;
+        launch_gemv(ln, "lmhead", c, a, m->p_lm, PRO_NORM, EPI_LOGITS);
+        if (kind == STEP_TOPK && top_k > 1) {
+            const int chunks = (m->V + kTopkChunk - 1) / kTopkChunk;
+            ln.go("topk1", topk_stage1_kernel, dim3(chunks, B), dim3(kTopkThreads), 0, (const float*)c->logits,
+                  m->V, (const uint8_t*)c->seen, penalty, top_k, c->topk_stage);
+            ln.go("topk2", topk_stage2_kernel, dim3(1, B), dim3(kTopkThreads), (size_t)chunks * top_k * 8,
+                  (const Cand*)c->topk_stage, chunks * top_k, top_k, c->topk_ids, c->topk_scores);
+        }
+    }
+    ln.go("step_end", step_end_kernel, dim3(1), dim3(128), 0, B, c->tokens, c->pos,
+          (const uint32_t*)c->best_ids, c->history, c->ctl);
+    if (n_kernels) *n_kernels = ln.kernels;
+    return ln.status;
+}
+
+static bool graphs_disabled() { return getenv("GEMMA4_DISABLE_CUDA_GRAPH") != nullptr; }
+
+// Replays (capturing on first use) the step graph keyed on (kind, top_k, penalty bits), as the
+// reference keys its captured graph (decode.rs:689-699). The graph lives in the cache table.
+static int32_t launch_step(oxg4_cache* c, int kind, int top_k, float penalty) {
+    oxg4_model* m = c->m;
+    if (graphs_disabled() || m->profiling) {
+        int n = 0;
+        TRY(run_step(c, kind, top_k, penalty, &n));
+        m->launches += n;
+        return OXG4_OK;
+    }
+    uint32_t pbits;
+    memcpy(&pbits, &penalty, 4);
+    char key[64];
+    snprintf(key, sizeof key, "%d:%d:%08x", kind, top_k, pbits);
+    auto it = c->graphs.find(key);
+    if (it == c->graphs.end()) {
+        GraphEntry g;
+        CK(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
+        int n = 0;
+        int32_t s = run_step(c, kind, top_k, penalty, &n);
+        cudaError_t e = cudaStreamEndCapture(m->stream, &g.graph);   // always end the capture (cuda_graph.rs:84-97)
+        if (s != OXG4_OK) {
+            if (g.graph) cudaGraphDestroy(g.graph);
+            return s;
+        }
+        CK(e);
+        CK(cudaGraphInstantiate(&g.exec, g.graph, 0));
+        g.kernels = n;
+        if (getenv("GEMMA4_PROFILE")) fprintf(stderr, "Gemma4 CUDA Graph: captured step kind %d (%d kernels)\n", kind, n);
+        it = c->graphs.emplace(key, g).first;
+    }
+    CK(cudaGraphLaunch(it->second.exec, m->stream));
+    m->launches += it->second.kernels;
+    return OXG4_OK;
+}
+
+static int32_t check_tokens(oxg4_cache* c, const uint32_t* tokens, bool allow_inactive) {
+    for (int b = 0; b < c->B; ++b) {
+        if (tokens[b] == kInactiveToken) {
+            if (!allow_inactive) return fail(OXG4_INVALID_ARGUMENT, "token id exceeds CUDA decode vocabulary");
+            continue;
+        }
+        if (tokens[b] >= (uint32_t)c->m->V)
+            return fail(OXG4_INVALID_ARGUMENT, "token id exceeds CUDA decode vocabulary");     // decode.rs:675-679
+        if (c->pos_host[b] >= c->max_seq[b])
+            return fail(OXG4_INVALID_SHAPE, "sequence %d is longer than the cache table's max_sequence", b);
+    }
+    return OXG4_OK;
+}
+
+static int32_t stage_inputs(oxg4_cache* c, const uint32_t* tokens, int mark_seen, int feed_back) {
+    cudaStream_t st = c->m->stream;
+    memcpy(c->h_tokens, tokens, sizeof(uint32_t) * c->B);
+    c->h_ctl->mark_seen = mark_seen;
+    c->h_ctl->feed_back = feed_back;
+    c->h_ctl->step = 0;
+    c->h_ctl->history_cap = c->history_cap;
+    CK(cudaMemcpyAsync(c->tokens, c->h_tokens, sizeof(uint32_t) * c->B, cudaMemcpyHostToDevice, st));
+    CK(cudaMemcpyAsync(c->ctl, c->h_ctl, sizeof(StepCtl), cudaMemcpyHostToDevice, st));
+    return OXG4_OK;
+}
+
+static void advance_host(oxg4_cache* c, const uint32_t* tokens, int steps = 1) {
+    for (int b = 0; b < c->B; ++b)
+        if (tokens[b] != kInactiveToken) c->pos_host[b] += steps;
+}
+
+static void softcap(float* v, size_t n, float cap) {     // mod.rs:573-579
+    if (cap > 0.0f)
+        for (size_t i = 0; i < n; ++i) v[i] = tanhf(v[i] / cap) * cap;
+}
+
+extern "C" int32_t oxg4_prefill_token(oxg4_model* m, oxg4_cache* c, const uint32_t* tokens) {
+    if (!m || !c || !tokens || c->m != m) return fail(OXG4_INVALID_ARGUMENT, "null or mismatched handle");
+    TRY(bind_device(m));
+    TRY(check_tokens(c, tokens, true));
+    TRY(stage_inputs(c, tokens, 0, 0));
+    TRY(launch_step(c, STEP_PREFILL, 0, 1.0f));
+    CK(cudaStreamSynchronize(m->stream));
+    advance_host(c, tokens);
+    return OXG4_OK;
+}
+
+extern "C" int32_t oxg4_decode_logits(oxg4_model* m, oxg4_cache* c, const uint32_t* tokens, float* logits) {
+    if (!m || !c || !tokens || !logits || c->m != m) return fail(OXG4_INVALID_ARGUMENT, "null or mismatched handle");
+    TRY(bind_device(m));
+    TRY(check_tokens(c, tokens, true));
+    TRY(stage_inputs(c, tokens, 0, 0));
+    TRY(launch_step(c, STEP_LOGITS, 1, 1.0f));
+    CK(cudaMemcpyAsync(logits, c->logits, sizeof(float) * (size_t)c->B * m->V, cudaMemcpyDeviceToHost, m->stream));
+    CK(cudaStreamSynchronize(m->stream));
+    softcap(logits, (size_t)c->B * m->V, m->cfg.final_logit_softcapping);
+    advance_host(c, tokens);
+    return OXG4_OK;
+}
+
+extern "C" int32_t oxg4_decode_topk(oxg4_model* m, oxg4_cache* c, const uint32_t* tokens, int32_t top_k,
+                                    float penalty, int32_t mark_seen, uint32_t* ids, float* scores) {
+    if (!m || !c || !tokens || !ids || !scores || c->m != m) return fail(OXG4_INVALID_ARGUMENT, "null or mismatched handle");
+    TRY(bind_device(m));
+    TRY(check_tokens(c, tokens, true));
+    top_k = std::min(std::max(top_k, 1), 64);                 // decode.rs:680
+    top_k = std::min(top_k, m->V);
+    TRY(stage_inputs(c, tokens, mark_seen ? 1 : 0, 0));
+    TRY(launch_step(c, STEP_TOPK, top_k, penalty));
+    const uint32_t* src_i = top_k == 1 ? c->best_ids : c->topk_ids;
+    const float* src_s = top_k == 1 ? c->best_scores : c->topk_scores;
+    CK(cudaMemcpyAsync(c->h_ids, src_i, sizeof(uint32_t) * c->B * top_k, cudaMemcpyDeviceToHost, m->stream));
+    CK(cudaMemcpyAsync(c->h_scores, src_s, sizeof(float) * c->B * top_k, cudaMemcpyDeviceToHost, m->stream));
+    CK(cudaStreamSynchronize(m->stream));
+    memcpy(ids, c->h_ids, sizeof(uint32_t) * c->B * top_k);
+    memcpy(scores, c->h_scores, sizeof(float) * c->B * top_k);
+    softcap(scores, (size_t)c->B * top_k, m->cfg.final_logit_softcapping);
+    advance_host(c, tokens);
+    return OXG4_OK;
+}
+
+extern "C" int32_t oxg4_decode_greedy(oxg4_model* m, oxg4_cache* c, const uint32_t* first_tokens, int32_t steps,
+                                      uint32_t* out_ids, float* ms_per_step) {
+    if (!m || !c || !first_tokens || !out_ids || c->m != m) return fail(OXG4_INVALID_ARGUMENT, "null or mismatched handle");
+    if (steps <= 0) return fail(OXG4_INVALID_ARGUMENT, "steps must be positive");
+    TRY(bind_device(m));
+    TRY(check_tokens(c, first_tokens, true));
+    for (int b = 0; b < c->B; ++b)
+        if (first_tokens[b] != kInactiveToken && c->pos_host[b] + steps > c->max_seq[b])
+            return fail(OXG4_INVALID_SHAPE, "sequence %d would outgrow the cache table's max_sequence", b);
+    if (c->history_cap < steps) {
+        uint32_t* h = nullptr;
+        TRY(dalloc(c, &h, (size_t)steps * c->B));
+        c->history = h;
+        c->history_cap = steps;
+        // the history pointer is a kernel argument: graphs captured with the old one are stale
+        for (auto& g : c->graphs) {
+            if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
+            if (g.second.graph) cudaGraphDestroy(g.second.graph);
+        }
+        c->graphs.clear();
+    }
+    TRY(stage_inputs(c, first_tokens, 0, 1));
+    // capture (if needed) before the timed region
+    if (!graphs_disabled()) {
+        uint32_t pbits;
+        float one = 1.0f;
+        memcpy(&pbits, &one, 4);
+        char key[64];
+        snprintf(key, sizeof key, "%d:%d:%08x", (int)STEP_TOPK, 1, pbits);
+        if (c->graphs.find(key) == c->graphs.end()) {
+            // one warm step outside the timed loop would change the state; capture does not execute
+            GraphEntry g;
+            CK(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
+            int n = 0;
+            int32_t s = run_step(c, STEP_TOPK, 1, 1.0f, &n);
+            cudaError_t e = cudaStreamEndCapture(m->stream, &g.graph);
+            if (s != OXG4_OK) { if (g.graph) cudaGraphDestroy(g.graph); return s; }
+            CK(e);
+            CK(cudaGraphInstantiate(&g.exec, g.graph, 0));
+            g.kernels = n;
+            c->graphs.emplace(key, g);
+        }
+    }
+    CK(cudaEventRecord(c->ev0, m->stream));
+    for (int s = 0; s < steps; ++s) TRY(launch_step(c, STEP_TOPK, 1, 1.0f));
+    CK(cudaEventRecord(c->ev1, m->stream));
+    CK(cudaMemcpyAsync(out_ids, c->history, sizeof(uint32_t) * (size_t)steps * c->B, cudaMemcpyDeviceToHost, m->stream));
+    CK(cudaStreamSynchronize(m->stream));
+    float ms = 0;
+    CK(cudaEventElapsedTime(&ms, c->ev0, c->ev1));
+    if (ms_per_step) *ms_per_step = ms / steps;
+    advance_host(c, first_tokens, steps);
+    return OXG4_OK;
+}
+
+extern "C" int32_t oxg4_profile_step(oxg4_model* m, oxg4_cache* c, const uint32_t* tokens) {
+    if (!m || !c || !tokens || c->m != m) return fail(OXG4_INVALID_ARGUMENT, "null or mismatched handle");
+    TRY(bind_device(m));
+    TRY(check_tokens(c, tokens, true));
+    TRY(stage_inputs(c, tokens, 0, 0));
+    m->profiling = true;
+    m->prof_events.clear();
+    int32_t s = launch_step(c, STEP_TOPK, 1, 1.0f);
+    m->profiling = false;
+    if (s != OXG4_OK) return s;
+    CK(cudaStreamSynchronize(m->stream));
+    m->profile.clear();
+    for (auto& pe : m->prof_events) {
+        float ms = 0;
+        cudaEventElapsedTime(&ms, pe.second.first, pe.second.second);
+        ProfileSlot& ps = m->profile[pe.first];
+        ps.ms += ms;
+        ps.count += 1;
+        cudaEventDestroy(pe.second.first);
+        cudaEventDestroy(pe.second.second);
+    }
+    m->prof_events.clear();
+    advance_host(c, tokens);
+    return OXG4_OK;
+}
+
+extern "C" float oxg4_profile_ms(const oxg4_model* m, const char* kind) {
+    if (!m || !kind) return -1.0f;
+    auto it = m->profile.find(kind);
+    if (it == m->profile.end() || it->second.count == 0) return -1.0f;
+    return (float)(it->second.ms / it->second.count);
+}
+
+extern "C" int32_t oxg4_prefill(oxg4_model* m, oxg4_cache* c, const uint32_t* tokens, const int32_t* lens,
+                                float* last_logits) {
+    if (!m || !c || !tokens || !lens || c->m != m) return fail(OXG4_INVALID_ARGUMENT, "null or mismatched handle");
+    const int B = c->B;
+    int maxlen = 0;
+    std::vector<int64_t> off(B + 1, 0);
+    for (int b = 0; b < B; ++b) {
+        if (lens[b] <= 0) return fail(OXG4_INVALID_ARGUMENT, "batched prefill requires at least one token per sequence");
+        if (c->pos_host[b] != 0) return fail(OXG4_INVALID_ARGUMENT, "batched prefill requires an empty cache table");   // decode.rs:392-396
+        if (lens[b] > c->max_seq[b]) return fail(OXG4_INVALID_SHAPE, "prompt does not fit the cache table");
+        off[b + 1] = off[b] + lens[b];
+        maxlen = std::max(maxlen, lens[b]);
+    }
+    // The prompt is ingested with the decode step, one token per sequence and step, as the
+    // reference's prefill_token does (decode.rs:464-472); shorter prompts sit out once exhausted.
+    std::vector<uint32_t> step_tokens(B);
+    for (int t = 0; t + 1 < maxlen; ++t) {
+        for (int b = 0; b < B; ++b) step_tokens[b] = (t + 1 < lens[b]) ? tokens[off[b] + t] : kInactiveToken;
+        TRY(oxg4_prefill_token(m, c, step_tokens.data()));
+    }
+    for (int b = 0; b < B; ++b) step_tokens[b] = tokens[off[b] + lens[b] - 1];
+    if (last_logits) return oxg4_decode_logits(m, c, step_tokens.data(), last_logits);
+    return oxg4_prefill_token(m, c, step_tokens.data());
+}
+
+// ------------------------------------------------------------------------------------------------
+// host mirror of the generation loop (models/gemma4/generation.rs, sampling.rs)
+// ------------------------------------------------------------------------------------------------
+static inline int32_t total_order_key(float f) {      // f32::total_cmp
+    int32_t b;
+    memcpy(&b, &f, 4);
+    b ^= (int32_t)(((uint32_t)(b >> 31)) >> 1);
+    return b;
+}
+
+struct Scored {
+    int64_t id;
+    float v;
+};
+
+static int64_t draw(std::vector<Scored>& cand, float top_p, uint64_t* random) {
+    const float maximum = cand[0].v;
+    float total = 0.0f;
+    for (auto& s : cand) { s.v = expf(s.v - maximum); total += s.v; }
+    if (total == 0.0f || !std::isfinite(total)) return -1;
+    for (auto& s : cand) s.v /= total;
+    if (top_p < 1.0f) {
+        float cumulative = 0.0f;
+        size_t keep = 0;
+        for (auto& s : cand) {
+            cumulative += s.v;
+            ++keep;
+            if (cumulative >= top_p) break;
+        }
+        cand.resize(std::max<size_t>(keep, 1));
+        total = 0.0f;
+        for (auto& s : cand) total += s.v;
+    } else {
+        total = 1.0f;
+    }
+    uint64_t r = *random;
+    if (r == 0) r = 0x4d595df4d0f33173ull;
+    r ^= r << 13;
+    r ^= r >> 7;
+    r ^= r << 17;
+    *random = r;
+    const float unit = (float)((uint32_t)(r >> 40)) / 16777216.0f;
+    float threshold = unit * total;
+    for (auto& s : cand) {
+        if (threshold <= s.v) return s.id;
+        threshold -= s.v;
+    }
+    return cand.back().id;
+}
+
+extern "C" int64_t oxg4_sample_token(const float* logits, int64_t n, float temperature, int64_t top_k, float top_p,
+                                     uint64_t* random) {
+    if (!logits || !random || n <= 0 || !(temperature > 0.0f) || !(top_p >= 0.0f && top_p <= 1.0f)) return -1;
+    std::vector<Scored> cand;
+    cand.reserve((size_t)n);
+    for (int64_t i = 0; i < n; ++i)
+        if (std::isfinite(logits[i])) cand.push_back({i, logits[i] / temperature});
+    if (cand.empty()) return -1;
+    auto desc = [](const Scored& a, const Scored& b) { return total_order_key(a.v) > total_order_key(b.v); };
+    const size_t keep = (size_t)std::min<int64_t>(std::max<int64_t>(top_k, 1), (int64_t)cand.size());
+    if (keep < cand.size()) {
+        std::partial_sort(cand.begin(), cand.begin() + keep, cand.end(), desc);
+        cand.resize(keep);
+    } else {
+        std::sort(cand.begin(), cand.end(), desc);
+    }
+    return draw(cand, top_p, random);
+}
+
+extern "C" int64_t oxg4_sample_topk_candidates(const uint32_t* ids, const float* scores, int64_t n, float temperature,
+                                               float top_p, uint64_t* random) {
+    if (!ids || !scores || !random || n <= 0 || !(temperature > 0.0f) || !(top_p >= 0.0f && top_p <= 1.0f)) return -1;
+    std::vector<Scored> cand;
+    for (int64_t i = 0; i < n; ++i)
+        if (std::isfinite(scores[i])) cand.push_back({(int64_t)ids[i], scores[i] / temperature});
+    if (cand.empty()) return -1;
+    std::stable_sort(cand.begin(), cand.end(),
+                     [](const Scored& a, const Scored& b) { return total_order_key(a.v) > total_order_key(b.v); });
+    return draw(cand, top_p, random);
+}
+
+extern "C" int32_t oxg4_generate(oxg4_model* m, const uint32_t* prompt, int64_t n_prompt,
+                                 const oxg4_generation_config* g, int32_t kv_dtype, oxg4_token_callback on_token,
+                                 void* user, uint32_t* out_ids, int64_t* n_out) {
+    if (!m || !g || !out_ids || !n_out) return fail(OXG4_INVALID_ARGUMENT, "null argument");
+    // GenerationConfig::validate (generation.rs:6-33)
+    if (!std::isfinite(g->temperature) || g->temperature <= 0.0f)
+        return fail(OXG4_INVALID_ARGUMENT, "generation temperature must be finite and greater than zero");
+    if (!std::isfinite(g->top_p) || g->top_p < 0.0f || g->top_p > 1.0f)
+        return fail(OXG4_INVALID_ARGUMENT, "generation top_p must be finite and between zero and one");
+    if (g->top_k == 0) return fail(OXG4_INVALID_ARGUMENT, "generation top_k must be greater than zero");
+    if (!std::isfinite(g->repetition_penalty) || g->repetition_penalty < 1.0f)
+        return fail(OXG4_INVALID_ARGUMENT, "generation repetition_penalty must be finite and at least one");
+    for (int64_t i = 0; i < g->n_stop_sequences; ++i)
+        if (g->stop_sequence_lens[i] == 0)
+            return fail(OXG4_INVALID_ARGUMENT, "generation stop-token sequences cannot be empty");
+    if (!prompt || n_prompt <= 0)
+        return fail(OXG4_INVALID_ARGUMENT, "Gemma 4 generation requires at least one input token");
+    if (g->max_new_tokens < 0 || n_prompt + g->max_new_tokens > 0x7fffffff)
+        return fail(OXG4_INVALID_ARGUMENT, "Gemma 4 sequence length overflow");
+    const int32_t max_seq = (int32_t)(n_prompt + g->max_new_tokens);
+    oxg4_cache* cache = nullptr;
+    TRY(oxg4_cache_create(m, 1, &max_seq, 256, kv_dtype, &cache));
+    std::vector<float> logits((size_t)m->V);
+    const int32_t len = (int32_t)n_prompt;
+    int32_t s = oxg4_prefill(m, cache, prompt, &len, logits.data());
+    if (s != OXG4_OK) { oxg4_cache_destroy(cache); return s; }
+    uint64_t random = g->seed;
+    std::vector<uint32_t> generated;
+    uint32_t ids[64];
+    float scores[64];
+    int n_cand = 0;
+    bool have_cand = false;
+    for (int64_t it = 0; it < g->max_new_tokens; ++it) {
+        if (!have_cand && g->repetition_penalty > 1.0f) {
+            // apply_repetition_penalty over the tokens generated so far (generation.rs:143-157)
+            std::vector<uint32_t> uniq(generated);
+            std::sort(uniq.begin(), uniq.end());
+            uniq.erase(std::unique(uniq.begin(), uniq.end()), uniq.end());
+            for (uint32_t t : uniq)
+                if (t < (uint32_t)m->V) logits[t] = logits[t] >= 0.0f ? logits[t] / g->repetition_penalty : logits[t] * g->repetition_penalty;
+        }
+        const int64_t next = have_cand
+                                 ? oxg4_sample_topk_candidates(ids, scores, n_cand, g->temperature, g->top_p, &random)
+                                 : oxg4_sample_token(logits.data(), m->V, g->temperature, g->top_k, g->top_p, &random);
+        if (next < 0) { oxg4_cache_destroy(cache); return fail(OXG4_INVALID_ARGUMENT, "invalid sampling input"); }
+        generated.push_back((uint32_t)next);
+        if (on_token && on_token((uint32_t)next, user) != 0) {
+            oxg4_cache_destroy(cache);
+            return fail(OXG4_INVALID_ARGUMENT, "token callback returned an error");
+        }
+        bool stop = false;
+        for (int64_t e = 0; e < g->n_eos; ++e) stop |= g->eos_token_ids[e] == (uint32_t)next;
+        int64_t so = 0;
+        for (int64_t q = 0; q < g->n_stop_sequences && !stop; ++q) {
+            const int64_t sl = g->stop_sequence_lens[q];
+            if ((int64_t)generated.size() >= sl &&
+                std::equal(g->stop_sequences + so, g->stop_sequences + so + sl, generated.end() - sl))
+                stop = true;
+            so += sl;
+        }
+        if (stop) break;
+        const uint32_t tok = (uint32_t)next;
+        n_cand = (int)std::min<int64_t>(std::max<int64_t>(g->top_k, 1), 64);
+        n_cand = std::min(n_cand, m->V);
+        s = oxg4_decode_topk(m, cache, &tok, n_cand, g->repetition_penalty, 1, ids, scores);
+        if (s != OXG4_OK) { oxg4_cache_destroy(cache); return s; }
+        have_cand = true;
+    }
+    oxg4_cache_destroy(cache);
+    memcpy(out_ids, prompt, sizeof(uint32_t) * (size_t)n_prompt);
+    memcpy(out_ids + n_prompt, generated.data(), sizeof(uint32_t) * generated.size());
+    *n_out = n_prompt + (int64_t)generated.size();
+    return OXG4_OK;
+}

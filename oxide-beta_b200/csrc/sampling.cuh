@@ -1,0 +1,125 @@
+// Step bookkeeping and top-k selection kernels.
+//
+// step_begin / step_end replace the reference's one-thread decode_state_update / mark_seen
+// launches (crates/oxide-torch-cuda/src/kernel_module.rs:1287-1317,1981-1986): the token ids and
+// positions of every sequence live on the device so that a captured step can be replayed for any
+// position. topk_stage1 / topk_stage2 produce the same list as the reference's two-stage top-k
+// (kernel_module.rs:1988-2075): descending score, lowest index first among equal scores,
+// repetition penalty applied to seen tokens, NaN never selected, unused slots (-inf, 0).
+#pragma once
+#include "common.cuh"
+
+namespace oxg4 {
+
+struct StepCtl {              // device-resident control words, written by the host before a step
+    int32_t mark_seen;        // 1: seen[b][token[b]] = 1 at step begin
+    int32_t feed_back;        // 1: next token[b] = arg-max of this step (device-resident greedy loop)
+    int32_t step;             // steps run since the loop started (index into `history`)
+    int32_t history_cap;      // capacity of `history` in steps
+};
+
+__global__ void step_begin_kernel(int B, int V, const uint32_t* tokens, uint8_t* seen, const StepCtl* ctl) {
+    pdl_wait();
+    pdl_launch();
+    if (!ctl->mark_seen) return;
+    for (int b = threadIdx.x; b < B; b += blockDim.x) {       // launched as a single block
+        const uint32_t t = tokens[b];
+        if (t != kInactiveToken && t < (uint32_t)V) seen[(size_t)b * V + t] = 1;
+    }
+}
+
+__global__ void step_end_kernel(int B, uint32_t* tokens, int32_t* pos, const uint32_t* best_ids,
+                                uint32_t* history, StepCtl* ctl) {
+    pdl_wait();
+    pdl_launch();
+    const int fb = ctl->feed_back;
+    const int step = ctl->step;
+    const int hist_cap = ctl->history_cap;
+    for (int b = threadIdx.x; b < B; b += blockDim.x) {       // launched as a single block
+        if (tokens[b] == kInactiveToken) continue;
+        pos[b] += 1;
+        if (fb) {
+            const uint32_t nxt = best_ids[b];
+            if (step < hist_cap) history[(size_t)step * B + b] = nxt;
+            tokens[b] = nxt;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && fb) ctl->step = step + 1;
+}
+
+constexpr int kTopkThreads = 256;
+constexpr int kTopkChunk = 2048;
+
+// k rounds of block-wide arg-max with removal over `n` candidates held in shared memory.
+DEVINL void topk_rounds(float* sc, uint32_t* id, int n, int top_k, Cand* wbest, Cand* out) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int r = 0; r < top_k; ++r) {
+        Cand c{-INFINITY, 0xffffffffu};
+        int where = -1;
+        for (int i = tid; i < n; i += kTopkThreads) {
+            Cand o{sc[i], id[i]};
+            if (o.s > -INFINITY && cand_better(o, c)) { c = o; where = i; }
+        }
+        Cand w = warp_best(c);
+        if (lane == 0) wbest[warp] = w;
+        __syncthreads();
+        Cand best = wbest[0];
+        for (int j = 1; j < kTopkThreads / 32; ++j)
+            if (cand_better(wbest[j], best)) best = wbest[j];
+        if (where >= 0 && c.s == best.s && c.i == best.i) sc[where] = -INFINITY;   // unique index
+        if (tid == 0) {
+            out[r].s = best.s;
+            out[r].i = best.i == 0xffffffffu ? 0u : best.i;
+        }
+        __syncthreads();
+    }
+}
+
+// grid (chunks, B): per-chunk sorted top-k
+__global__ void __launch_bounds__(kTopkThreads)
+topk_stage1_kernel(const float* logits, int V, const uint8_t* seen, float penalty, int top_k, Cand* stage) {
+    __shared__ float sc[kTopkChunk];
+    __shared__ uint32_t id[kTopkChunk];
+    __shared__ Cand wbest[kTopkThreads / 32];
+    pdl_wait();
+    pdl_launch();
+    const int b = blockIdx.y;
+    const int start = blockIdx.x * kTopkChunk;
+    const int n = min(kTopkChunk, V - start);
+    for (int i = threadIdx.x; i < n; i += kTopkThreads) {
+        float s = logits[(size_t)b * V + start + i];
+        if (seen[(size_t)b * V + start + i] != 0 && penalty > 1.0f) s = s >= 0.0f ? s / penalty : s * penalty;
+        sc[i] = (s == s) ? s : -INFINITY;         // NaN is never selected
+        id[i] = (uint32_t)(start + i);
+    }
+    __syncthreads();
+    topk_rounds(sc, id, n, top_k, wbest, stage + ((size_t)b * gridDim.x + blockIdx.x) * top_k);
+}
+
+// grid (1, B): merge of chunks * top_k candidates; dynamic shared memory = n * 8 bytes
+__global__ void __launch_bounds__(kTopkThreads)
+topk_stage2_kernel(const Cand* stage, int n, int top_k, uint32_t* ids, float* scores) {
+    extern __shared__ __align__(16) unsigned char sm2[];
+    float* sc = reinterpret_cast<float*>(sm2);
+    uint32_t* id = reinterpret_cast<uint32_t*>(sm2) + n;
+    __shared__ Cand wbest[kTopkThreads / 32];
+    __shared__ Cand outc[64];
+    pdl_wait();
+    pdl_launch();
+    const int b = blockIdx.y;
+    for (int i = threadIdx.x; i < n; i += kTopkThreads) {
+        const Cand c = stage[(size_t)b * n + i];
+        sc[i] = c.s;
+        id[i] = c.i;
+    }
+    __syncthreads();
+    topk_rounds(sc, id, n, top_k, wbest, outc);
+    __syncthreads();
+    for (int r = threadIdx.x; r < top_k; r += kTopkThreads) {
+        ids[(size_t)b * top_k + r] = outc[r].i;
+        scores[(size_t)b * top_k + r] = outc[r].s;
+    }
+}
+
+}  // namespace oxg4

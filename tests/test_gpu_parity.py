@@ -1,0 +1,277 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle on identical
+seeded weights and prompts.
+
+Tolerances (from the benchmark specification): greedy token ids bit-exact over the first 32
+generated tokens; logits max-abs <= 1e-3 in f32 mode and <= 2e-2 in BF16 mode.
+"""
+import os
+
+import numpy as np
+import pytest
+
+from util import build_pair, margin, orc, pkg, small_cfg, syn
+
+pytestmark = pytest.mark.gpu
+
+TOL_F32 = 1e-3
+TOL_BF16 = 2e-2
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def run_both(gpu, oracle, prompt, n_decode, kv_dtype, page_tokens=256, max_seq=None):
+    """Teacher-forced comparison: both sides consume the oracle's greedy tokens; returns
+    (max logits diff, gpu greedy ids, oracle greedy ids, min oracle margin)."""
+    max_seq = max_seq or (len(prompt) + n_decode)
+    table = gpu.new_cache_table(max_seq, page_tokens=page_tokens, kv_dtype=kv_dtype)
+    cache = oracle.new_cache(max_seq)
+    for t in prompt[:-1]:
+        cache.prefill_token(int(t))
+    ref = cache.decode_logits(int(prompt[-1]))
+    got = gpu.prefill_prompt(prompt, table)
+    worst = float(np.abs(got - ref).max())
+    g_ids, o_ids, margins = [], [], []
+    for _ in range(n_decode):
+        o_tok = int(np.argmax(ref))
+        g_ids.append(int(np.argmax(got)))
+        o_ids.append(o_tok)
+        margins.append(margin(ref))
+        ref = cache.decode_logits(o_tok)
+        got = gpu.decode_token(o_tok, table)
+        worst = max(worst, float(np.abs(got - ref).max()))
+    return worst, g_ids, o_ids, min(margins)
+
+
+# ---- configuration 1: tiny f32 model ------------------------------------------------------------
+
+@pytest.fixture(scope="module")
+def c1():
+    cfg = syn.workload("c1")["cfg"]
+    gpu, oracle = build_pair(cfg, "f32", kv_bf16=False)
+    return cfg, gpu, oracle
+
+
+def test_c1_greedy_tokens_bit_exact_and_logits(c1):
+    cfg, gpu, oracle = c1
+    prompt = syn.prompt_ids(cfg["vocab_size"], 16, seed=1)
+    worst, g_ids, o_ids, mm = run_both(gpu, oracle, prompt, 32, pkg.F32)
+    assert g_ids == o_ids, f"first divergence margin {mm}"
+    assert worst <= TOL_F32, worst
+    gold = np.load(os.path.join(GOLDEN, "c1_hf_gemma4.npz"))
+    assert o_ids == gold["tokens"].tolist()
+
+
+def test_c1_generate_api_matches_fixture_and_oracle(c1):
+    cfg, gpu, oracle = c1
+    gold = np.load(os.path.join(GOLDEN, "c1_hf_gemma4.npz"))
+    weights = dict(syn.generate_weights(cfg, 0, "f32"))
+    model = pkg.Gemma4ForCausalLM.from_weights(cfg, weights, pkg.Device.Cuda(0), kv_dtype=pkg.F32)
+    streamed = []
+    out = model.generate_stream(gold["prompt"], pkg.GenerationConfig.greedy(32), streamed.append)
+    assert out[:16] == gold["prompt"].tolist()
+    assert out[16:] == gold["tokens"].tolist() == streamed
+    assert out[16:] == oracle.generate(gold["prompt"], 32, top_k=1).tolist()
+
+
+def test_c1_long_prompt_crosses_sliding_window(c1):
+    cfg, gpu, oracle = c1
+    gold = np.load(os.path.join(GOLDEN, "c1_hf_gemma4.npz"))
+    table = gpu.new_cache_table(208, kv_dtype=pkg.F32)
+    logits = gpu.prefill_prompt(gold["long_prompt"], table)
+    assert np.abs(logits - gold["long_logits"]).max() <= TOL_F32
+    assert table.position() == 200
+
+
+def test_c1_sampled_generation_matches_oracle(c1):
+    """Non-greedy path: top-k 8 candidates with repetition penalty, xorshift sampling on the host."""
+    cfg, gpu, oracle = c1
+    prompt = syn.prompt_ids(cfg["vocab_size"], 12, seed=4)
+    weights = dict(syn.generate_weights(cfg, 0, "f32"))
+    model = pkg.Gemma4ForCausalLM.from_weights(cfg, weights, pkg.Device.Cuda(0), kv_dtype=pkg.F32)
+    g = pkg.GenerationConfig(max_new_tokens=24, temperature=0.9, top_k=8, top_p=0.9, repetition_penalty=1.3,
+                             eos_token_ids=[], seed=1234)
+    ours = model.generate(prompt, g)[12:]
+    ref = oracle.generate(prompt, 24, temperature=0.9, top_k=8, top_p=0.9, repetition_penalty=1.3, seed=1234)
+    assert ours == ref.tolist()
+
+
+def test_c1_decode_topk_lists_match_oracle(c1):
+    cfg, gpu, oracle = c1
+    table = gpu.new_cache_table(16, kv_dtype=pkg.F32)
+    cache = oracle.new_cache(16)
+    tok = 7
+    for step, (k, pen) in enumerate([(1, 1.0), (5, 1.0), (64, 1.5), (64, 1.5), (3, 2.0)]):
+        got = gpu.decode_topk(tok, table, k, pen, True)
+        ids, scores = cache.decode_topk(tok, k, pen, True)
+        assert [g[0] for g in got] == ids.tolist(), (step, k)
+        np.testing.assert_allclose([g[1] for g in got], scores, atol=TOL_F32)
+        tok = int(ids[0])
+
+
+def test_c1_graph_replay_equals_eager(c1):
+    cfg, gpu, oracle = c1
+    prompt = syn.prompt_ids(cfg["vocab_size"], 10, seed=9)
+    outs = []
+    for disable in (False, True):
+        if disable:
+            os.environ["GEMMA4_DISABLE_CUDA_GRAPH"] = "1"
+        try:
+            table = gpu.new_cache_table(32, kv_dtype=pkg.F32)
+            logits = [gpu.prefill_prompt(prompt, table)]
+            tok = int(np.argmax(logits[0]))
+            for _ in range(6):
+                logits.append(gpu.decode_token(tok, table))
+                tok = int(np.argmax(logits[-1]))
+            outs.append(np.stack(logits))
+        finally:
+            os.environ.pop("GEMMA4_DISABLE_CUDA_GRAPH", None)
+    assert np.array_equal(outs[0], outs[1])           # same kernels, same order: identical bits
+
+
+def test_c1_device_greedy_loop_equals_host_loop(c1):
+    cfg, gpu, oracle = c1
+    prompt = syn.prompt_ids(cfg["vocab_size"], 16, seed=1)
+    table = gpu.new_cache_table(64, kv_dtype=pkg.F32)
+    first = int(np.argmax(gpu.prefill_prompt(prompt, table)))
+    ids, ms = gpu.decode_greedy(first, table, 20)
+    table2 = gpu.new_cache_table(64, kv_dtype=pkg.F32)
+    tok = int(np.argmax(gpu.prefill_prompt(prompt, table2)))
+    host = []
+    for _ in range(20):
+        tok = gpu.decode_topk(tok, table2, 1, 1.0, False)[0][0]
+        host.append(tok)
+    assert ids[:, 0].tolist() == host
+    assert ms > 0 and table.position() == 36
+
+
+def test_error_paths_on_device(c1):
+    cfg, gpu, oracle = c1
+    table = gpu.new_cache_table(4, kv_dtype=pkg.F32)
+    with pytest.raises(pkg.Oxg4Error) as e:
+        gpu.decode_topk(cfg["vocab_size"], table, 1, 1.0, True)       # decode.rs:675-679
+    assert "token id exceeds" in e.value.message
+    with pytest.raises(pkg.Oxg4Error):
+        gpu.prefill_prompt([], table)
+    with pytest.raises(pkg.Oxg4Error):
+        gpu.new_cache_table(0)                                         # cache.rs:36-38
+    gpu.prefill_prompt([1, 2, 3, 4], table, want_logits=False)
+    with pytest.raises(pkg.Oxg4Error) as e:
+        gpu.decode_token(5, table)                                     # cache is full
+    assert e.value.kind == "INVALID_SHAPE"
+    with pytest.raises(pkg.Oxg4Error) as e:
+        gpu.prefill_prompt([1, 2], table)                              # decode.rs:392-396
+    assert "empty cache table" in e.value.message
+    table.reset()
+    assert table.position() == 0
+    info = table._info()
+    assert info.layer_count == 2 and info.physical_cache_count == 2 and info.shared_layer_count == 0
+    assert gpu.weight_count() == 2 + 2 * 12 and gpu.weight_bytes() > 0
+
+
+# ---- BF16 recipe on small shapes: every head_dim / group size / cache type ------------------------
+
+@pytest.mark.parametrize("head_dim,heads,kv_heads,kv", [
+    (64, 4, 1, "bf16"), (64, 8, 1, "f32"), (128, 4, 2, "bf16"), (128, 2, 2, "f32"), (256, 4, 2, "bf16"),
+    (256, 4, 1, "f32")])
+def test_bf16_small_models(head_dim, heads, kv_heads, kv):
+    cfg = small_cfg(hidden=192, layers=3, heads=heads, kv_heads=kv_heads, head_dim=head_dim, inter=448,
+                    vocab=1000, window=12,
+                    layer_types=["sliding_attention", "full_attention", "sliding_attention"])
+    gpu, oracle = build_pair(cfg, "bf16", kv_bf16=(kv == "bf16"), norm_jitter=0.1)
+    prompt = syn.prompt_ids(cfg["vocab_size"], 20, seed=11)          # longer than the window
+    worst, g_ids, o_ids, mm = run_both(gpu, oracle, prompt, 16, pkg.BF16 if kv == "bf16" else pkg.F32,
+                                       page_tokens=8)
+    assert worst <= TOL_BF16, worst
+    if g_ids != o_ids:
+        assert mm < 2 * worst, f"token mismatch with margin {mm}, logits diff {worst}"
+
+
+def test_partial_rotary_and_rope_factor():
+    cfg = small_cfg(hidden=128, layers=2, heads=2, kv_heads=1, head_dim=64, inter=256, vocab=512, window=8,
+                    layer_types=["sliding_attention", "full_attention"])
+    cfg["rope_parameters"]["full_attention"].update(partial_rotary_factor=0.25, factor=8.0)
+    gpu, oracle = build_pair(cfg, "f32", kv_bf16=False, norm_jitter=0.1)
+    prompt = syn.prompt_ids(cfg["vocab_size"], 14, seed=12)
+    worst, g_ids, o_ids, _ = run_both(gpu, oracle, prompt, 8, pkg.F32, page_tokens=4)
+    assert worst <= TOL_F32 and g_ids == o_ids
+
+
+def test_ragged_shapes_odd_sizes():
+    """Hidden / intermediate sizes that are not multiples of the 512-byte chunk, vocabulary that is
+    odd, context of one token."""
+    cfg = small_cfg(hidden=136, layers=2, heads=2, kv_heads=2, head_dim=64, inter=200, vocab=777, window=5)
+    gpu, oracle = build_pair(cfg, "bf16", kv_bf16=True, norm_jitter=0.1)
+    worst, g_ids, o_ids, mm = run_both(gpu, oracle, np.array([3], dtype=np.uint32), 12, pkg.BF16, page_tokens=2)
+    assert worst <= TOL_BF16
+    if g_ids != o_ids:
+        assert mm < 2 * worst
+
+
+# ---- batches ---------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("batch", [2, 3, 5])
+def test_batched_ragged_decode_matches_per_sequence_oracle(batch):
+    cfg = small_cfg(hidden=128, layers=2, heads=4, kv_heads=2, head_dim=64, inter=256, vocab=600, window=10,
+                    layer_types=["sliding_attention", "full_attention"])
+    gpu, oracle = build_pair(cfg, "bf16", kv_bf16=True, norm_jitter=0.1)
+    lens = [3 + 4 * b for b in range(batch)]
+    prompts = [syn.prompt_ids(cfg["vocab_size"], n, seed=20 + b) for b, n in enumerate(lens)]
+    max_seq = [n + 6 for n in lens]
+    table = gpu.new_cache_table(max_seq, batch=batch, page_tokens=4, kv_dtype=pkg.BF16)
+    got = gpu.prefill_prompt(np.concatenate(prompts), table, lens=lens)
+    caches, refs = [], []
+    for b in range(batch):
+        c = oracle.new_cache(max_seq[b])
+        for t in prompts[b][:-1]:
+            c.prefill_token(int(t))
+        refs.append(c.decode_logits(int(prompts[b][-1])))
+        caches.append(c)
+    refs = np.stack(refs)
+    assert np.abs(got - refs).max() <= TOL_BF16
+    for _ in range(5):
+        toks = refs.argmax(-1).astype(np.uint32)
+        ids, scores = gpu.decode_topk(toks, table, 1, 1.0, True)
+        refs = np.stack([caches[b].decode_logits(int(toks[b])) for b in range(batch)])
+        for b in range(batch):
+            assert abs(scores[b, 0] - refs[b].max()) <= TOL_BF16
+            assert ids[b, 0] == refs[b].argmax() or margin(refs[b]) < 2 * TOL_BF16
+    assert [table.position(b) for b in range(batch)] == [n + 5 for n in lens]
+
+
+def test_batch_rows_are_independent():
+    """The same sequence placed in different rows of a batch, next to different neighbours, yields
+    bit-identical logits (no cross-row leakage; fixed reduction order)."""
+    cfg = small_cfg(hidden=128, layers=2, heads=4, kv_heads=2, head_dim=64, inter=256, vocab=600, window=10)
+    gpu, _ = build_pair(cfg, "bf16", kv_bf16=True, want_oracle=False)
+    a = syn.prompt_ids(cfg["vocab_size"], 9, seed=30)
+    b = syn.prompt_ids(cfg["vocab_size"], 5, seed=31)
+    t1 = gpu.new_cache_table([16, 16], batch=2, page_tokens=4)
+    l1 = gpu.prefill_prompt(np.concatenate([a, b]), t1, lens=[9, 5])
+    t2 = gpu.new_cache_table([16, 16, 16], batch=3, page_tokens=4)
+    l2 = gpu.prefill_prompt(np.concatenate([b, b, a]), t2, lens=[5, 5, 9])
+    assert np.array_equal(l1[0], l2[2]) and np.array_equal(l1[1], l2[0]) and np.array_equal(l2[0], l2[1])
+
+
+# ---- benchmark architectures at reduced depth / context (full widths, full vocabulary) -------------------------
+
+@pytest.mark.parametrize("name,layers", [("c2", 7), ("c3", 6)])
+def test_benchmark_architecture_reduced_depth(name, layers):
+    w = syn.workload(name)
+    cfg = syn.scaled_down(w["cfg"], layers=layers)
+    gpu, oracle = build_pair(cfg, "bf16", kv_bf16=True)
+    prompt = syn.prompt_ids(cfg["vocab_size"], 24, seed=1)
+    worst, g_ids, o_ids, mm = run_both(gpu, oracle, prompt, 8, pkg.BF16)
+    assert worst <= TOL_BF16, worst
+    assert g_ids == o_ids or mm < 2 * worst, (mm, worst)
+
+
+def test_determinism_two_runs_identical():
+    cfg = syn.scaled_down(syn.workload("c2")["cfg"], layers=3, vocab=8192)
+    gpu, _ = build_pair(cfg, "bf16", kv_bf16=True, want_oracle=False)
+    prompt = syn.prompt_ids(cfg["vocab_size"], 40, seed=5)
+    runs = []
+    for _ in range(2):
+        table = gpu.new_cache_table(64)
+        first = int(np.argmax(gpu.prefill_prompt(prompt, table)))
+        ids, _ = gpu.decode_greedy(first, table, 16)
+        runs.append((ids.copy(), gpu.decode_token(int(ids[-1, 0]), table)))
+    assert np.array_equal(runs[0][0], runs[1][0]) and np.array_equal(runs[0][1], runs[1][1])
