@@ -152,6 +152,8 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
     ap.add_argument("--prompt", type=int, default=None, help="override the prompt length")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=None, help="profiling aid: keep only the first LAYERS layers")
+    ap.add_argument("--vocab", type=int, default=None, help="profiling aid: shrink the vocabulary")
     args = ap.parse_args()
     warmup = max(args.warmup, 3)
 
@@ -162,6 +164,8 @@ def main():
     syn = pkg.synthetic
     w = syn.workload(args.workload)
     cfg, B = w["cfg"], w["batch"]
+    if args.layers or args.vocab:
+        cfg = syn.scaled_down(cfg, layers=args.layers, vocab=args.vocab)
     prompt_len = args.prompt or (w["prompt"] if isinstance(w["prompt"], int) else w["prompt"][1])
 
     import torch
@@ -286,7 +290,9 @@ def main():
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": args.workload, "batch": B, "prompt": lens[0] if len(set(lens)) == 1 else "ragged",
+        "config": {"workload": args.workload + (f" (reduced: layers={args.layers} vocab={args.vocab})"
+                                                 if (args.layers or args.vocab) else ""),
+                   "batch": B, "prompt": lens[0] if len(set(lens)) == 1 else "ragged",
                    "context_at_timing": contexts[0], "kv_dtype": "bf16", "page_tokens": 256,
                    "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
                    "l2": "per-step inputs (weights + KV) exceed the 126 MB L2; no flush",

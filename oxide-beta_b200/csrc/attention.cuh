@@ -25,7 +25,8 @@ constexpr int kAttnThreads = 256;
 constexpr int kAttnWarps = kAttnThreads / 32;
 
 struct AttnArgs {
-    PartialSpec qkv;         // QKV projection partials, columns q | k | v
+    const float* qkv;        // [B, qkv_n] QKV projection output, columns q | k | v
+    int qkv_n;
     int B, Nq, Nkv;
     const float* q_norm;     // [D]
     const float* k_norm;     // [D]
@@ -144,7 +145,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
             float ss = 0.0f;
 #pragma unroll
             for (int e = 0; e < EPT; ++e) {
-                const float v = sum_partials(a.qkv, a.B, b, col + lane * EPT + e);
+                const float v = a.qkv[(size_t)b * a.qkv_n + col + lane * EPT + e];
                 t[e] = v;
                 ss += v * v;
             }

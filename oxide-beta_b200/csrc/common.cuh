@@ -97,21 +97,6 @@ DEVINL Cand warp_best(Cand c) {
     return c;
 }
 
-// Where the pieces of a projection's output row were stored by the producing launch.
-struct PartialSpec {
-    const float* buf;   // [slots, B, n]
-    int n;              // (virtual) rows of the producing projection
-    int cpr;            // chunks per row of the producer
-    int lr;             // chunks per warp run of the producer
-};
-DEVINL float sum_partials(const PartialSpec& p, int B, int b, int r) {
-    const int first = (int)(((long long)r * p.cpr) / p.lr);
-    const int last = (int)(((long long)(r + 1) * p.cpr - 1) / p.lr);
-    float t = 0.0f;
-    for (int s = 0; s <= last - first; ++s) t += p.buf[((size_t)s * B + b) * p.n + r];
-    return t;
-}
-
 // kernel_module.rs:1441-1458 — tanh-GELU through expf, times the up projection.
 DEVINL float gelu_mul(float x, float up) {
     float inner = 0.7978846f * (x + 0.044715f * x * x * x);

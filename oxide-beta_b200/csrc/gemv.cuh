@@ -8,19 +8,18 @@
 //                        (or h = embedding row * sqrt(H) for the first layer), store h once, then
 //                        x = bf16(rmsnorm(h, w_norm))
 //             PRO_PLAIN: x = bf16(in)
-//             PRO_GEGLU: x = bf16(gelu_tanh(gate) * up) from the gate/up projection's partials
 //   body      out[n] = sum_k x[k] * W[n,k], f32 accumulate, 16-byte coalesced streaming loads,
 //             warp-shuffle reductions
-//   epilogue  EPI_PARTIAL / EPI_GATEUP: store row-segment partial sums (see below)
-//             EPI_LOGITS : optional logits store + running arg-max with repetition penalty
+//   epilogue  EPI_STORE : out[b, n]
+//             EPI_GATEUP: out[b, i] = gelu_tanh(gate_i . x) * (up_i . x)
+//             EPI_LOGITS: optional logits store + running arg-max with repetition penalty
 //
-// Work split (EPI_PARTIAL / EPI_GATEUP). The matrix is cut into 512-byte chunks (one 16-byte load
-// per lane); the N * chunks_per_row chunks are dealt out as equal contiguous runs, one per warp of
-// the grid, so every SM streams the same number of bytes whatever the matrix shape. A run that
-// ends inside a row leaves a partial sum; the pieces of a row are stored in consecutive "slots"
-// [slot, batch row, n] and added up, in slot order, by the consuming kernel (PartialSpec), which
-// makes the split-K reduction deterministic without atomics. EPI_GATEUP streams gate and up as
-// one matrix of 2*I virtual rows (even rows gate_i, odd rows up_i).
+// Work split (EPI_STORE / EPI_GATEUP). Every CTA owns a contiguous block of output rows (for
+// EPI_GATEUP a block of (gate_i, up_i) pairs, streamed as 2*I virtual rows). The block is cut into
+// 512-byte chunks (one 16-byte load per lane) and the chunks are dealt out as equal contiguous runs
+// to the 16 warps, so all warps stream the same number of bytes whatever the matrix shape. A run
+// that ends inside a row leaves a partial sum; the pieces of a row meet in shared memory and are
+// added in a fixed order, which keeps the split-K reduction deterministic without atomics.
 //
 // The kernel is HBM-bound: bytes per launch = N * K * sizeof(weight).
 #pragma once
@@ -28,26 +27,27 @@
 
 namespace oxg4 {
 
-enum { PRO_PLAIN = 0, PRO_NORM = 1, PRO_GEGLU = 2 };
-enum { EPI_PARTIAL = 0, EPI_GATEUP = 1, EPI_LOGITS = 2 };
+enum { PRO_PLAIN = 0, PRO_NORM = 1 };
+enum { EPI_STORE = 0, EPI_GATEUP = 1, EPI_LOGITS = 2 };
 
 constexpr int kGemvThreads = 512;
 constexpr int kGemvWarps = kGemvThreads / 32;
+constexpr int kGemvMaxJ = 11;        // PRO_NORM keeps hidden/512 values per thread: hidden <= 5632
 
 struct GemvArgs {
     const void* W0;          // [N, K] row-major (EPI_GATEUP: gate)
-    const void* W1;          // EPI_GATEUP: up projection [N, K]
+    const void* W1;          // EPI_GATEUP: up projection
     int N, K;                // rows (EPI_GATEUP: virtual rows = 2 * intermediate), columns
-    int cpr, lr;             // chunks per row, chunks per warp run
+    int cpr;                 // 512-byte chunks per row
+    int slots;               // most pieces a row is cut into inside one CTA
     int B;                   // activation rows in the step
     // PRO_PLAIN
     const float* in;         // [B, K]
-    // PRO_GEGLU: `raw` describes the gate/up partials (2*K virtual rows)
     // PRO_NORM (K == hidden size)
     const float* h_in;       // [B, K] residual stream before the pending update (unused with embed)
     float* h_out;            // [B, K] residual stream after it (written by block 0)
-    PartialSpec raw;         // previous projection's partials (buf == null: nothing pending)
-    const float* w_post;     // norm weight applied to the previous projection
+    const float* raw;        // [B, K] previous projection output still to be normed and added, or null
+    const float* w_post;     // norm weight applied to `raw`
     float scalar;            // layer_scalar of the layer that just ended (1.0 otherwise)
     const float* w_norm;     // norm weight producing x
     const void* embed;       // embedding table [V, K] (same element type as W0), or null
@@ -55,8 +55,8 @@ struct GemvArgs {
     float embed_scale;
     float eps;
     // epilogue
-    float* out;              // PARTIAL/GATEUP: [slots, B, N]; LOGITS: [B, N] or null
-    const uint8_t* seen;     // LOGITS: [B, N] repetition bitmap or null
+    float* out;              // STORE: [B, N]; GATEUP: [B, N/2]; LOGITS: [B, n_total] or null
+    const uint8_t* seen;     // LOGITS: [B, n_total] repetition bitmap or null
     float penalty;
     int row_offset;          // LOGITS: first vocabulary row of this rank's slice
     int n_total;             // LOGITS: full vocabulary (row stride of `out` and `seen`)
@@ -110,6 +110,13 @@ DEVINL void fma16(float (&acc)[NB], const uint4& w, const typename WTraits<WT>::
     }
 }
 
+// rows [first, first + count) of `total` rows dealt to `parts` CTAs as evenly as possible
+DEVINL void block_range(int total, int parts, int idx, int& first, int& count) {
+    const int base = total / parts, rem = total % parts;
+    first = idx * base + min(idx, rem);
+    count = base + (idx < rem ? 1 : 0);
+}
+
 template <typename WT, int NB, int PRO, int EPI>
 __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a) {
     typedef WTraits<WT> T;
@@ -120,7 +127,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a)
     const int K = a.K;
     XT* xs = reinterpret_cast<XT*>(smem_raw);                                        // [NB][K]
     float* red = reinterpret_cast<float*>(smem_raw + (size_t)NB * K * sizeof(XT));   // [NB*32]
-    float* hs = red + NB * 32;                         // [NB][K] (PRO_NORM) / Cand scratch (LOGITS)
+    float* pieces = red + NB * 32;                     // [rows_cta][slots][NB] / Cand scratch
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int b0 = blockIdx.y * NB;
     const int nb = min(NB, a.B - b0);
@@ -133,7 +140,20 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a)
             return (const WT*)a.W0 + (size_t)r * K;
     };
 
-    // ---- pre-dependency section: warm L2 with the start of what this CTA will stream ----
+    // this CTA's block of (virtual) rows
+    int row_first = 0, rows_cta = 0;
+    if constexpr (EPI == EPI_GATEUP) {
+        block_range(a.N / 2, gridDim.x, blockIdx.x, row_first, rows_cta);
+        row_first *= 2;
+        rows_cta *= 2;
+    } else if constexpr (EPI == EPI_STORE) {
+        block_range(a.N, gridDim.x, blockIdx.x, row_first, rows_cta);
+    }
+    const int chunks_cta = rows_cta * a.cpr;
+    const int lr = max(1, (chunks_cta + kGemvWarps - 1) / kGemvWarps);   // chunks per warp run
+
+    // ---- pre-dependency section: nothing here reads what the previous kernel wrote ----
+    // warm L2 with the start of what this CTA will stream
     if constexpr (EPI == EPI_LOGITS) {
         const int U = (a.N + 1) / 2;
         const int lines_per_row = (int)((row_bytes + 127) / 128);
@@ -145,15 +165,22 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a)
             for (int l = tid; l < nl; l += kGemvThreads) prefetch_l2(p0 + (size_t)l * 128);
         }
     } else {
-        const long long TC = (long long)a.N * a.cpr;
-        long long c = (long long)blockIdx.x * kGemvWarps * a.lr;
-        const long long cend = min(TC, c + (long long)kGemvWarps * a.lr);
         // at most 512 chunks (256 KiB) per CTA; one 128-byte line per thread and step
-        const long long cstop = min(cend, c + 512);
-        for (long long cc = c + (tid >> 2); cc < cstop; cc += kGemvThreads / 4) {
-            const int r = (int)(cc / a.cpr);
-            const int col = (int)(cc % a.cpr) * STEP + (tid & 3) * (STEP / 4);
+        const int cstop = min(chunks_cta, 512);
+        for (int cc = (tid >> 2); cc < cstop; cc += kGemvThreads / 4) {
+            const int r = row_first + cc / a.cpr;
+            const int col = (cc % a.cpr) * STEP + (tid & 3) * (STEP / 4);
             if (col < K) prefetch_l2((const char*)(row_ptr(r) + col));
+        }
+    }
+    // norm weights are model constants: fetch them before waiting on the previous kernel
+    float wpost[kGemvMaxJ], wnorm[kGemvMaxJ];
+    if constexpr (PRO == PRO_NORM) {
+#pragma unroll
+        for (int j = 0; j < kGemvMaxJ; ++j) {
+            const int i = tid + j * kGemvThreads;
+            wnorm[j] = (i < K) ? a.w_norm[i] : 0.0f;
+            wpost[j] = (i < K && a.w_post) ? a.w_post[i] : 0.0f;
         }
     }
     pdl_wait();
@@ -163,66 +190,52 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a)
         for (int b = 0; b < nb; ++b)
             for (int i = tid; i < K; i += kGemvThreads)
                 T::store_x(xs + (size_t)b * K + i, a.in[(size_t)(b0 + b) * K + i]);
-    } else if constexpr (PRO == PRO_GEGLU) {
-        for (int b = 0; b < nb; ++b)
-            for (int i = tid; i < K; i += kGemvThreads) {
-                const float g = sum_partials(a.raw, a.B, b0 + b, 2 * i);
-                const float u = sum_partials(a.raw, a.B, b0 + b, 2 * i + 1);
-                T::store_x(xs + (size_t)b * K + i, gelu_mul(g, u));
-            }
     } else {
-        float ss[NB];
         const bool writer = (blockIdx.x == 0);
-        if (a.embed != nullptr) {
-            // kernel_module.rs:1272-1285: embedding row widened to f32, times sqrt(hidden)
+        for (int b = 0; b < nb; ++b) {
+            float hv[kGemvMaxJ];
+            float ss[1];
+            if (a.embed != nullptr) {
+                // kernel_module.rs:1272-1285: embedding row widened to f32, times sqrt(hidden)
+                uint32_t tok = a.tokens[b0 + b];
+                if (tok == kInactiveToken) tok = 0;
 #pragma unroll
-            for (int b = 0; b < NB; ++b) {
-                ss[b] = 0.0f;
-                if (b < nb) {
-                    uint32_t tok = a.tokens[b0 + b];
-                    if (tok == kInactiveToken) tok = 0;
-                    for (int i = tid; i < K; i += kGemvThreads) {
-                        float h = T::elem(a.embed, (size_t)tok * K + i) * a.embed_scale;
-                        hs[(size_t)b * K + i] = h;
-                        if (writer) a.h_out[(size_t)(b0 + b) * K + i] = h;
-                        ss[b] += h * h;
-                    }
+                for (int j = 0; j < kGemvMaxJ; ++j) {
+                    const int i = tid + j * kGemvThreads;
+                    hv[j] = (i < K) ? T::elem(a.embed, (size_t)tok * K + i) * a.embed_scale : 0.0f;
+                }
+            } else {
+                float t[kGemvMaxJ];
+                ss[0] = 0.0f;
+#pragma unroll
+                for (int j = 0; j < kGemvMaxJ; ++j) {
+                    const int i = tid + j * kGemvThreads;
+                    t[j] = (i < K) ? a.raw[(size_t)(b0 + b) * K + i] : 0.0f;
+                    hv[j] = (i < K) ? a.h_in[(size_t)(b0 + b) * K + i] : 0.0f;
+                    ss[0] += t[j] * t[j];
+                }
+                block_sum<1>(ss, red);
+                const float r = 1.0f / sqrtf(ss[0] / (float)K + a.eps);
+#pragma unroll
+                for (int j = 0; j < kGemvMaxJ; ++j) hv[j] = (hv[j] + t[j] * r * wpost[j]) * a.scalar;
+            }
+            ss[0] = 0.0f;
+#pragma unroll
+            for (int j = 0; j < kGemvMaxJ; ++j) {
+                const int i = tid + j * kGemvThreads;
+                if (i < K) {
+                    if (writer) a.h_out[(size_t)(b0 + b) * K + i] = hv[j];
+                    ss[0] += hv[j] * hv[j];
                 }
             }
-        } else {
+            block_sum<1>(ss, red);
+            const float r2 = 1.0f / sqrtf(ss[0] / (float)K + a.eps);
 #pragma unroll
-            for (int b = 0; b < NB; ++b) {
-                ss[b] = 0.0f;
-                if (b < nb)
-                    for (int i = tid; i < K; i += kGemvThreads) {
-                        const float t = sum_partials(a.raw, a.B, b0 + b, i);
-                        hs[(size_t)b * K + i] = t;
-                        ss[b] += t * t;
-                    }
+            for (int j = 0; j < kGemvMaxJ; ++j) {
+                const int i = tid + j * kGemvThreads;
+                if (i < K) T::store_x(xs + (size_t)b * K + i, hv[j] * r2 * wnorm[j]);
             }
-            block_sum<NB>(ss, red);
-            float r[NB];
-#pragma unroll
-            for (int b = 0; b < NB; ++b) { r[b] = 1.0f / sqrtf(ss[b] / (float)K + a.eps); ss[b] = 0.0f; }
-#pragma unroll
-            for (int b = 0; b < NB; ++b)
-                if (b < nb)
-                    for (int i = tid; i < K; i += kGemvThreads) {
-                        const float nrm = hs[(size_t)b * K + i] * r[b] * a.w_post[i];
-                        const float h = (a.h_in[(size_t)(b0 + b) * K + i] + nrm) * a.scalar;
-                        hs[(size_t)b * K + i] = h;
-                        if (writer) a.h_out[(size_t)(b0 + b) * K + i] = h;
-                        ss[b] += h * h;
-                    }
         }
-        block_sum<NB>(ss, red);
-#pragma unroll
-        for (int b = 0; b < NB; ++b)
-            if (b < nb) {
-                const float r = 1.0f / sqrtf(ss[b] / (float)K + a.eps);
-                for (int i = tid; i < K; i += kGemvThreads)
-                    T::store_x(xs + (size_t)b * K + i, hs[(size_t)b * K + i] * r * a.w_norm[i]);
-            }
     }
     // rows of a partial batch chunk that do not exist read zeros
     for (int b = nb; b < NB; ++b)
@@ -231,20 +244,18 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a)
     pdl_launch();
 
     if constexpr (EPI != EPI_LOGITS) {
-        // ---- body: this warp's contiguous run of chunks, cut at row boundaries ----
-        const long long TC = (long long)a.N * a.cpr;
-        const long long g = (long long)blockIdx.x * kGemvWarps + warp;
-        long long c0 = g * a.lr;
-        const long long c1 = min(TC, c0 + a.lr);
+        // ---- body: this warp's contiguous run of the CTA's chunks, cut at row boundaries ----
+        int c0 = warp * lr;
+        const int c1 = min(chunks_cta, c0 + lr);
         const bool ragged = (K % STEP) != 0;          // the last chunk of a row is partly empty
         while (c0 < c1) {
-            const int r = (int)(c0 / a.cpr);
-            const long long rend = min(c1, (long long)(r + 1) * a.cpr);
-            const int cc = (int)(c0 - (long long)r * a.cpr);
-            const int ncs = (int)(rend - c0);
+            const int rl = c0 / a.cpr;                 // row inside the CTA's block
+            const int rend = min(c1, (rl + 1) * a.cpr);
+            const int cc = c0 - rl * a.cpr;
+            const int ncs = rend - c0;
             const bool has_tail = ragged && (cc + ncs == a.cpr);
             const int nfull = has_tail ? ncs - 1 : ncs;
-            const WT* p = row_ptr(r) + (size_t)cc * STEP + lane * EPL;
+            const WT* p = row_ptr(row_first + rl) + (size_t)cc * STEP + lane * EPL;
             int k = cc * STEP + lane * EPL;
             float acc[NB];
 #pragma unroll
@@ -259,12 +270,23 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a)
                 p += 8 * STEP;
                 k += 8 * STEP;
             }
-            for (; j + 2 <= nfull; j += 2) {
+            if (j + 4 <= nfull) {
+                uint4 w[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) w[q] = ldg_stream16(p + q * STEP);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) fma16<WT, NB>(acc, w[q], xs, K, k + q * STEP);
+                p += 4 * STEP;
+                k += 4 * STEP;
+                j += 4;
+            }
+            if (j + 2 <= nfull) {
                 uint4 w0 = ldg_stream16(p), w1 = ldg_stream16(p + STEP);
                 fma16<WT, NB>(acc, w0, xs, K, k);
                 fma16<WT, NB>(acc, w1, xs, K, k + STEP);
                 p += 2 * STEP;
                 k += 2 * STEP;
+                j += 2;
             }
             for (; j < ncs; ++j) {
                 if (k < K) {
@@ -277,12 +299,33 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a)
 #pragma unroll
             for (int b = 0; b < NB; ++b) acc[b] = warp_sum(acc[b]);
             if (lane == 0) {
-                const int slot = (int)(g - ((long long)r * a.cpr) / a.lr);
+                const int slot = warp - (rl * a.cpr) / lr;
 #pragma unroll
-                for (int b = 0; b < NB; ++b)
-                    if (b < nb) a.out[((size_t)slot * a.B + b0 + b) * a.N + r] = acc[b];
+                for (int b = 0; b < NB; ++b) pieces[((size_t)rl * a.slots + slot) * NB + b] = acc[b];
             }
             c0 = rend;
+        }
+        __syncthreads();
+        // ---- epilogue: add the pieces of each row in slot order ----
+        auto row_total = [&](int rl, int b) -> float {
+            const int first = (rl * a.cpr) / lr;
+            const int last = ((rl + 1) * a.cpr - 1) / lr;
+            float t = 0.0f;
+            for (int s = 0; s <= last - first; ++s) t += pieces[((size_t)rl * a.slots + s) * NB + b];
+            return t;
+        };
+        if constexpr (EPI == EPI_STORE) {
+            for (int idx = tid; idx < rows_cta * nb; idx += kGemvThreads) {
+                const int rl = idx % rows_cta, b = idx / rows_cta;
+                a.out[(size_t)(b0 + b) * a.N + row_first + rl] = row_total(rl, b);
+            }
+        } else {
+            const int pairs = rows_cta / 2;
+            for (int idx = tid; idx < pairs * nb; idx += kGemvThreads) {
+                const int pl = idx % pairs, b = idx / pairs;
+                const float g = row_total(2 * pl, b), u = row_total(2 * pl + 1, b);
+                a.out[(size_t)(b0 + b) * (a.N / 2) + row_first / 2 + pl] = gelu_mul(g, u);
+            }
         }
     } else {
         // ---- body: one warp per row pair; logits + running arg-max ----
@@ -343,7 +386,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a)
             }
         }
         // block-level arg-max, then the last block to arrive merges all blocks
-        Cand* wc = reinterpret_cast<Cand*>(hs);           // hs is free after the prologue
+        Cand* wc = reinterpret_cast<Cand*>(pieces);
         __shared__ unsigned int s_last;
         if (lane == 0)
             for (int b = 0; b < NB; ++b) wc[b * kGemvWarps + warp] = best[b];
@@ -378,17 +421,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a)
             if (tid == 0) a.ticket[blockIdx.y] = 0u;       // ready for the next launch / replay
         }
     }
-}
-
-// dynamic shared memory the kernel needs
-template <typename WT, int NB, int PRO>
-inline size_t gemv_smem_bytes(int K) {
-    size_t x = (size_t)NB * K * sizeof(typename WTraits<WT>::XT);
-    size_t red = (size_t)(NB * 32) * sizeof(float);
-    size_t hs = (PRO == PRO_NORM) ? (size_t)NB * K * sizeof(float) : 0;
-    size_t cands = (size_t)NB * kGemvWarps * sizeof(Cand);
-    if (hs < cands) hs = cands;
-    return x + red + hs;
 }
 
 }  // namespace oxg4

@@ -76,8 +76,8 @@ struct LayerPlan {            // Gemma4DecodeLayerPlan (gemma4_cuda/mod.rs:65-93
     float* inv_freq = nullptr;
 };
 
-struct GemvPlan {             // how a projection is cut into warp runs
-    int N = 0, K = 0, cpr = 0, lr = 0, grid = 0, slots = 0;
+struct GemvPlan {             // how a projection is cut into CTA row blocks and warp runs
+    int N = 0, K = 0, cpr = 0, grid = 0, slots = 1, rows_max = 0;
 };
 
 struct ProfileSlot {
@@ -132,18 +132,18 @@ static inline float host_bf16_to_f32(uint16_t h) {
     return f;
 }
 
-static GemvPlan make_plan(int N, int K, int es, int num_sms) {
+static GemvPlan make_plan(int N, int K, int es, int num_sms, int group /*rows that stay in one CTA*/) {
     GemvPlan p;
     p.N = N;
     p.K = K;
     const int step = 32 * (16 / es);
     p.cpr = (K + step - 1) / step;
-    const long long TC = (long long)N * p.cpr;
-    p.grid = (int)std::min<long long>(num_sms, (TC + kGemvWarps - 1) / kGemvWarps);
-    if (p.grid < 1) p.grid = 1;
-    p.lr = (int)((TC + (long long)p.grid * kGemvWarps - 1) / ((long long)p.grid * kGemvWarps));
-    if (p.lr < 1) p.lr = 1;
-    p.slots = (p.cpr - 1) / p.lr + 2;
+    const int groups = N / group;
+    p.grid = std::max(1, std::min(num_sms, groups));
+    const int rows_min = (groups / p.grid) * group;
+    p.rows_max = ((groups + p.grid - 1) / p.grid) * group;
+    const int lr_min = std::max(1, (rows_min * p.cpr + kGemvWarps - 1) / kGemvWarps);
+    p.slots = std::min(kGemvWarps, (p.cpr - 1) / lr_min + 2);
     return p;
 }
 
@@ -292,14 +292,22 @@ static int32_t need(oxg4_model* m, const std::string& name, std::vector<int64_t>
     return OXG4_OK;
 }
 
+// opt a kernel in to the full 227 KiB of shared memory (static + dynamic) of an sm_100 CTA
+template <typename F>
+static int32_t allow_big_smem(F* kernel) {
+    cudaFuncAttributes fa;
+    CK(cudaFuncGetAttributes(&fa, (const void*)kernel));
+    const int big = 227 * 1024 - (int)fa.sharedSizeBytes;
+    CK(cudaFuncSetAttribute((const void*)kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    return OXG4_OK;
+}
+
 template <typename WT, int NB>
 static int32_t set_gemv_attrs() {
-    const int big = 227 * 1024;
-#define SETA(PRO, EPI) CK(cudaFuncSetAttribute(gemv_kernel<WT, NB, PRO, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, big))
-    SETA(PRO_NORM, EPI_PARTIAL);
-    SETA(PRO_PLAIN, EPI_PARTIAL);
+#define SETA(PRO, EPI) TRY(allow_big_smem(gemv_kernel<WT, NB, PRO, EPI>))
+    SETA(PRO_NORM, EPI_STORE);
+    SETA(PRO_PLAIN, EPI_STORE);
     SETA(PRO_NORM, EPI_GATEUP);
-    SETA(PRO_GEGLU, EPI_PARTIAL);
     SETA(PRO_NORM, EPI_LOGITS);
 #undef SETA
     return OXG4_OK;
@@ -307,11 +315,10 @@ static int32_t set_gemv_attrs() {
 
 template <typename KT, int D>
 static int32_t set_attn_attrs() {
-    const int big = 160 * 1024;
-    CK(cudaFuncSetAttribute(attn_decode_kernel<KT, D, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-    CK(cudaFuncSetAttribute(attn_decode_kernel<KT, D, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-    CK(cudaFuncSetAttribute(attn_decode_kernel<KT, D, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-    CK(cudaFuncSetAttribute(attn_decode_kernel<KT, D, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    TRY(allow_big_smem(attn_decode_kernel<KT, D, 1>));
+    TRY(allow_big_smem(attn_decode_kernel<KT, D, 2>));
+    TRY(allow_big_smem(attn_decode_kernel<KT, D, 4>));
+    TRY(allow_big_smem(attn_decode_kernel<KT, D, 8>));
     return OXG4_OK;
 }
 
@@ -377,11 +384,11 @@ extern "C" int32_t oxg4_model_finalize(oxg4_model* m) {
         CK(cudaMalloc(&p.inv_freq, sizeof(float) * (D / 2)));
         CK(cudaMemcpy(p.inv_freq, inv.data(), sizeof(float) * (D / 2), cudaMemcpyHostToDevice));
     }
-    m->p_qkv = make_plan((int)(QW + 2 * KW), H, m->es, m->num_sms);
-    m->p_o = make_plan(H, (int)QW, m->es, m->num_sms);
-    m->p_gateup = make_plan(2 * m->I, H, m->es, m->num_sms);
-    m->p_down = make_plan(H, m->I, m->es, m->num_sms);
-    m->p_lm = make_plan(m->Vloc, H, m->es, m->num_sms);
+    m->p_qkv = make_plan((int)(QW + 2 * KW), H, m->es, m->num_sms, 1);
+    m->p_o = make_plan(H, (int)QW, m->es, m->num_sms, 1);
+    m->p_gateup = make_plan(2 * m->I, H, m->es, m->num_sms, 2);
+    m->p_down = make_plan(H, m->I, m->es, m->num_sms, 1);
+    m->p_lm = make_plan(m->Vloc, H, m->es, m->num_sms, 1);
     m->p_lm.grid = std::min(m->num_sms, std::max(1, (m->Vloc + 2 * kGemvWarps - 1) / (2 * kGemvWarps)));
     if (m->es == 2) {
         TRY((set_gemv_attrs<uint16_t, 1>())); TRY((set_gemv_attrs<uint16_t, 2>())); TRY((set_gemv_attrs<uint16_t, 4>()));
@@ -520,11 +527,11 @@ static int32_t cache_build(oxg4_cache* c) {
     TRY(dalloc(c, &c->ctl, 1));
     TRY(dalloc(c, &c->hA, (size_t)B * H));
     TRY(dalloc(c, &c->hB, (size_t)B * H));
-    TRY(dalloc(c, &c->qkv_raw, (size_t)m->p_qkv.slots * B * m->p_qkv.N));
+    TRY(dalloc(c, &c->qkv_raw, (size_t)B * m->p_qkv.N));
     TRY(dalloc(c, &c->attn_out, (size_t)B * m->Nq * D));
-    TRY(dalloc(c, &c->o_raw, (size_t)m->p_o.slots * B * H));
-    TRY(dalloc(c, &c->gu_raw, (size_t)m->p_gateup.slots * B * m->p_gateup.N));
-    TRY(dalloc(c, &c->down_raw, (size_t)m->p_down.slots * B * H));
+    TRY(dalloc(c, &c->o_raw, (size_t)B * H));
+    TRY(dalloc(c, &c->gu_raw, (size_t)B * m->I));
+    TRY(dalloc(c, &c->down_raw, (size_t)B * H));
     TRY(dalloc(c, &c->logits, (size_t)B * m->V));
     TRY(dalloc(c, &c->attn_part, (size_t)B * m->Nkv * smax * m->G * (D + 2)));
     TRY(dalloc(c, &c->attn_ticket, (size_t)B * m->Nkv));
@@ -664,10 +671,9 @@ struct Launcher {
 template <typename WT>
 static void (*pick_gemv(int nb, int pro, int epi))(const GemvArgs) {
 #define PICK(NB)                                                                              \
-    if (pro == PRO_NORM && epi == EPI_PARTIAL) return gemv_kernel<WT, NB, PRO_NORM, EPI_PARTIAL>;   \
-    if (pro == PRO_PLAIN && epi == EPI_PARTIAL) return gemv_kernel<WT, NB, PRO_PLAIN, EPI_PARTIAL>; \
+    if (pro == PRO_NORM && epi == EPI_STORE) return gemv_kernel<WT, NB, PRO_NORM, EPI_STORE>;       \
+    if (pro == PRO_PLAIN && epi == EPI_STORE) return gemv_kernel<WT, NB, PRO_PLAIN, EPI_STORE>;     \
     if (pro == PRO_NORM && epi == EPI_GATEUP) return gemv_kernel<WT, NB, PRO_NORM, EPI_GATEUP>;     \
-    if (pro == PRO_GEGLU && epi == EPI_PARTIAL) return gemv_kernel<WT, NB, PRO_GEGLU, EPI_PARTIAL>; \
     if (pro == PRO_NORM && epi == EPI_LOGITS) return gemv_kernel<WT, NB, PRO_NORM, EPI_LOGITS>;
     if (nb == 1) { PICK(1) }
     if (nb == 2) { PICK(2) }
@@ -683,15 +689,19 @@ static void launch_gemv(Launcher& ln, const char* kind, oxg4_cache* c, GemvArgs 
     a.N = p.N;
     a.K = p.K;
     a.cpr = p.cpr;
-    a.lr = p.lr;
+    a.slots = p.slots;
     a.B = B;
     a.eps = m->cfg.rms_norm_eps;
     const size_t xes = m->es == 2 ? 2 : 4;
     size_t smem = (size_t)nb * p.K * xes + (size_t)nb * 32 * 4;
-    size_t extra = pro == PRO_NORM ? (size_t)nb * p.K * 4 : 0;
+    size_t extra = (size_t)p.rows_max * p.slots * nb * 4;
     extra = std::max(extra, (size_t)nb * kGemvWarps * sizeof(Cand));
+    if (pro == PRO_NORM && p.K > kGemvMaxJ * kGemvThreads) {
+        ln.status = fail(OXG4_UNSUPPORTED, "hidden size above %d is not supported", kGemvMaxJ * kGemvThreads);
+        return;
+    }
     smem += extra;
-    if (smem > 227 * 1024) {
+    if (smem > 226 * 1024) {
         ln.status = fail(OXG4_UNSUPPORTED, "projection %s needs %zu bytes of shared memory", kind, smem);
         return;
     }
@@ -712,15 +722,6 @@ static void (*pick_attn(int D, int G))(const AttnArgs) {
     PA(64) PA(128) PA(256)
 #undef PA
     return nullptr;
-}
-
-static PartialSpec spec_of(const float* buf, const GemvPlan& p) {
-    PartialSpec s;
-    s.buf = buf;
-    s.n = p.N;
-    s.cpr = p.cpr;
-    s.lr = p.lr;
-    return s;
 }
 
 // Launches every kernel of one step on the model's stream (eagerly or under stream capture).
@@ -744,16 +745,17 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
                 a.tokens = c->tokens;
                 a.embed_scale = sqrtf((float)H);
             } else {
-                a.raw = spec_of(c->down_raw, m->p_down);
+                a.raw = c->down_raw;
                 a.w_post = m->layers[l - 1].post_ff_ln;
                 a.scalar = m->layers[l - 1].layer_scalar;
             }
             a.out = c->qkv_raw;
-            launch_gemv(ln, "qkv", c, a, m->p_qkv, PRO_NORM, EPI_PARTIAL);
+            launch_gemv(ln, "qkv", c, a, m->p_qkv, PRO_NORM, EPI_STORE);
         }
         {   // q/k norm + RoPE + v norm + KV append + attention (decode.rs:99-157)
             AttnArgs a{};
-            a.qkv = spec_of(c->qkv_raw, m->p_qkv);
+            a.qkv = c->qkv_raw;
+            a.qkv_n = m->p_qkv.N;
             a.B = B;
             a.Nq = m->Nq;
             a.Nkv = m->Nkv;
@@ -784,7 +786,7 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
             a.W0 = p.wo;
             a.in = c->attn_out;
             a.out = c->o_raw;
-            launch_gemv(ln, "o", c, a, m->p_o, PRO_PLAIN, EPI_PARTIAL);
+            launch_gemv(ln, "o", c, a, m->p_o, PRO_PLAIN, EPI_STORE);
         }
         {   // post-attention norm + residual, pre-FF norm, gate and up projections (decode.rs:161-171, 14-16)
             GemvArgs a{};
@@ -792,7 +794,7 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
             a.W1 = p.wup;
             a.h_in = c->hB;
             a.h_out = c->hA;
-            a.raw = spec_of(c->o_raw, m->p_o);
+            a.raw = c->o_raw;
             a.w_post = p.post_attn_ln;
             a.scalar = 1.0f;
             a.w_norm = p.pre_ff_ln;
@@ -802,9 +804,9 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
         {   // GeGLU + down projection (decode.rs:17-18)
             GemvArgs a{};
             a.W0 = p.wdown;
-            a.raw = spec_of(c->gu_raw, m->p_gateup);
+            a.in = c->gu_raw;
             a.out = c->down_raw;
-            launch_gemv(ln, "down", c, a, m->p_down, PRO_GEGLU, EPI_PARTIAL);
+            launch_gemv(ln, "down", c, a, m->p_down, PRO_PLAIN, EPI_STORE);
         }
     }
     if (kind != STEP_PREFILL) {
@@ -814,7 +816,7 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
         a.W0 = (const char*)m->embed + (size_t)m->v0 * H * m->es;
         a.h_in = c->hA;
         a.h_out = c->hB;
-        a.raw = spec_of(c->down_raw, m->p_down);
+        a.raw = c->down_raw;
         a.w_post = m->layers[L - 1].post_ff_ln;
         a.scalar = m->layers[L - 1].layer_scalar;
         a.w_norm = m->final_norm;
