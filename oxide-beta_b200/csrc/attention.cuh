@@ -44,6 +44,9 @@ struct AttnArgs {
     float* part;             // [B, Nkv, n_splits, G, D + 2]
     unsigned int* ticket;    // [B, Nkv]
     float* out;              // [B, Nq * D]
+    // weights of a later kernel to pull into L2 while this kernel runs (each CTA takes a slice)
+    const void* pf_ptr;
+    unsigned long long pf_bytes;
 };
 
 template <typename KT, int EPT> struct KVec;
@@ -112,6 +115,16 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
     const int s = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int half = D / 2;
 
+    if (tid == 0 && a.pf_bytes) {
+        constexpr unsigned long long PIECE = 32 * 1024;
+        const unsigned long long npieces = (a.pf_bytes + PIECE - 1) / PIECE;
+        const unsigned long long ncta = (unsigned long long)gridDim.x * gridDim.y * gridDim.z;
+        const unsigned long long me = ((unsigned long long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+        for (unsigned long long pi = me; pi < npieces; pi += ncta) {
+            const unsigned long long off = pi * PIECE;
+            prefetch_l2_bulk((const char*)a.pf_ptr + off, (size_t)min(PIECE, a.pf_bytes - off));
+        }
+    }
     pdl_wait();
     pdl_launch();
 

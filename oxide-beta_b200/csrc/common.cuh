@@ -55,6 +55,10 @@ DEVINL uint32_t ldg_stream4(const void* p) {
     return v;
 }
 DEVINL void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+// Bulk L2 prefetch of a contiguous range (address and size multiples of 16 bytes).
+DEVINL void prefetch_l2_bulk(const void* p, size_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"((uint32_t)bytes) : "memory");
+}
 
 // Deterministic block-wide sums of NV values at once. `red` holds NV * 32 floats of shared memory.
 // Every thread returns the same totals (summed in warp order).

@@ -54,6 +54,9 @@ struct GemvArgs {
     const uint32_t* tokens;  // [B]
     float embed_scale;
     float eps;
+    // weights of later kernels to pull into L2 while this kernel runs (each CTA takes a slice)
+    const void* pf_ptr[2];
+    unsigned long long pf_bytes[2];
     // epilogue
     float* out;              // STORE: [B, N]; GATEUP: [B, N/2]; LOGITS: [B, n_total] or null
     const uint8_t* seen;     // LOGITS: [B, n_total] repetition bitmap or null
@@ -165,12 +168,35 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a)
             for (int l = tid; l < nl; l += kGemvThreads) prefetch_l2(p0 + (size_t)l * 128);
         }
     } else {
-        // at most 512 chunks (256 KiB) per CTA; one 128-byte line per thread and step
-        const int cstop = min(chunks_cta, 512);
-        for (int cc = (tid >> 2); cc < cstop; cc += kGemvThreads / 4) {
-            const int r = row_first + cc / a.cpr;
-            const int col = (cc % a.cpr) * STEP + (tid & 3) * (STEP / 4);
-            if (col < K) prefetch_l2((const char*)(row_ptr(r) + col));
+        // this CTA's own block is contiguous in memory (two slabs for gate/up): bulk L2 prefetch
+        if (tid < 8 && rows_cta > 0) {
+            constexpr size_t PIECE = 32 * 1024;
+            const size_t cap = 256 * 1024;
+            if constexpr (EPI == EPI_GATEUP) {
+                const size_t slab = min((size_t)(rows_cta / 2) * row_bytes, cap / 2);
+                const char* g0 = (const char*)a.W0 + (size_t)(row_first / 2) * row_bytes;
+                const char* u0 = (const char*)a.W1 + (size_t)(row_first / 2) * row_bytes;
+                for (size_t off = (size_t)(tid >> 1) * PIECE; off < slab; off += 4 * PIECE)
+                    prefetch_l2_bulk(((tid & 1) ? u0 : g0) + off, min(PIECE, slab - off));
+            } else {
+                const size_t slab = min((size_t)rows_cta * row_bytes, cap);
+                const char* s0 = (const char*)a.W0 + (size_t)row_first * row_bytes;
+                for (size_t off = (size_t)tid * PIECE; off < slab; off += 8 * PIECE)
+                    prefetch_l2_bulk(s0 + off, min(PIECE, slab - off));
+            }
+        }
+    }
+    // slices of later kernels' weights
+    if (tid >= 32 && tid < 34) {
+        const int which = tid - 32;
+        const unsigned long long total = a.pf_bytes[which];
+        if (total) {
+            constexpr unsigned long long PIECE = 32 * 1024;
+            const unsigned long long npieces = (total + PIECE - 1) / PIECE;
+            for (unsigned long long pi = blockIdx.x; pi < npieces; pi += gridDim.x) {
+                const unsigned long long off = pi * PIECE;
+                prefetch_l2_bulk((const char*)a.pf_ptr[which] + off, (size_t)min(PIECE, total - off));
+            }
         }
     }
     // norm weights are model constants: fetch them before waiting on the previous kernel

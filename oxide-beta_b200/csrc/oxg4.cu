@@ -93,6 +93,7 @@ struct oxg4_model {
     cudaStream_t stream = nullptr;
     int num_sms = 148;
     bool use_pdl = true;
+    bool far_prefetch = false;     // pull later kernels' weights into L2 during latency-bound kernels
     bool finalized = false;
     std::map<std::string, Tensor> tensors;
     std::vector<LayerPlan> layers;
@@ -202,6 +203,7 @@ extern "C" int32_t oxg4_model_create(const oxg4_config* c, int32_t device, oxg4_
     m->v0 = m->Vloc * c->tp_rank;
     m->es = esz;
     m->use_pdl = getenv("OXG4_DISABLE_PDL") == nullptr;
+    m->far_prefetch = getenv("OXG4_FAR_PREFETCH") != nullptr;   // measured slower on B200: off by default
     if (cudaSetDevice(device) != cudaSuccess) { delete m; return fail(OXG4_CUDA, "Gemma 4 CUDA error: cudaSetDevice"); }
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, device) == cudaSuccess) m->num_sms = prop.multiProcessorCount;
@@ -750,6 +752,12 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
                 a.scalar = m->layers[l - 1].layer_scalar;
             }
             a.out = c->qkv_raw;
+            if (m->far_prefetch) {
+                a.pf_ptr[0] = p.wo;
+                a.pf_bytes[0] = (unsigned long long)m->p_o.N * m->p_o.K * m->es;
+                a.pf_ptr[1] = p.wgate;
+                a.pf_bytes[1] = (unsigned long long)m->I * H * m->es;
+            }
             launch_gemv(ln, "qkv", c, a, m->p_qkv, PRO_NORM, EPI_STORE);
         }
         {   // q/k norm + RoPE + v norm + KV append + attention (decode.rs:99-157)
@@ -777,6 +785,10 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
             a.part = c->attn_part;
             a.ticket = c->attn_ticket;
             a.out = c->attn_out;
+            if (m->far_prefetch) {
+                a.pf_ptr = p.wup;
+                a.pf_bytes = (unsigned long long)m->I * H * m->es;
+            }
             auto fn = c->kv_dtype == OXG4_BF16 ? pick_attn<uint16_t>(D, m->G) : pick_attn<float>(D, m->G);
             const size_t smem = sizeof(float) * (size_t)(m->G * D + 2 * D + 2 * kAttnWarps * m->G + kAttnWarps * m->G * D);
             ln.go("attn", fn, dim3(a.n_splits, m->Nkv, B), dim3(kAttnThreads), smem, a);
@@ -799,6 +811,10 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
             a.scalar = 1.0f;
             a.w_norm = p.pre_ff_ln;
             a.out = c->gu_raw;
+            if (m->far_prefetch) {
+                a.pf_ptr[0] = p.wdown;
+                a.pf_bytes[0] = (unsigned long long)m->p_down.N * m->p_down.K * m->es;
+            }
             launch_gemv(ln, "gateup", c, a, m->p_gateup, PRO_NORM, EPI_GATEUP);
         }
         {   // GeGLU + down projection (decode.rs:17-18)
@@ -806,6 +822,15 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
             a.W0 = p.wdown;
             a.in = c->gu_raw;
             a.out = c->down_raw;
+            if (m->far_prefetch) {
+                if (l + 1 < L) {
+                    a.pf_ptr[0] = m->layers[l + 1].wqkv;
+                    a.pf_bytes[0] = (unsigned long long)m->p_qkv.N * m->p_qkv.K * m->es;
+                } else if (kind != STEP_PREFILL) {
+                    a.pf_ptr[0] = (const char*)m->embed + (size_t)m->v0 * H * m->es;
+                    a.pf_bytes[0] = std::min<unsigned long long>((unsigned long long)m->Vloc * H * m->es, 64ull << 20);
+                }
+            }
             launch_gemv(ln, "down", c, a, m->p_down, PRO_PLAIN, EPI_STORE);
         }
     }
