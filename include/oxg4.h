@@ -164,6 +164,12 @@ int64_t oxg4_kernel_launches(const oxg4_model* model);
 int32_t oxg4_profile_step(oxg4_model* model, oxg4_cache* cache, const uint32_t* tokens);
 float oxg4_profile_ms(const oxg4_model* model, const char* kind);
 
+/* Diagnostics (no counterpart in the reference): when the environment variable OXG4_TIMELINE is
+ * set before oxg4_model_create, every kernel of a step stamps the GPU's nanosecond timer at entry,
+ * after its dependency wait, after its prologue and at exit. Copies the stamps of the most recent
+ * step, four per kernel in launch order, to `out`. */
+int32_t oxg4_debug_timeline(oxg4_cache* cache, unsigned long long* out, int32_t max_entries);
+
 /* ---- host-side mirror of the generation loop -------------------------------------------------------- */
 
 /* GenerationConfig (models/gemma4/config.rs:7-33). */

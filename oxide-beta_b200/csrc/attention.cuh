@@ -47,6 +47,7 @@ struct AttnArgs {
     // weights of a later kernel to pull into L2 while this kernel runs (each CTA takes a slice)
     const void* pf_ptr;
     unsigned long long pf_bytes;
+    unsigned long long* ts;  // optional timeline slots of this launch (4 entries) or null
 };
 
 template <typename KT, int EPT> struct KVec;
@@ -125,8 +126,19 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
             prefetch_l2_bulk((const char*)a.pf_ptr + off, (size_t)min(PIECE, a.pf_bytes - off));
         }
     }
+    // model constants for this lane's slice of a head: fetched before the dependency wait
+    float wq[EPT], wk[EPT], fr[EPT];
+#pragma unroll
+    for (int e = 0; e < EPT; ++e) {
+        const int d = lane * EPT + e;
+        wq[e] = a.q_norm[d];
+        wk[e] = a.k_norm[d];
+        fr[e] = a.inv_freq[d % (D / 2)];
+    }
+    stamp(a.ts, 0);
     pdl_wait();
     pdl_launch();
+    stamp(a.ts, 1);
 
     const bool active = a.tokens[b] != kInactiveToken;
     const int pos = a.pos[b];
@@ -166,9 +178,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
             const float r = 1.0f / sqrtf(ss / (float)D + a.eps);
             float* dst = task < G ? qs + task * D : (task == G ? kcur : vcur);
             if (task <= G) {
-                const float* w = task < G ? a.q_norm : a.k_norm;
 #pragma unroll
-                for (int e = 0; e < EPT; ++e) dst[lane * EPT + e] = t[e] * r * w[lane * EPT + e];
+                for (int e = 0; e < EPT; ++e) dst[lane * EPT + e] = t[e] * r * (task < G ? wq[e] : wk[e]);
                 __syncwarp();
                 float o[EPT];
 #pragma unroll
@@ -177,7 +188,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
                     const int fi = d % half;
                     float v = dst[d];
                     if (fi < a.rotary_half) {
-                        const float angle = (float)pos * a.inv_freq[fi];
+                        const float angle = (float)pos * fr[e];
                         const float pv = dst[d < half ? d + half : d - half];
                         const float rotated = d < half ? -pv : pv;
                         v = v * cosf(angle) + rotated * sinf(angle);
@@ -205,6 +216,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
             }
         }
         __syncthreads();
+        stamp(a.ts, 2);
 
         float q[G][EPT];
 #pragma unroll
@@ -316,25 +328,46 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
     if (s_last) {
         __threadfence();
         if (active) {
+            // (m, l) of every split -> shared memory, one scale factor per (split, head), then the
+            // weighted sum over splits with independent loads (fixed split order)
+            constexpr int PS = G * (D + 2);
+            float* sf = wacc;                         // [n_eff][G] m, then exp(m - M)
+            float* sl = wacc + a.n_splits * G;        // [n_eff][G] l
+            float* sL = sl + a.n_splits * G;          // [G]
+            for (int idx = tid; idx < n_eff * G; idx += kAttnThreads) {
+                const int sp = idx / G, g = idx % G;
+                sf[idx] = __ldcg(part + (size_t)sp * PS + g * (D + 2) + D);
+                sl[idx] = __ldcg(part + (size_t)sp * PS + g * (D + 2) + D + 1);
+            }
+            __syncthreads();
+            if (warp < G) {
+                const int g = warp;
+                float M = -INFINITY;
+                for (int sp = lane; sp < n_eff; sp += 32) M = fmaxf(M, sf[sp * G + g]);
+                M = warp_max(M);
+                float L = 0.0f;
+                for (int sp = lane; sp < n_eff; sp += 32) {
+                    const float ms = sf[sp * G + g];
+                    const float e = (ms == -INFINITY) ? 0.0f : expf(ms - M);
+                    sf[sp * G + g] = e;
+                    L += e * sl[sp * G + g];
+                }
+                L = warp_sum(L);
+                if (lane == 0) sL[g] = L;
+            }
+            __syncthreads();
             for (int idx = tid; idx < G * D; idx += kAttnThreads) {
                 const int g = idx / D, d = idx % D;
-                float M = -INFINITY;
-                for (int sp = 0; sp < n_eff; ++sp)
-                    M = fmaxf(M, __ldcg(part + (size_t)sp * (G * (D + 2)) + g * (D + 2) + D));
-                float A = 0.0f, L = 0.0f;
-                for (int sp = 0; sp < n_eff; ++sp) {
-                    const float* ps = part + (size_t)sp * (G * (D + 2)) + g * (D + 2);
-                    const float ms = __ldcg(ps + D);
-                    if (ms == -INFINITY) continue;
-                    const float e = expf(ms - M);
-                    A += e * __ldcg(ps + d);
-                    L += e * __ldcg(ps + D + 1);
-                }
-                a.out[(size_t)b * a.Nq * D + (size_t)(kvh * G + g) * D + d] = A / L;
+                const float* ps = part + g * (D + 2) + d;
+                float A = 0.0f;
+#pragma unroll 8
+                for (int sp = 0; sp < n_eff; ++sp) A += sf[sp * G + g] * __ldcg(ps + (size_t)sp * PS);
+                a.out[(size_t)b * a.Nq * D + (size_t)(kvh * G + g) * D + d] = A / sL[g];
             }
         }
         if (tid == 0) a.ticket[b * a.Nkv + kvh] = 0u;
     }
+    stamp(a.ts, 3);
 }
 
 template <int D, int G>

@@ -55,6 +55,14 @@ DEVINL uint32_t ldg_stream4(const void* p) {
     return v;
 }
 DEVINL void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+// Optional device timeline: block (0,0,0) thread 0 stores the global nanosecond timer.
+DEVINL void stamp(unsigned long long* ts, int slot) {
+    if (ts != nullptr && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        ts[slot] = t;
+    }
+}
 // Bulk L2 prefetch of a contiguous range (address and size multiples of 16 bytes).
 DEVINL void prefetch_l2_bulk(const void* p, size_t bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"((uint32_t)bytes) : "memory");

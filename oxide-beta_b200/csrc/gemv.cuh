@@ -41,6 +41,7 @@ struct GemvArgs {
     int cpr;                 // 512-byte chunks per row
     int slots;               // most pieces a row is cut into inside one CTA
     int B;                   // activation rows in the step
+    int bpp;                 // activation rows per pass (tensor-core kernel: grid.y = ceil(B / bpp))
     // PRO_PLAIN
     const float* in;         // [B, K]
     // PRO_NORM (K == hidden size)
@@ -57,6 +58,7 @@ struct GemvArgs {
     // weights of later kernels to pull into L2 while this kernel runs (each CTA takes a slice)
     const void* pf_ptr[2];
     unsigned long long pf_bytes[2];
+    unsigned long long* ts;  // optional timeline slots of this launch (4 entries) or null
     // epilogue
     float* out;              // STORE: [B, N]; GATEUP: [B, N/2]; LOGITS: [B, n_total] or null
     const uint8_t* seen;     // LOGITS: [B, n_total] repetition bitmap or null
@@ -209,7 +211,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a)
             wpost[j] = (i < K && a.w_post) ? a.w_post[i] : 0.0f;
         }
     }
+    stamp(a.ts, 0);
     pdl_wait();
+    stamp(a.ts, 1);
 
     // ---- prologue: build x[nb][K] in shared memory ----
     if constexpr (PRO == PRO_PLAIN) {
@@ -268,6 +272,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a)
         for (int i = tid; i < K; i += kGemvThreads) xs[(size_t)b * K + i] = (XT)0;
     __syncthreads();
     pdl_launch();
+    stamp(a.ts, 2);
 
     if constexpr (EPI != EPI_LOGITS) {
         // ---- body: this warp's contiguous run of the CTA's chunks, cut at row boundaries ----
@@ -447,6 +452,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a)
             if (tid == 0) a.ticket[blockIdx.y] = 0u;       // ready for the next launch / replay
         }
     }
+    stamp(a.ts, 3);
 }
 
 }  // namespace oxg4

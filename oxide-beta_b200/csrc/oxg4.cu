@@ -21,6 +21,7 @@
 #include "../../include/oxg4.h"
 #include "attention.cuh"
 #include "gemv.cuh"
+#include "gemv_mma.cuh"
 #include "sampling.cuh"
 
 using namespace oxg4;
@@ -93,7 +94,8 @@ struct oxg4_model {
     cudaStream_t stream = nullptr;
     int num_sms = 148;
     bool use_pdl = true;
-    bool far_prefetch = false;     // pull later kernels' weights into L2 during latency-bound kernels
+    bool far_prefetch = false;
+    bool timeline = false;        // OXG4_TIMELINE: kernels stamp the global timer into the cache's buffer     // pull later kernels' weights into L2 during latency-bound kernels
     bool finalized = false;
     std::map<std::string, Tensor> tensors;
     std::vector<LayerPlan> layers;
@@ -103,6 +105,7 @@ struct oxg4_model {
     int H = 0, D = 0, Nq = 0, Nkv = 0, I = 0, V = 0, Vloc = 0, v0 = 0, G = 0;
     int es = 2;               // bytes per weight element
     GemvPlan p_qkv, p_o, p_gateup, p_down, p_lm;
+    int p_lm_simt_grid = 1;    // the SIMT logits kernel deals row pairs to warps across the grid
     long long launches = 0;
     std::map<std::string, ProfileSlot> profile;
     bool profiling = false;
@@ -203,6 +206,7 @@ extern "C" int32_t oxg4_model_create(const oxg4_config* c, int32_t device, oxg4_
     m->v0 = m->Vloc * c->tp_rank;
     m->es = esz;
     m->use_pdl = getenv("OXG4_DISABLE_PDL") == nullptr;
+    m->timeline = getenv("OXG4_TIMELINE") != nullptr;
     m->far_prefetch = getenv("OXG4_FAR_PREFETCH") != nullptr;   // measured slower on B200: off by default
     if (cudaSetDevice(device) != cudaSuccess) { delete m; return fail(OXG4_CUDA, "Gemma 4 CUDA error: cudaSetDevice"); }
     cudaDeviceProp prop;
@@ -315,6 +319,15 @@ static int32_t set_gemv_attrs() {
     return OXG4_OK;
 }
 
+template <int MB>
+static int32_t set_mma_attrs() {
+    TRY(allow_big_smem(gemv_mma_kernel<MB, PRO_NORM, EPI_STORE>));
+    TRY(allow_big_smem(gemv_mma_kernel<MB, PRO_PLAIN, EPI_STORE>));
+    TRY(allow_big_smem(gemv_mma_kernel<MB, PRO_NORM, EPI_GATEUP>));
+    TRY(allow_big_smem(gemv_mma_kernel<MB, PRO_NORM, EPI_LOGITS>));
+    return OXG4_OK;
+}
+
 template <typename KT, int D>
 static int32_t set_attn_attrs() {
     TRY(allow_big_smem(attn_decode_kernel<KT, D, 1>));
@@ -391,9 +404,11 @@ extern "C" int32_t oxg4_model_finalize(oxg4_model* m) {
     m->p_gateup = make_plan(2 * m->I, H, m->es, m->num_sms, 2);
     m->p_down = make_plan(H, m->I, m->es, m->num_sms, 1);
     m->p_lm = make_plan(m->Vloc, H, m->es, m->num_sms, 1);
-    m->p_lm.grid = std::min(m->num_sms, std::max(1, (m->Vloc + 2 * kGemvWarps - 1) / (2 * kGemvWarps)));
+    m->p_lm_simt_grid = std::min(m->num_sms, std::max(1, (m->Vloc + 2 * kGemvWarps - 1) / (2 * kGemvWarps)));
     if (m->es == 2) {
-        TRY((set_gemv_attrs<uint16_t, 1>())); TRY((set_gemv_attrs<uint16_t, 2>())); TRY((set_gemv_attrs<uint16_t, 4>()));
+        TRY((set_gemv_attrs<uint16_t, 1>()));
+        TRY((set_mma_attrs<8>()));
+        TRY((set_mma_attrs<16>()));
     } else {
         TRY((set_gemv_attrs<float, 1>())); TRY((set_gemv_attrs<float, 2>())); TRY((set_gemv_attrs<float, 4>()));
     }
@@ -462,7 +477,9 @@ struct oxg4_cache {
     std::map<std::string, GraphEntry> graphs;
     std::vector<void*> owned;                 // every device allocation, for destroy
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    unsigned long long* ts_buf = nullptr;     // [kMaxTimeline][4] optional device timeline
 };
+constexpr int kMaxTimeline = 1024;
 
 template <typename T>
 static int32_t dalloc(oxg4_cache* c, T** p, size_t count, bool zero = true) {
@@ -519,7 +536,7 @@ static int32_t cache_build(oxg4_cache* c) {
     // split-KV geometry: enough CTAs to fill the GPU a few times over at the longest context
     const int pairs = std::max(1, m->Nkv * B);
     const int want = std::max(1, (8 * m->num_sms + pairs - 1) / pairs);
-    c->min_split = 32;
+    c->min_split = 16;
     c->splits_full = std::max(1, std::min({want, 64, (maxf + c->min_split - 1) / c->min_split}));
     c->splits_slide = std::max(1, std::min({want, 64, (maxs + c->min_split - 1) / c->min_split}));
     const int smax = std::max(c->splits_full, c->splits_slide);
@@ -537,7 +554,7 @@ static int32_t cache_build(oxg4_cache* c) {
     TRY(dalloc(c, &c->logits, (size_t)B * m->V));
     TRY(dalloc(c, &c->attn_part, (size_t)B * m->Nkv * smax * m->G * (D + 2)));
     TRY(dalloc(c, &c->attn_ticket, (size_t)B * m->Nkv));
-    TRY(dalloc(c, &c->lm_ticket, (size_t)(B + 3) / 4 + 1));
+    TRY(dalloc(c, &c->lm_ticket, (size_t)B + 1));
     TRY(dalloc(c, &c->blk_best, (size_t)B * m->num_sms));
     const int chunks = (m->V + kTopkChunk - 1) / kTopkChunk;
     TRY(dalloc(c, &c->topk_stage, (size_t)B * chunks * 64));
@@ -545,6 +562,7 @@ static int32_t cache_build(oxg4_cache* c) {
     TRY(dalloc(c, &c->best_scores, B));
     TRY(dalloc(c, &c->topk_ids, (size_t)B * 64));
     TRY(dalloc(c, &c->topk_scores, (size_t)B * 64));
+    if (m->timeline) TRY(dalloc(c, &c->ts_buf, (size_t)kMaxTimeline * 4));
     CK(cudaMallocHost(&c->h_tokens, sizeof(uint32_t) * B));
     CK(cudaMallocHost(&c->h_ctl, sizeof(StepCtl)));
     CK(cudaMallocHost(&c->h_ids, sizeof(uint32_t) * B * 64));
@@ -635,7 +653,9 @@ extern "C" int32_t oxg4_cache_reset(oxg4_cache* c) {
 // ------------------------------------------------------------------------------------------------
 struct Launcher {
     oxg4_model* m;
+    unsigned long long* ts_base = nullptr;
     int kernels = 0;
+    unsigned long long* ts() const { return (ts_base && kernels < kMaxTimeline) ? ts_base + (size_t)kernels * 4 : nullptr; }
     int32_t status = OXG4_OK;
 
     template <typename... KArgs, typename... Args>
@@ -678,37 +698,66 @@ static void (*pick_gemv(int nb, int pro, int epi))(const GemvArgs) {
     if (pro == PRO_NORM && epi == EPI_GATEUP) return gemv_kernel<WT, NB, PRO_NORM, EPI_GATEUP>;     \
     if (pro == PRO_NORM && epi == EPI_LOGITS) return gemv_kernel<WT, NB, PRO_NORM, EPI_LOGITS>;
     if (nb == 1) { PICK(1) }
-    if (nb == 2) { PICK(2) }
-    if (nb == 4) { PICK(4) }
+    if constexpr (sizeof(WT) == 4) {      // BF16 weights with more than one row use the tensor-core kernel
+        if (nb == 2) { PICK(2) }
+        if (nb == 4) { PICK(4) }
+    }
 #undef PICK
+    return nullptr;
+}
+
+template <int MB>
+static void (*pick_mma(int pro, int epi))(const GemvArgs) {
+    if (pro == PRO_NORM && epi == EPI_STORE) return gemv_mma_kernel<MB, PRO_NORM, EPI_STORE>;
+    if (pro == PRO_PLAIN && epi == EPI_STORE) return gemv_mma_kernel<MB, PRO_PLAIN, EPI_STORE>;
+    if (pro == PRO_NORM && epi == EPI_GATEUP) return gemv_mma_kernel<MB, PRO_NORM, EPI_GATEUP>;
+    if (pro == PRO_NORM && epi == EPI_LOGITS) return gemv_mma_kernel<MB, PRO_NORM, EPI_LOGITS>;
     return nullptr;
 }
 
 static void launch_gemv(Launcher& ln, const char* kind, oxg4_cache* c, GemvArgs a, const GemvPlan& p, int pro, int epi) {
     oxg4_model* m = c->m;
     const int B = c->B;
-    const int nb = B >= 3 ? 4 : B;
     a.N = p.N;
     a.K = p.K;
     a.cpr = p.cpr;
     a.slots = p.slots;
     a.B = B;
     a.eps = m->cfg.rms_norm_eps;
-    const size_t xes = m->es == 2 ? 2 : 4;
-    size_t smem = (size_t)nb * p.K * xes + (size_t)nb * 32 * 4;
-    size_t extra = (size_t)p.rows_max * p.slots * nb * 4;
-    extra = std::max(extra, (size_t)nb * kGemvWarps * sizeof(Cand));
+    a.ts = ln.ts();
     if (pro == PRO_NORM && p.K > kGemvMaxJ * kGemvThreads) {
         ln.status = fail(OXG4_UNSUPPORTED, "hidden size above %d is not supported", kGemvMaxJ * kGemvThreads);
         return;
     }
+    const size_t limit = 226 * 1024;
+    if (m->es == 2 && B > 1) {
+        // tensor-core kernel: as many activation rows per pass as shared memory allows (at most 16)
+        auto need = [&](int nb) { return (((size_t)nb * p.K * 2 + 15) & ~(size_t)15) + 128 + (size_t)2 * kMmaRowsPerPass * kGemvWarps * nb * 4; };
+        int bpp = std::min(B, 16);
+        while (bpp > 1 && need(bpp) > limit) --bpp;
+        if (need(bpp) > limit) {
+            ln.status = fail(OXG4_UNSUPPORTED, "projection %s needs %zu bytes of shared memory", kind, need(bpp));
+            return;
+        }
+        a.bpp = bpp;
+        auto fn = bpp <= 8 ? pick_mma<8>(pro, epi) : pick_mma<16>(pro, epi);
+        dim3 grid(p.grid, (B + bpp - 1) / bpp, 1);
+        ln.go(kind, fn, grid, dim3(kGemvThreads), need(bpp), a);
+        return;
+    }
+    // one activation row with BF16 weights, or f32 weights: SIMT kernel
+    const int nb = B >= 3 ? 4 : B;
+    a.bpp = nb;
+    size_t smem = (size_t)nb * p.K * m->es + (size_t)nb * 32 * 4;
+    size_t extra = (size_t)p.rows_max * p.slots * nb * 4;
+    extra = std::max(extra, (size_t)nb * kGemvWarps * sizeof(Cand));
     smem += extra;
-    if (smem > 226 * 1024) {
+    if (smem > limit) {
         ln.status = fail(OXG4_UNSUPPORTED, "projection %s needs %zu bytes of shared memory", kind, smem);
         return;
     }
     auto fn = m->es == 2 ? pick_gemv<uint16_t>(nb, pro, epi) : pick_gemv<float>(nb, pro, epi);
-    dim3 grid(p.grid, (B + nb - 1) / nb, 1);
+    dim3 grid(epi == EPI_LOGITS ? m->p_lm_simt_grid : p.grid, (B + nb - 1) / nb, 1);
     ln.go(kind, fn, grid, dim3(kGemvThreads), smem, a);
 }
 
@@ -730,6 +779,7 @@ static void (*pick_attn(int D, int G))(const AttnArgs) {
 static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* n_kernels) {
     oxg4_model* m = c->m;
     Launcher ln{m};
+    ln.ts_base = c->ts_buf;
     const int B = c->B, L = m->cfg.num_hidden_layers, H = m->H, D = m->D;
     ln.go("step_begin", step_begin_kernel, dim3(1), dim3(128), 0, B, m->V,
           (const uint32_t*)c->tokens, c->seen, (const StepCtl*)c->ctl);
@@ -789,6 +839,7 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
                 a.pf_ptr = p.wup;
                 a.pf_bytes = (unsigned long long)m->I * H * m->es;
             }
+            a.ts = ln.ts();
             auto fn = c->kv_dtype == OXG4_BF16 ? pick_attn<uint16_t>(D, m->G) : pick_attn<float>(D, m->G);
             const size_t smem = sizeof(float) * (size_t)(m->G * D + 2 * D + 2 * kAttnWarps * m->G + kAttnWarps * m->G * D);
             ln.go("attn", fn, dim3(a.n_splits, m->Nkv, B), dim3(kAttnThreads), smem, a);
@@ -1067,6 +1118,15 @@ extern "C" int32_t oxg4_profile_step(oxg4_model* m, oxg4_cache* c, const uint32_
     }
     m->prof_events.clear();
     advance_host(c, tokens);
+    return OXG4_OK;
+}
+
+extern "C" int32_t oxg4_debug_timeline(oxg4_cache* c, unsigned long long* out, int32_t max_entries) {
+    if (!c || !out) return fail(OXG4_INVALID_ARGUMENT, "null argument");
+    if (!c->ts_buf) return fail(OXG4_UNSUPPORTED, "timeline recording is off (set OXG4_TIMELINE before creating the model)");
+    TRY(bind_device(c->m));
+    const int n = std::min(max_entries, kMaxTimeline * 4);
+    CK(cudaMemcpy(out, c->ts_buf, sizeof(unsigned long long) * n, cudaMemcpyDeviceToHost));
     return OXG4_OK;
 }
 
