@@ -414,6 +414,7 @@ extern "C" int32_t oxg4_model_finalize(oxg4_model* m) {
     }
     TRY((set_attn_attrs<uint16_t, 64>())); TRY((set_attn_attrs<uint16_t, 128>())); TRY((set_attn_attrs<uint16_t, 256>()));
     TRY((set_attn_attrs<float, 64>())); TRY((set_attn_attrs<float, 128>())); TRY((set_attn_attrs<float, 256>()));
+    TRY(allow_big_smem(topk_stage2_kernel));
     CK(cudaDeviceSynchronize());
     m->finalized = true;
     return OXG4_OK;

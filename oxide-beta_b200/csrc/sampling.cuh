@@ -89,7 +89,7 @@ topk_stage1_kernel(const float* logits, int V, const uint8_t* seen, float penalt
     const int n = min(kTopkChunk, V - start);
     for (int i = threadIdx.x; i < n; i += kTopkThreads) {
         float s = logits[(size_t)b * V + start + i];
-        if (seen[(size_t)b * V + start + i] != 0 && penalty > 1.0f) s = s >= 0.0f ? s / penalty : s * penalty;
+        if (seen != nullptr && penalty > 1.0f && seen[(size_t)b * V + start + i] != 0) s = s >= 0.0f ? s / penalty : s * penalty;
         sc[i] = (s == s) ? s : -INFINITY;         // NaN is never selected
         id[i] = (uint32_t)(start + i);
     }
