@@ -239,7 +239,8 @@ void gqa_decode_ring(const float* q, const LayerCache& c, int heads, int window,
 }
 
 // decode.rs:43-174 + 4-21 + 353-369; one token through every layer. Returns hidden state.
-void forward_token(const Model& m, Cache& cache, uint32_t token, std::vector<float>& hidden) {
+void forward_token(const Model& m, Cache& cache, uint32_t token, std::vector<float>& hidden,
+                   const float* inject = nullptr, float* trace = nullptr) {
     const Config& c = m.c;
     const bool bf = c.mode == 1;
     const int H = c.hidden;
@@ -257,6 +258,9 @@ void forward_token(const Model& m, Cache& cache, uint32_t token, std::vector<flo
         const LayerW& w = m.L[l];
         LayerCache& lc = cache.L[l];
         const int D = w.head_dim;
+        // layer-wise teacher forcing for tests: replace / record the layer's input hidden state
+        if (inject) std::memcpy(hidden.data(), inject + (size_t)l * H, sizeof(float) * H);
+        if (trace) std::memcpy(trace + (size_t)l * H, hidden.data(), sizeof(float) * H);
         const int QW = c.heads * D, KW = c.kv_heads * D;
         // attention block
         rms_norm_rows(hidden.data(), w.input_ln.v.data(), x.data(), 1, H, c.eps, bf);
@@ -305,6 +309,7 @@ void forward_token(const Model& m, Cache& cache, uint32_t token, std::vector<flo
         // layer_scalar (tensor_ops.rs:244-267)
         for (int i = 0; i < H; ++i) hidden[i] = hidden[i] * w.layer_scalar;
     }
+    if (trace) std::memcpy(trace + (size_t)c.layers * H, hidden.data(), sizeof(float) * H);
     cache.position += 1;
 }
 
@@ -731,6 +736,19 @@ int64_t orc_generate(void* model, const uint32_t* prompt, int64_t n_prompt, cons
     }
     orc_cache_destroy(c);
     return n_gen;
+}
+
+// One token with layer-wise teacher forcing (test aid, no counterpart in the reference):
+// inject_or_null [layers, hidden] replaces the input of every layer; trace_or_null
+// [layers + 1, hidden] receives the input of every layer and the final hidden state.
+int orc_decode_trace(void* model, void* cache, uint32_t token, const float* inject_or_null,
+                     float* trace_or_null, float* logits_or_null) {
+    Model* m = (Model*)model;
+    if ((int64_t)token >= m->c.vocab) return -1;
+    std::vector<float> hidden;
+    forward_token(*m, *(Cache*)cache, token, hidden, inject_or_null, trace_or_null);
+    if (logits_or_null) lm_head(*m, hidden, logits_or_null);
+    return 0;
 }
 
 int orc_num_threads(void) {

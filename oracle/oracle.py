@@ -264,6 +264,20 @@ class OracleCache:
             raise ValueError("token id exceeds vocabulary")
         return logits
 
+    def decode_trace(self, token: int, inject=None, want_logits=True):
+        """One token; returns (trace [layers + 1, hidden], logits). `inject` [layers, hidden] replaces
+        the input hidden state of every layer (layer-wise teacher forcing)."""
+        cfg = self.model.cfg
+        L, H = cfg["num_hidden_layers"], cfg["hidden_size"]
+        trace = np.empty((L + 1, H), dtype=np.float32)
+        logits = np.empty(cfg["vocab_size"], dtype=np.float32) if want_logits else None
+        inj = None if inject is None else np.ascontiguousarray(inject, dtype=np.float32)
+        rc = lib().orc_decode_trace(self.model._h, self._h, C.c_uint32(token), None if inj is None else _fp(inj),
+                                    _fp(trace), None if logits is None else _fp(logits))
+        if rc != 0:
+            raise ValueError("token id exceeds vocabulary")
+        return trace, logits
+
     def decode_topk(self, token: int, top_k=1, penalty=1.0, mark_seen=True, want_logits=False):
         ids = np.zeros(64, dtype=np.uint32)
         scores = np.zeros(64, dtype=np.float32)
