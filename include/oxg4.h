@@ -164,6 +164,29 @@ int64_t oxg4_kernel_launches(const oxg4_model* model);
 int32_t oxg4_profile_step(oxg4_model* model, oxg4_cache* cache, const uint32_t* tokens);
 float oxg4_profile_ms(const oxg4_model* model, const char* kind);
 
+/* Top-k selection that allocates nothing (no counterpart in the reference). It is meant for callers
+ * that are not allowed to allocate device memory at the moment they need a top-k: code running
+ * between cudaStreamBeginCapture and cudaStreamEndCapture on a stream, where cudaMalloc is illegal;
+ * serving loops with a fixed memory budget that forbid allocation after start-up; and hosts that own
+ * every byte of device memory through their own arena. The usual path (oxg4_decode_topk) keeps its
+ * candidate lists in buffers that oxg4_cache_create allocates; this variant runs the same two
+ * kernels with the candidate lists in a fixed 512 KiB array inside the library image, so it calls
+ * no cudaMalloc, cudaFree or any other allocating routine.
+ *   logits_dev  [rows, vocab] f32, DEVICE pointer        seen_dev  [rows, vocab] bytes or NULL (DEVICE)
+ *   ids_dev     [rows, top_k] u32, DEVICE pointer        scores_dev [rows, top_k] f32, DEVICE pointer
+ *   cuda_stream a cudaStream_t (NULL = the default stream); the call only enqueues work on it.
+ * Limits: rows <= 4 and vocab <= 524288 per call (larger sizes are rejected with
+ * OXG4_INVALID_SHAPE); top_k is clamped to 1..=64 as in oxg4_decode_topk. Result order, tie-break,
+ * penalty and NaN handling are those of oxg4_decode_topk.
+ * The array is shared by every call on a device and keeps the previous call's contents. Nothing in
+ * it has to start at zero (each call overwrites every entry it later reads), but two calls whose
+ * kernels overlap on the GPU (different streams, no ordering between them) race on it: order them.
+ * The first call on each device looks up the array's device address and configures the merge
+ * kernel; make that first call before any stream capture begins. */
+int32_t oxg4_topk_noalloc(const float* logits_dev, int32_t rows, int32_t vocab, const uint8_t* seen_dev,
+                          float repetition_penalty, int32_t top_k, uint32_t* ids_dev, float* scores_dev,
+                          void* cuda_stream);
+
 /* Diagnostics (no counterpart in the reference): when the environment variable OXG4_TIMELINE is
  * set before oxg4_model_create, every kernel of a step stamps the GPU's nanosecond timer at entry,
  * after its dependency wait, after its prologue and at exit. Copies the stamps of the most recent

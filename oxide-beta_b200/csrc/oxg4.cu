@@ -1318,3 +1318,53 @@ extern "C" int32_t oxg4_generate(oxg4_model* m, const uint32_t* prompt, int64_t 
     *n_out = n_prompt + (int64_t)generated.size();
     return OXG4_OK;
 }
+
+// ------------------------------------------------------------------------------------------------
+// top-k without any allocation
+// ------------------------------------------------------------------------------------------------
+// Scratch of oxg4_topk_noalloc: the per-chunk candidate lists that the first top-k stage hands to the
+// second. It is part of the library image, so every GPU that loads the library holds these 512 KiB
+// until the process exits. All calls on a device share it.
+constexpr int kNoAllocMaxRows = 4;
+constexpr int kNoAllocMaxVocab = 524288;
+constexpr int kNoAllocMaxChunks = kNoAllocMaxVocab / kTopkChunk;
+static __device__ __align__(256) Cand g_noalloc_topk_scratch[kNoAllocMaxRows * kNoAllocMaxChunks * 64];
+
+// g_noalloc_topk_scratch is a host-side stand-in in host code, not a device address; the device address
+// is looked up once per device with that device current.
+static Cand* g_noalloc_scratch_addr[64] = {};
+
+extern "C" int32_t oxg4_topk_noalloc(const float* logits_dev, int32_t rows, int32_t vocab,
+                                     const uint8_t* seen_dev, float repetition_penalty, int32_t top_k,
+                                     uint32_t* ids_dev, float* scores_dev, void* cuda_stream) {
+    if (!logits_dev || !ids_dev || !scores_dev) return fail(OXG4_INVALID_ARGUMENT, "null argument");
+    if (rows < 1 || rows > kNoAllocMaxRows)
+        return fail(OXG4_INVALID_SHAPE, "oxg4_topk_noalloc handles 1..%d rows per call, got %d", kNoAllocMaxRows, rows);
+    if (vocab < 1 || vocab > kNoAllocMaxVocab)
+        return fail(OXG4_INVALID_SHAPE, "oxg4_topk_noalloc handles a vocabulary of at most %d, got %d", kNoAllocMaxVocab, vocab);
+    top_k = std::min(std::max(top_k, 1), 64);
+    top_k = std::min(top_k, vocab);
+    int dev = 0;
+    CK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(OXG4_UNSUPPORTED, "device ordinal %d out of range", dev);
+    if (g_noalloc_scratch_addr[dev] == nullptr) {
+        // first call on this device: resolve the array's device address and opt the merge kernel in to
+        // its shared-memory size. Neither call allocates; both should happen outside stream capture.
+        Cand* p = nullptr;
+        CK(cudaGetSymbolAddress((void**)&p, g_noalloc_topk_scratch));
+        TRY(allow_big_smem(topk_stage2_kernel));
+        g_noalloc_scratch_addr[dev] = p;
+    }
+    Cand* scratch = g_noalloc_scratch_addr[dev];
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    const int chunks = (vocab + kTopkChunk - 1) / kTopkChunk;
+    // every scratch entry the merge reads is written by the first stage of the same call, so nothing
+    // has to be cleared between calls
+    topk_stage1_kernel<<<dim3(chunks, rows), kTopkThreads, 0, st>>>(logits_dev, vocab, seen_dev, repetition_penalty,
+                                                                    top_k, scratch);
+    CK(cudaGetLastError());
+    topk_stage2_kernel<<<dim3(1, rows), kTopkThreads, (size_t)chunks * top_k * 8, st>>>(scratch, chunks * top_k, top_k,
+                                                                                        ids_dev, scores_dev);
+    CK(cudaGetLastError());
+    return OXG4_OK;
+}
