@@ -202,15 +202,22 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
+    # the 12B / 27B workloads are tensor-parallel across the ranks; the smaller ones run one replica per GPU
+    tp = world if (world > 1 and args.workload in ("c4", "c5")) else 1
     t_load = time.perf_counter()
-    state = pkg.Gemma4CudaState(pkg.Gemma4TextConfig(cfg), local_rank, pkg.BF16)
+    state = pkg.Gemma4CudaState(pkg.Gemma4TextConfig(cfg), local_rank, pkg.BF16, tp_rank=rank if tp > 1 else 0,
+                                tp_size=tp)
     host_weights = []
-    keep_host = (rank == 0 and world == 1 and not args.no_cpu_baseline)
+    keep_host = (rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload in ("c1", "c2", "c3"))
     for name, a in torch_weights(cfg, f"cuda:{local_rank}"):
         state.upload(name, a)
         if keep_host:
             host_weights.append((name, a))
     state.finalize()
+    if tp > 1:
+        ids = [pkg.Gemma4CudaState.tp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        state.tp_init(ids[0])
     torch.cuda.empty_cache()
     load_s = time.perf_counter() - t_load
 
@@ -257,8 +264,9 @@ def main():
         t = torch.tensor([ms_step, e2e_s], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_step, e2e_s = float(t[0]), float(t[1])
-    value = world * B * 1000.0 / ms_step
-    e2e_value = world * B * e2e_steps / e2e_s
+    replicas = world // tp
+    value = replicas * B * 1000.0 / ms_step
+    e2e_value = replicas * B * e2e_steps / e2e_s
 
     # dominant-kernel timing: eager steps with CUDA events around every launch
     contexts = [table.position(b) for b in range(B)]
@@ -288,13 +296,14 @@ def main():
         return
     out = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
-        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if tp > 1 else "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
         "config": {"workload": args.workload + (f" (reduced: layers={args.layers} vocab={args.vocab})"
                                                  if (args.layers or args.vocab) else ""),
                    "batch": B, "prompt": lens[0] if len(set(lens)) == 1 else "ragged",
                    "context_at_timing": contexts[0], "kv_dtype": "bf16", "page_tokens": 256,
-                   "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
+                   "parallelism": "single GPU" if world == 1 else (f"tp{tp} (NCCL all-reduce after O and down)"
+                                                                   if tp > 1 else f"{world} independent replicas"),
                    "l2": "per-step inputs (weights + KV) exceed the 126 MB L2; no flush",
                    "load_s": round(load_s, 2), "prefill_s": round(prefill_s, 2)},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * B + 16, "d2h_bytes_per_step": 8 * B,

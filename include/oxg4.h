@@ -107,6 +107,11 @@ int32_t oxg4_synchronize(oxg4_model* model);
  * its model with the same tp_size and its own tp_rank; rank 0 obtains an id, the host program
  * distributes the 128 bytes to the other ranks, and all ranks call oxg4_model_tp_init. */
 int32_t oxg4_tp_unique_id(void* out_128_bytes);
+/* The sub-matrix of checkpoint tensor `name` ([rows, cols]) that rank tp_rank of tp_size keeps:
+ * out4 = {first row, rows kept, first column, columns kept}. Pure host arithmetic. q/k/v, gate and up
+ * are split by rows (whole heads / intermediate columns), o and down by columns, the rest replicated. */
+int32_t oxg4_tp_shard(const char* name, int64_t rows, int64_t cols, int32_t tp_rank, int32_t tp_size,
+                      int32_t heads, int32_t kv_heads, int32_t head_dim, int32_t intermediate, int64_t* out4);
 int32_t oxg4_model_tp_init(oxg4_model* model, const void* unique_id_128_bytes);
 
 /* ---- KV cache: new_cache_table (gemma4_cuda/cache.rs:31-95) -------------------------------------- */

@@ -7,8 +7,8 @@ from the repository root.
 from . import _native, synthetic
 from ._native import BF16, F32, INACTIVE, Oxg4Error, library_path
 from .gemma4 import (Device, Gemma4CudaCacheTable, Gemma4CudaState, Gemma4ForCausalLM, Gemma4TextConfig,
-                     GenerationConfig, sample_token, sample_topk_candidates)
+                     GenerationConfig, sample_token, sample_topk_candidates, tp_shard)
 
 __all__ = ["BF16", "F32", "INACTIVE", "Oxg4Error", "Device", "Gemma4CudaCacheTable", "Gemma4CudaState",
            "Gemma4ForCausalLM", "Gemma4TextConfig", "GenerationConfig", "sample_token",
-           "sample_topk_candidates", "synthetic", "library_path"]
+           "sample_topk_candidates", "synthetic", "library_path", "tp_shard"]

@@ -55,6 +55,8 @@ SYMBOLS = {
     "oxg4_weight_bytes": (C.c_int64, [C.c_void_p]),
     "oxg4_synchronize": (C.c_int32, [C.c_void_p]),
     "oxg4_tp_unique_id": (C.c_int32, [C.c_void_p]),
+    "oxg4_tp_shard": (C.c_int32, [C.c_char_p, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                  C.c_int32, C.POINTER(C.c_int64)]),
     "oxg4_model_tp_init": (C.c_int32, [C.c_void_p, C.c_void_p]),
     "oxg4_cache_create": (C.c_int32, [C.c_void_p, C.c_int32, C.POINTER(C.c_int32), C.c_int32, C.c_int32,
                                       C.POINTER(C.c_void_p)]),

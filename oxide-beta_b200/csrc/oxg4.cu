@@ -23,6 +23,7 @@
 #include "gemv.cuh"
 #include "gemv_mma.cuh"
 #include "sampling.cuh"
+#include "tp.h"
 
 using namespace oxg4;
 
@@ -107,6 +108,8 @@ struct oxg4_model {
     GemvPlan p_qkv, p_o, p_gateup, p_down, p_lm;
     int p_lm_simt_grid = 1;    // the SIMT logits kernel deals row pairs to warps across the grid
     long long launches = 0;
+    int tp = 1, tp_rank = 0;
+    void* comm = nullptr;         // ncclComm_t once oxg4_model_tp_init has run
     std::map<std::string, ProfileSlot> profile;
     bool profiling = false;
     std::vector<std::pair<std::string, std::pair<cudaEvent_t, cudaEvent_t>>> prof_events;
@@ -167,7 +170,8 @@ extern "C" int32_t oxg4_model_create(const oxg4_config* c, int32_t device, oxg4_
     if (c->head_dim != 64 && c->head_dim != 128 && c->head_dim != 256)
         return fail(OXG4_UNSUPPORTED, "head_dim must be 64, 128 or 256");
     const int tp = c->tp_size <= 0 ? 1 : c->tp_size;
-    if (tp != 1) return fail(OXG4_UNSUPPORTED, "tensor parallelism is not available in this build");
+    if (tp != 1 && tp != 2 && tp != 4 && tp != 8) return fail(OXG4_INVALID_ARGUMENT, "tp_size must be 1, 2, 4 or 8");
+    if (c->tp_rank < 0 || c->tp_rank >= tp) return fail(OXG4_INVALID_ARGUMENT, "tp_rank out of range");
     if (c->num_key_value_heads % tp != 0 || c->intermediate_size % tp != 0 || c->vocab_size % tp != 0)
         return fail(OXG4_INVALID_SHAPE, "tp_size must divide kv heads, intermediate size and vocabulary");
     const int g = c->num_attention_heads / c->num_key_value_heads;
@@ -205,6 +209,8 @@ extern "C" int32_t oxg4_model_create(const oxg4_config* c, int32_t device, oxg4_
     m->Vloc = c->vocab_size / tp;
     m->v0 = m->Vloc * c->tp_rank;
     m->es = esz;
+    m->tp = tp;
+    m->tp_rank = c->tp_rank;
     m->use_pdl = getenv("OXG4_DISABLE_PDL") == nullptr;
     m->timeline = getenv("OXG4_TIMELINE") != nullptr;
     m->far_prefetch = getenv("OXG4_FAR_PREFETCH") != nullptr;   // measured slower on B200: off by default
@@ -226,6 +232,7 @@ extern "C" void oxg4_model_destroy(oxg4_model* m) {
     cudaStreamSynchronize(m->stream);
     for (auto& kv : m->tensors) cudaFree(kv.second.d);
     for (auto& l : m->layers) cudaFree(l.inv_freq);
+    if (m->comm) nccl().CommDestroy(m->comm);
     cudaStreamDestroy(m->stream);
     delete m;
 }
@@ -275,9 +282,15 @@ extern "C" int32_t oxg4_model_upload(oxg4_model* m, const char* name, int32_t dt
             src = conv.data();
         }
         t.dtype = dst_dtype;
-        t.bytes = (size_t)count * dst_es;
+        // tensor parallelism: keep only this rank's rows / columns (csrc/tp.h)
+        const ShardSpec sh = shard_of(n, shape[0], shape[1], m->tp_rank, m->tp, m->cfg.num_attention_heads,
+                                      m->cfg.num_key_value_heads, m->cfg.head_dim, m->cfg.intermediate_size);
+        t.shape = {sh.nrows, sh.ncols};
+        t.bytes = (size_t)sh.nrows * sh.ncols * dst_es;
         CK(cudaMalloc(&t.d, t.bytes));
-        CK(cudaMemcpy(t.d, src, t.bytes, cudaMemcpyHostToDevice));   // synchronous: done on return
+        const char* s0 = (const char*)src + ((size_t)sh.row0 * shape[1] + sh.col0) * dst_es;
+        CK(cudaMemcpy2D(t.d, (size_t)sh.ncols * dst_es, s0, (size_t)shape[1] * dst_es, (size_t)sh.ncols * dst_es,
+                        (size_t)sh.nrows, cudaMemcpyHostToDevice));   // synchronous: done on return
     }
     auto it = m->tensors.find(n);
     if (it != m->tensors.end()) { cudaFree(it->second.d); m->tensors.erase(it); }
@@ -434,8 +447,40 @@ extern "C" int32_t oxg4_synchronize(oxg4_model* m) {
 }
 extern "C" int64_t oxg4_kernel_launches(const oxg4_model* m) { return m ? m->launches : 0; }
 
-extern "C" int32_t oxg4_tp_unique_id(void*) { return fail(OXG4_UNSUPPORTED, "tensor parallelism is not available in this build"); }
-extern "C" int32_t oxg4_model_tp_init(oxg4_model*, const void*) { return fail(OXG4_UNSUPPORTED, "tensor parallelism is not available in this build"); }
+extern "C" int32_t oxg4_tp_shard(const char* name, int64_t rows, int64_t cols, int32_t tp_rank, int32_t tp_size,
+                                 int32_t heads, int32_t kv_heads, int32_t head_dim, int32_t intermediate,
+                                 int64_t* out4) {
+    if (!name || !out4) return fail(OXG4_INVALID_ARGUMENT, "null argument");
+    if (tp_size < 1 || tp_rank < 0 || tp_rank >= tp_size) return fail(OXG4_INVALID_ARGUMENT, "tp_rank out of range");
+    const ShardSpec s = shard_of(canonical(name), rows, cols, tp_rank, tp_size, heads, kv_heads, head_dim, intermediate);
+    out4[0] = s.row0; out4[1] = s.nrows; out4[2] = s.col0; out4[3] = s.ncols;
+    return OXG4_OK;
+}
+
+extern "C" int32_t oxg4_tp_unique_id(void* out) {
+    if (!out) return fail(OXG4_INVALID_ARGUMENT, "null argument");
+    if (!nccl().load()) return fail(OXG4_NCCL, "NCCL: %s", nccl().error.c_str());
+    NcclApi::UniqueId id;
+    const int rc = nccl().GetUniqueId(&id);
+    if (rc != 0) return fail(OXG4_NCCL, "NCCL: ncclGetUniqueId: %s", nccl().GetErrorString(rc));
+    memcpy(out, &id, sizeof id);
+    return OXG4_OK;
+}
+
+extern "C" int32_t oxg4_model_tp_init(oxg4_model* m, const void* unique_id) {
+    if (!m || !unique_id) return fail(OXG4_INVALID_ARGUMENT, "null argument");
+    if (m->tp == 1) return OXG4_OK;
+    if (m->comm) return fail(OXG4_INVALID_ARGUMENT, "tensor-parallel communicator already initialised");
+    TRY(bind_device(m));
+    if (!nccl().load()) return fail(OXG4_NCCL, "NCCL: %s", nccl().error.c_str());
+    NcclApi::UniqueId id;
+    memcpy(&id, unique_id, sizeof id);
+    NcclApi::Comm comm = nullptr;
+    const int rc = nccl().CommInitRank(&comm, m->tp, id, m->tp_rank);
+    if (rc != 0) return fail(OXG4_NCCL, "NCCL: ncclCommInitRank: %s", nccl().GetErrorString(rc));
+    m->comm = comm;
+    return OXG4_OK;
+}
 
 // ------------------------------------------------------------------------------------------------
 // cache table + per-batch workspace
@@ -468,7 +513,8 @@ struct oxg4_cache {
           *gu_raw = nullptr, *down_raw = nullptr, *logits = nullptr, *attn_part = nullptr;
     unsigned int *attn_ticket = nullptr, *lm_ticket = nullptr;
     Cand *blk_best = nullptr, *topk_stage = nullptr;
-    uint32_t *best_ids = nullptr, *topk_ids = nullptr;
+    uint32_t *best_ids = nullptr, *topk_ids = nullptr, *tp_ids = nullptr;
+    float* tp_scores = nullptr;
     float *best_scores = nullptr, *topk_scores = nullptr;
     // pinned staging
     uint32_t* h_tokens = nullptr;
@@ -559,6 +605,8 @@ static int32_t cache_build(oxg4_cache* c) {
     TRY(dalloc(c, &c->blk_best, (size_t)B * m->num_sms));
     const int chunks = (m->V + kTopkChunk - 1) / kTopkChunk;
     TRY(dalloc(c, &c->topk_stage, (size_t)B * chunks * 64));
+    TRY(dalloc(c, &c->tp_ids, (size_t)B * m->tp));
+    TRY(dalloc(c, &c->tp_scores, (size_t)B * m->tp));
     TRY(dalloc(c, &c->best_ids, B));
     TRY(dalloc(c, &c->best_scores, B));
     TRY(dalloc(c, &c->topk_ids, (size_t)B * 64));
@@ -687,6 +735,22 @@ struct Launcher {
             cudaEventRecord(e1, m->stream);
             m->prof_events.push_back({kind, {e0, e1}});
         }
+        ++kernels;
+    }
+
+    // in-place sum over the tensor-parallel ranks (one NCCL all-reduce on the model's stream)
+    void allreduce(float* buf, size_t count) {
+        if (status != OXG4_OK || m->tp == 1) return;
+        if (!m->comm) { status = fail(OXG4_NCCL, "tensor-parallel model used before oxg4_model_tp_init"); return; }
+        const int rc = nccl().AllReduce(buf, buf, count, NcclApi::kFloat32, NcclApi::kSum, m->comm, m->stream);
+        if (rc != 0) { status = fail(OXG4_NCCL, "NCCL: ncclAllReduce: %s", nccl().GetErrorString(rc)); return; }
+        ++kernels;
+    }
+    void allgather(const void* src, void* dst, size_t bytes_per_rank) {
+        if (status != OXG4_OK || m->tp == 1) return;
+        if (!m->comm) { status = fail(OXG4_NCCL, "tensor-parallel model used before oxg4_model_tp_init"); return; }
+        const int rc = nccl().AllGather(src, dst, bytes_per_rank, NcclApi::kUint8, m->comm, m->stream);
+        if (rc != 0) { status = fail(OXG4_NCCL, "NCCL: ncclAllGather: %s", nccl().GetErrorString(rc)); return; }
         ++kernels;
     }
 };
@@ -851,6 +915,7 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
             a.in = c->attn_out;
             a.out = c->o_raw;
             launch_gemv(ln, "o", c, a, m->p_o, PRO_PLAIN, EPI_STORE);
+            ln.allreduce(c->o_raw, (size_t)B * H);        // row-split projection: sum the ranks' partial outputs
         }
         {   // post-attention norm + residual, pre-FF norm, gate and up projections (decode.rs:161-171, 14-16)
             GemvArgs a{};
@@ -884,6 +949,7 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
                 }
             }
             launch_gemv(ln, "down", c, a, m->p_down, PRO_PLAIN, EPI_STORE);
+            ln.allreduce(c->down_raw, (size_t)B * H);
         }
     }
     if (kind != STEP_PREFILL) {
@@ -907,7 +973,19 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
         a.ticket = c->lm_ticket;
         a.best_ids = c->best_ids;
         a.best_scores = c->best_scores;
+        if (m->tp > 1 && want_logits) {
+            // every rank fills its vocabulary columns; the others stay zero and the sum assembles the row
+            if (cudaMemsetAsync(c->logits, 0, sizeof(float) * (size_t)B * m->V, m->stream) != cudaSuccess)
+                ln.status = fail(OXG4_CUDA, "Gemma 4 CUDA error: cudaMemsetAsync failed");
+        }
         launch_gemv(ln, "lmhead", c, a, m->p_lm, PRO_NORM, EPI_LOGITS);
+        if (m->tp > 1) {
+            if (want_logits) ln.allreduce(c->logits, (size_t)B * m->V);
+            ln.allgather(c->best_scores, c->tp_scores, sizeof(float) * B);
+            ln.allgather(c->best_ids, c->tp_ids, sizeof(uint32_t) * B);
+            ln.go("tp_pick", tp_pick_kernel, dim3(1), dim3(128), 0, B, m->tp, (const float*)c->tp_scores,
+                  (const uint32_t*)c->tp_ids, c->best_ids, c->best_scores);
+        }
         if (kind == STEP_TOPK && top_k > 1) {
             const int chunks = (m->V + kTopkChunk - 1) / kTopkChunk;
             ln.go("topk1", topk_stage1_kernel, dim3(chunks, B), dim3(kTopkThreads), 0, (const float*)c->logits,

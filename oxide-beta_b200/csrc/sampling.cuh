@@ -48,6 +48,23 @@ __global__ void step_end_kernel(int B, uint32_t* tokens, int32_t* pos, const uin
     if (threadIdx.x == 0 && fb) ctl->step = step + 1;
 }
 
+// Tensor parallelism: every rank holds the arg-max of its vocabulary slice; after an all-gather this
+// picks the global winner (same tie-break as everywhere: higher score, then lower id).
+__global__ void tp_pick_kernel(int B, int ranks, const float* all_scores, const uint32_t* all_ids,
+                               uint32_t* ids, float* scores) {
+    pdl_wait();
+    pdl_launch();
+    for (int b = threadIdx.x; b < B; b += blockDim.x) {
+        Cand best{all_scores[b], all_ids[b]};
+        for (int r = 1; r < ranks; ++r) {
+            const Cand c{all_scores[(size_t)r * B + b], all_ids[(size_t)r * B + b]};
+            if (cand_better(c, best)) best = c;
+        }
+        ids[b] = best.i;
+        scores[b] = best.s;
+    }
+}
+
 constexpr int kTopkThreads = 256;
 constexpr int kTopkChunk = 2048;
 

@@ -208,6 +208,16 @@ class Gemma4CudaState:
         st.finalize()
         return st
 
+    @staticmethod
+    def tp_unique_id() -> bytes:
+        """128-byte NCCL id created on one rank; the caller distributes it to the others."""
+        buf = C.create_string_buffer(128)
+        N.check(N.lib().oxg4_tp_unique_id(buf))
+        return buf.raw
+
+    def tp_init(self, unique_id: bytes):
+        N.check(N.lib().oxg4_model_tp_init(self._h, C.c_char_p(unique_id)))
+
     def upload(self, name: str, array):
         a = np.ascontiguousarray(array)
         if a.dtype == np.uint16:
@@ -303,6 +313,14 @@ class Gemma4CudaState:
         N.check(N.lib().oxg4_profile_step(self._h, table._h, _ptr(t)))
         kinds = ["qkv", "attn", "o", "gateup", "down", "lmhead", "step_begin", "step_end"]
         return {k: N.lib().oxg4_profile_ms(self._h, k.encode()) for k in kinds}
+
+
+def tp_shard(name: str, rows: int, cols: int, tp_rank: int, tp_size: int, cfg: "Gemma4TextConfig"):
+    """(row0, nrows, col0, ncols) of the slice a tensor-parallel rank keeps of a checkpoint tensor."""
+    out = (C.c_int64 * 4)()
+    N.check(N.lib().oxg4_tp_shard(name.encode(), rows, cols, tp_rank, tp_size, cfg.num_attention_heads,
+                                  cfg.num_key_value_heads, cfg.head_dim, cfg.intermediate_size, out))
+    return tuple(out)
 
 
 def sample_token(logits, config: GenerationConfig, random: np.ndarray) -> int:

@@ -1,0 +1,155 @@
+"""Tensor-parallel tests.
+
+CPU part (world size 2, gloo): the shard table — every rank keeps a disjoint slice, the slices
+tile the tensor, and a row-split followed by a column-split projection summed over ranks equals the
+unsplit computation (the identity the all-reduce relies on).
+
+GPU part (needs 2 GPUs, skipped otherwise): a TP-2 model driven by two processes produces the same
+greedy tokens as the single-GPU model, and logits within the f32 tolerance.
+"""
+import os
+import subprocess
+import sys
+import textwrap
+
+import numpy as np
+import pytest
+
+from util import ROOT, pkg, syn
+
+WORKER_CPU = textwrap.dedent("""
+    import importlib, os, sys
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, os.environ["OXG4_ROOT"])
+    pkg = importlib.import_module("oxide-beta_b200")
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    cfg = pkg.Gemma4TextConfig(pkg.synthetic.small_test_cfg() if hasattr(pkg.synthetic, "small_test_cfg")
+                               else pkg.synthetic.workload("c1")["cfg"])
+    H, D, Nq, Nkv, I = cfg.hidden_size, cfg.head_dim, cfg.num_attention_heads, 2, cfg.intermediate_size
+    cfg.num_key_value_heads = Nkv
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal(H).astype(np.float32)
+    tensors = {"layers.0.self_attn.q_proj.weight": (Nq * D, H), "layers.0.self_attn.k_proj.weight": (Nkv * D, H),
+               "layers.0.self_attn.o_proj.weight": (H, Nq * D), "layers.0.mlp.gate_proj.weight": (I, H),
+               "layers.0.mlp.down_proj.weight": (H, I), "layers.0.input_layernorm.weight": (1, H)}
+    for name, (r, c) in tensors.items():
+        w = rng.standard_normal((r, c)).astype(np.float32)
+        r0, nr, c0, nc = pkg.tp_shard("model.language_model." + name, r, c, rank, world, cfg)
+        mine = w[r0:r0 + nr, c0:c0 + nc]
+        cover = torch.zeros((r, c))
+        cover[r0:r0 + nr, c0:c0 + nc] = 1
+        dist.all_reduce(cover)
+        if "layernorm" in name:
+            assert (nr, nc) == (r, c) and float(cover.min()) == world      # replicated
+            continue
+        assert float(cover.min()) == 1 and float(cover.max()) == 1, name   # slices tile the tensor once
+        if name.endswith("o_proj.weight") or name.endswith("down_proj.weight"):
+            # column split: partial outputs summed over ranks == full projection
+            v = rng.standard_normal(c).astype(np.float32)
+            part = torch.from_numpy(mine @ v[c0:c0 + nc])
+            dist.all_reduce(part)
+            assert np.allclose(part.numpy(), w @ v, rtol=1e-4, atol=1e-4), name
+        else:
+            # row split: ranks' outputs concatenated == full projection
+            outs = [torch.zeros(nr) for _ in range(world)]
+            dist.all_gather(outs, torch.from_numpy(mine @ x))
+            assert np.allclose(torch.cat(outs).numpy(), w @ x, rtol=1e-4, atol=1e-4), name
+    dist.barrier()
+    dist.destroy_process_group()
+    print("ok", rank)
+""")
+
+
+def _torchrun(script, nproc, extra_env=None, timeout=600):
+    env = dict(os.environ, OXG4_ROOT=ROOT, **(extra_env or {}))
+    path = os.path.join(ROOT, "tests", "_tp_worker_tmp.py")
+    with open(path, "w") as f:
+        f.write(script)
+    try:
+        return subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+                               "--master-addr", "127.0.0.1", "--master-port", "29611", path],
+                              env=env, capture_output=True, text=True, timeout=timeout)
+    finally:
+        os.unlink(path)
+
+
+def test_shard_table_world_size_2_gloo():
+    r = _torchrun(WORKER_CPU, 2)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    assert r.stdout.count("ok") == 2
+
+
+def test_shard_table_rejects_bad_rank():
+    cfg = pkg.Gemma4TextConfig(syn.workload("c3")["cfg"])
+    with pytest.raises(pkg.Oxg4Error):
+        pkg.tp_shard("layers.0.mlp.up_proj.weight", 10240, 2560, 4, 4, cfg)
+    assert pkg.tp_shard("layers.0.mlp.up_proj.weight", 10240, 2560, 3, 4, cfg) == (7680, 2560, 0, 2560)
+    assert pkg.tp_shard("layers.0.self_attn.v_proj.weight", 1024, 2560, 1, 4, cfg) == (256, 256, 0, 2560)
+    assert pkg.tp_shard("layers.0.mlp.down_proj.weight", 2560, 10240, 1, 2, cfg) == (0, 2560, 5120, 5120)
+    assert pkg.tp_shard("embed_tokens.weight", 262144, 2560, 1, 2, cfg) == (0, 262144, 0, 2560)
+
+
+WORKER_GPU = textwrap.dedent("""
+    import importlib, os, sys
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, os.environ["OXG4_ROOT"])
+    sys.path.insert(0, os.path.join(os.environ["OXG4_ROOT"], "tests"))
+    pkg = importlib.import_module("oxide-beta_b200")
+    syn = pkg.synthetic
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    torch.cuda.set_device(rank)
+    cfg = syn._cfg(2048, 256, 3, 8, 4, 64, 512, 16, ["sliding_attention", "full_attention", "sliding_attention"])
+    for dtype, kv, tol in (("f32", pkg.F32, 1e-3), ("bf16", pkg.BF16, None)):
+        weights = list(syn.generate_weights(cfg, seed=0, dtype=dtype, norm_jitter=0.1))
+        wd = pkg.F32 if dtype == "f32" else pkg.BF16
+        tp = pkg.Gemma4CudaState(pkg.Gemma4TextConfig(cfg), rank, wd, tp_rank=rank, tp_size=world)
+        for n, a in weights:
+            tp.upload(n, a)
+        tp.finalize()
+        ids = [pkg.Gemma4CudaState.tp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        tp.tp_init(ids[0])
+        B = 3
+        lens = [5, 9, 20]
+        prompts = [syn.prompt_ids(cfg["vocab_size"], n, seed=40 + b) for b, n in enumerate(lens)]
+        table = tp.new_cache_table([40] * B, batch=B, page_tokens=8, kv_dtype=kv)
+        logits = tp.prefill_prompt(np.concatenate(prompts), table, lens=lens)
+        toks = logits.argmax(-1).astype(np.uint32)
+        out, _ = tp.decode_greedy(toks, table, 10)
+        last = tp.decode_token(out[-1], table)
+        top = tp.decode_topk(last.argmax(-1).astype(np.uint32), table, 5, 1.2, True)
+        if rank == 0:
+            one = pkg.Gemma4CudaState.load(pkg.Gemma4TextConfig(cfg), weights, 0, wd)
+            t1 = one.new_cache_table([40] * B, batch=B, page_tokens=8, kv_dtype=kv)
+            l1 = one.prefill_prompt(np.concatenate(prompts), t1, lens=lens)
+            if tol is not None:
+                assert np.abs(l1 - logits).max() <= tol, np.abs(l1 - logits).max()
+                o1, _ = one.decode_greedy(l1.argmax(-1).astype(np.uint32), t1, 10)
+                assert np.array_equal(o1, out)
+                last1 = one.decode_token(o1[-1], t1)
+                assert np.abs(last1 - last).max() <= tol
+                top1 = one.decode_topk(last1.argmax(-1).astype(np.uint32), t1, 5, 1.2, True)
+                assert np.array_equal(top1[0], top[0]) and np.abs(top1[1] - top[1]).max() <= tol
+            else:
+                assert np.abs(l1 - logits).max() <= 2e-2, np.abs(l1 - logits).max()
+            print("tp parity ok", dtype, float(np.abs(l1 - logits).max()))
+        del table, tp
+        dist.barrier()
+    dist.destroy_process_group()
+""")
+
+
+@pytest.mark.gpu
+def test_tp2_matches_single_gpu():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    r = _torchrun(WORKER_GPU, 2, extra_env={"NCCL_NVLS_ENABLE": "0"}, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-6000:]
+    assert r.stdout.count("tp parity ok") == 2
