@@ -32,6 +32,9 @@ enum { EPI_STORE = 0, EPI_GATEUP = 1, EPI_LOGITS = 2 };
 
 constexpr int kGemvThreads = 512;
 constexpr int kGemvWarps = kGemvThreads / 32;
+constexpr int kSimtThreads = 1024;     // SIMT kernel: more warps, fewer registers, same bytes in flight per warp
+constexpr int kSimtWarps = kSimtThreads / 32;
+constexpr int kSimtMaxJ = 6;         // PRO_NORM keeps hidden/1024 values per thread: hidden <= 6144
 constexpr int kGemvMaxJ = 11;        // PRO_NORM keeps hidden/512 values per thread: hidden <= 5632
 
 struct GemvArgs {
@@ -123,7 +126,7 @@ DEVINL void block_range(int total, int parts, int idx, int& first, int& count) {
 }
 
 template <typename WT, int NB, int PRO, int EPI>
-__global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__(kSimtThreads, 1) gemv_kernel(const GemvArgs a) {
     typedef WTraits<WT> T;
     typedef typename T::XT XT;
     constexpr int EPL = T::EPL;
@@ -155,19 +158,19 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a)
         block_range(a.N, gridDim.x, blockIdx.x, row_first, rows_cta);
     }
     const int chunks_cta = rows_cta * a.cpr;
-    const int lr = max(1, (chunks_cta + kGemvWarps - 1) / kGemvWarps);   // chunks per warp run
+    const int lr = max(1, (chunks_cta + kSimtWarps - 1) / kSimtWarps);   // chunks per warp run
 
     // ---- pre-dependency section: nothing here reads what the previous kernel wrote ----
     // warm L2 with the start of what this CTA will stream
     if constexpr (EPI == EPI_LOGITS) {
         const int U = (a.N + 1) / 2;
         const int lines_per_row = (int)((row_bytes + 127) / 128);
-        for (int j = 0; j < 2 * kGemvWarps; ++j) {
+        for (int j = 0; j < 2 * kSimtWarps; ++j) {
             const int u = blockIdx.x + gridDim.x * j;
             if (u >= U) break;
             const char* p0 = (const char*)row_ptr(u * 2);
             const int nl = (u * 2 + 1 < a.N) ? 2 * lines_per_row : lines_per_row;   // rows are adjacent
-            for (int l = tid; l < nl; l += kGemvThreads) prefetch_l2(p0 + (size_t)l * 128);
+            for (int l = tid; l < nl; l += kSimtThreads) prefetch_l2(p0 + (size_t)l * 128);
         }
     } else {
         // this CTA's own block is contiguous in memory (two slabs for gate/up): bulk L2 prefetch
@@ -202,11 +205,11 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a)
         }
     }
     // norm weights are model constants: fetch them before waiting on the previous kernel
-    float wpost[kGemvMaxJ], wnorm[kGemvMaxJ];
+    float wpost[kSimtMaxJ], wnorm[kSimtMaxJ];
     if constexpr (PRO == PRO_NORM) {
 #pragma unroll
-        for (int j = 0; j < kGemvMaxJ; ++j) {
-            const int i = tid + j * kGemvThreads;
+        for (int j = 0; j < kSimtMaxJ; ++j) {
+            const int i = tid + j * kSimtThreads;
             wnorm[j] = (i < K) ? a.w_norm[i] : 0.0f;
             wpost[j] = (i < K && a.w_post) ? a.w_post[i] : 0.0f;
         }
@@ -218,28 +221,28 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a)
     // ---- prologue: build x[nb][K] in shared memory ----
     if constexpr (PRO == PRO_PLAIN) {
         for (int b = 0; b < nb; ++b)
-            for (int i = tid; i < K; i += kGemvThreads)
+            for (int i = tid; i < K; i += kSimtThreads)
                 T::store_x(xs + (size_t)b * K + i, a.in[(size_t)(b0 + b) * K + i]);
     } else {
         const bool writer = (blockIdx.x == 0);
         for (int b = 0; b < nb; ++b) {
-            float hv[kGemvMaxJ];
+            float hv[kSimtMaxJ];
             float ss[1];
             if (a.embed != nullptr) {
                 // kernel_module.rs:1272-1285: embedding row widened to f32, times sqrt(hidden)
                 uint32_t tok = a.tokens[b0 + b];
                 if (tok == kInactiveToken) tok = 0;
 #pragma unroll
-                for (int j = 0; j < kGemvMaxJ; ++j) {
-                    const int i = tid + j * kGemvThreads;
+                for (int j = 0; j < kSimtMaxJ; ++j) {
+                    const int i = tid + j * kSimtThreads;
                     hv[j] = (i < K) ? T::elem(a.embed, (size_t)tok * K + i) * a.embed_scale : 0.0f;
                 }
             } else {
-                float t[kGemvMaxJ];
+                float t[kSimtMaxJ];
                 ss[0] = 0.0f;
 #pragma unroll
-                for (int j = 0; j < kGemvMaxJ; ++j) {
-                    const int i = tid + j * kGemvThreads;
+                for (int j = 0; j < kSimtMaxJ; ++j) {
+                    const int i = tid + j * kSimtThreads;
                     t[j] = (i < K) ? a.raw[(size_t)(b0 + b) * K + i] : 0.0f;
                     hv[j] = (i < K) ? a.h_in[(size_t)(b0 + b) * K + i] : 0.0f;
                     ss[0] += t[j] * t[j];
@@ -247,12 +250,12 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a)
                 block_sum<1>(ss, red);
                 const float r = 1.0f / sqrtf(ss[0] / (float)K + a.eps);
 #pragma unroll
-                for (int j = 0; j < kGemvMaxJ; ++j) hv[j] = (hv[j] + t[j] * r * wpost[j]) * a.scalar;
+                for (int j = 0; j < kSimtMaxJ; ++j) hv[j] = (hv[j] + t[j] * r * wpost[j]) * a.scalar;
             }
             ss[0] = 0.0f;
 #pragma unroll
-            for (int j = 0; j < kGemvMaxJ; ++j) {
-                const int i = tid + j * kGemvThreads;
+            for (int j = 0; j < kSimtMaxJ; ++j) {
+                const int i = tid + j * kSimtThreads;
                 if (i < K) {
                     if (writer) a.h_out[(size_t)(b0 + b) * K + i] = hv[j];
                     ss[0] += hv[j] * hv[j];
@@ -261,15 +264,15 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a)
             block_sum<1>(ss, red);
             const float r2 = 1.0f / sqrtf(ss[0] / (float)K + a.eps);
 #pragma unroll
-            for (int j = 0; j < kGemvMaxJ; ++j) {
-                const int i = tid + j * kGemvThreads;
+            for (int j = 0; j < kSimtMaxJ; ++j) {
+                const int i = tid + j * kSimtThreads;
                 if (i < K) T::store_x(xs + (size_t)b * K + i, hv[j] * r2 * wnorm[j]);
             }
         }
     }
     // rows of a partial batch chunk that do not exist read zeros
     for (int b = nb; b < NB; ++b)
-        for (int i = tid; i < K; i += kGemvThreads) xs[(size_t)b * K + i] = (XT)0;
+        for (int i = tid; i < K; i += kSimtThreads) xs[(size_t)b * K + i] = (XT)0;
     __syncthreads();
     pdl_launch();
     stamp(a.ts, 2);
@@ -346,13 +349,13 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a)
             return t;
         };
         if constexpr (EPI == EPI_STORE) {
-            for (int idx = tid; idx < rows_cta * nb; idx += kGemvThreads) {
+            for (int idx = tid; idx < rows_cta * nb; idx += kSimtThreads) {
                 const int rl = idx % rows_cta, b = idx / rows_cta;
                 a.out[(size_t)(b0 + b) * a.N + row_first + rl] = row_total(rl, b);
             }
         } else {
             const int pairs = rows_cta / 2;
-            for (int idx = tid; idx < pairs * nb; idx += kGemvThreads) {
+            for (int idx = tid; idx < pairs * nb; idx += kSimtThreads) {
                 const int pl = idx % pairs, b = idx / pairs;
                 const float g = row_total(2 * pl, b), u = row_total(2 * pl + 1, b);
                 a.out[(size_t)(b0 + b) * (a.N / 2) + row_first / 2 + pl] = gelu_mul(g, u);
@@ -364,7 +367,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a)
 #pragma unroll
         for (int b = 0; b < NB; ++b) { best[b].s = -INFINITY; best[b].i = 0xffffffffu; }
         const int U = (a.N + 1) / 2;
-        for (int u = blockIdx.x + gridDim.x * warp; u < U; u += gridDim.x * kGemvWarps) {
+        for (int u = blockIdx.x + gridDim.x * warp; u < U; u += gridDim.x * kSimtWarps) {
             const int r0 = u * 2;
             const bool has1 = (r0 + 1 < a.N);
             const WT* p0 = row_ptr(r0);
@@ -420,12 +423,12 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a)
         Cand* wc = reinterpret_cast<Cand*>(pieces);
         __shared__ unsigned int s_last;
         if (lane == 0)
-            for (int b = 0; b < NB; ++b) wc[b * kGemvWarps + warp] = best[b];
+            for (int b = 0; b < NB; ++b) wc[b * kSimtWarps + warp] = best[b];
         __syncthreads();
         if (tid < nb) {
-            Cand c = wc[tid * kGemvWarps];
-            for (int w = 1; w < kGemvWarps; ++w)
-                if (cand_better(wc[tid * kGemvWarps + w], c)) c = wc[tid * kGemvWarps + w];
+            Cand c = wc[tid * kSimtWarps];
+            for (int w = 1; w < kSimtWarps; ++w)
+                if (cand_better(wc[tid * kSimtWarps + w], c)) c = wc[tid * kSimtWarps + w];
             a.blk_best[(size_t)(b0 + tid) * gridDim.x + blockIdx.x] = c;
         }
         __threadfence();
@@ -434,7 +437,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvArgs a)
         __syncthreads();
         if (s_last) {
             __threadfence();
-            for (int b = warp; b < nb; b += kGemvWarps) {
+            for (int b = warp; b < nb; b += kSimtWarps) {
                 Cand c{-INFINITY, 0xffffffffu};
                 for (int gi = lane; gi < (int)gridDim.x; gi += 32) {
                     const Cand* src = &a.blk_best[(size_t)(b0 + b) * gridDim.x + gi];

@@ -149,8 +149,8 @@ static GemvPlan make_plan(int N, int K, int es, int num_sms, int group /*rows th
     p.grid = std::max(1, std::min(num_sms, groups));
     const int rows_min = (groups / p.grid) * group;
     p.rows_max = ((groups + p.grid - 1) / p.grid) * group;
-    const int lr_min = std::max(1, (rows_min * p.cpr + kGemvWarps - 1) / kGemvWarps);
-    p.slots = std::min(kGemvWarps, (p.cpr - 1) / lr_min + 2);
+    const int lr_min = std::max(1, (rows_min * p.cpr + kSimtWarps - 1) / kSimtWarps);
+    p.slots = std::min(kSimtWarps, (p.cpr - 1) / lr_min + 2);
     return p;
 }
 
@@ -417,7 +417,7 @@ extern "C" int32_t oxg4_model_finalize(oxg4_model* m) {
     m->p_gateup = make_plan(2 * m->I, H, m->es, m->num_sms, 2);
     m->p_down = make_plan(H, m->I, m->es, m->num_sms, 1);
     m->p_lm = make_plan(m->Vloc, H, m->es, m->num_sms, 1);
-    m->p_lm_simt_grid = std::min(m->num_sms, std::max(1, (m->Vloc + 2 * kGemvWarps - 1) / (2 * kGemvWarps)));
+    m->p_lm_simt_grid = std::min(m->num_sms, std::max(1, (m->Vloc + 2 * kSimtWarps - 1) / (2 * kSimtWarps)));
     if (m->es == 2) {
         TRY((set_gemv_attrs<uint16_t, 1>()));
         TRY((set_mma_attrs<8>()));
@@ -790,8 +790,9 @@ static void launch_gemv(Launcher& ln, const char* kind, oxg4_cache* c, GemvArgs 
     a.B = B;
     a.eps = m->cfg.rms_norm_eps;
     a.ts = ln.ts();
-    if (pro == PRO_NORM && p.K > kGemvMaxJ * kGemvThreads) {
-        ln.status = fail(OXG4_UNSUPPORTED, "hidden size above %d is not supported", kGemvMaxJ * kGemvThreads);
+    if (pro == PRO_NORM && p.K > std::min(kGemvMaxJ * kGemvThreads, kSimtMaxJ * kSimtThreads)) {
+        ln.status = fail(OXG4_UNSUPPORTED, "hidden size above %d is not supported",
+                         std::min(kGemvMaxJ * kGemvThreads, kSimtMaxJ * kSimtThreads));
         return;
     }
     const size_t limit = 226 * 1024;
@@ -815,7 +816,7 @@ static void launch_gemv(Launcher& ln, const char* kind, oxg4_cache* c, GemvArgs 
     a.bpp = nb;
     size_t smem = (size_t)nb * p.K * m->es + (size_t)nb * 32 * 4;
     size_t extra = (size_t)p.rows_max * p.slots * nb * 4;
-    extra = std::max(extra, (size_t)nb * kGemvWarps * sizeof(Cand));
+    extra = std::max(extra, (size_t)nb * kSimtWarps * sizeof(Cand));
     smem += extra;
     if (smem > limit) {
         ln.status = fail(OXG4_UNSUPPORTED, "projection %s needs %zu bytes of shared memory", kind, smem);
@@ -823,7 +824,7 @@ static void launch_gemv(Launcher& ln, const char* kind, oxg4_cache* c, GemvArgs 
     }
     auto fn = m->es == 2 ? pick_gemv<uint16_t>(nb, pro, epi) : pick_gemv<float>(nb, pro, epi);
     dim3 grid(epi == EPI_LOGITS ? m->p_lm_simt_grid : p.grid, (B + nb - 1) / nb, 1);
-    ln.go(kind, fn, grid, dim3(kGemvThreads), smem, a);
+    ln.go(kind, fn, grid, dim3(kSimtThreads), smem, a);
 }
 
 template <typename KT>
