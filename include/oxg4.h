@@ -192,6 +192,16 @@ int32_t oxg4_topk_noalloc(const float* logits_dev, int32_t rows, int32_t vocab, 
                           float repetition_penalty, int32_t top_k, uint32_t* ids_dev, float* scores_dev,
                           void* cuda_stream);
 
+/* Layer-wise trace of one decode step, the counterpart of the reference's GEMMA4_TRACE_LAYERS
+ * fingerprints (gemma4_cuda/mod.rs:182-199, decode.rs:351-369), returning the tensors themselves.
+ * `trace` receives [layers + 1, batch, hidden] f32: the input of every layer as this library
+ * computed it (entry l > 0 = output of layer l - 1) and the final hidden state. `inject` (may be
+ * NULL) holds [layers, batch, hidden] f32 values that REPLACE the input of every layer after it
+ * has been recorded (layer-wise teacher forcing for parity tests); `logits` (may be NULL) receives
+ * [batch, vocab]. Runs eagerly (no graph) and advances the cache like oxg4_decode_logits. */
+int32_t oxg4_decode_trace(oxg4_model* model, oxg4_cache* cache, const uint32_t* tokens, const float* inject,
+                          float* trace, float* logits);
+
 /* Diagnostics (no counterpart in the reference): when the environment variable OXG4_TIMELINE is
  * set before oxg4_model_create, every kernel of a step stamps the GPU's nanosecond timer at entry,
  * after its dependency wait, after its prologue and at exit. Copies the stamps of the most recent

@@ -76,6 +76,7 @@ SYMBOLS = {
     "oxg4_profile_ms": (C.c_float, [C.c_void_p, C.c_char_p]),
     "oxg4_topk_noalloc": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_float, C.c_int32, C.c_void_p,
                                       C.c_void_p, C.c_void_p]),
+    "oxg4_decode_trace": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "oxg4_debug_timeline": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32]),
     "oxg4_generate": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64, C.POINTER(GenerationConfigC), C.c_int32,
                                   TOKEN_CALLBACK, C.c_void_p, C.c_void_p, C.POINTER(C.c_int64)]),

@@ -237,6 +237,13 @@ __global__ void __launch_bounds__(kSimtThreads, 1) gemv_kernel(const GemvArgs a)
                     const int i = tid + j * kSimtThreads;
                     hv[j] = (i < K) ? T::elem(a.embed, (size_t)tok * K + i) * a.embed_scale : 0.0f;
                 }
+            } else if (a.raw == nullptr) {
+                // nothing pending: h_in already is the layer's input (layer-wise tracing)
+#pragma unroll
+                for (int j = 0; j < kSimtMaxJ; ++j) {
+                    const int i = tid + j * kSimtThreads;
+                    hv[j] = (i < K) ? a.h_in[(size_t)(b0 + b) * K + i] : 0.0f;
+                }
             } else {
                 float t[kSimtMaxJ];
                 ss[0] = 0.0f;

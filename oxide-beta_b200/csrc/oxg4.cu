@@ -842,7 +842,13 @@ static void (*pick_attn(int D, int G))(const AttnArgs) {
 }
 
 // Launches every kernel of one step on the model's stream (eagerly or under stream capture).
-static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* n_kernels) {
+struct TraceCtx {
+    const float* inject_dev;   // [L][B][H] layer inputs to force, or null
+    float* trace_dev;          // [L+1][B][H] receives every layer's input and the final hidden state
+};
+
+static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* n_kernels,
+                        const TraceCtx* tr = nullptr) {
     oxg4_model* m = c->m;
     Launcher ln{m};
     ln.ts_base = c->ts_buf;
@@ -874,7 +880,23 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
                 a.pf_ptr[1] = p.wgate;
                 a.pf_bytes[1] = (unsigned long long)m->I * H * m->es;
             }
+            auto copy_trace = [&]() {
+                if (tr && ln.status == OXG4_OK &&
+                    cudaMemcpyAsync(tr->trace_dev + (size_t)l * B * H, c->hB, sizeof(float) * B * H,
+                                    cudaMemcpyDeviceToDevice, m->stream) != cudaSuccess)
+                    ln.status = fail(OXG4_CUDA, "Gemma 4 CUDA error: trace copy failed");
+            };
             launch_gemv(ln, "qkv", c, a, m->p_qkv, PRO_NORM, EPI_STORE);
+            copy_trace();          // the layer's input as this library computed it
+            if (tr && tr->inject_dev) {
+                // layer-wise teacher forcing: redo the projection from the forced input, nothing pending
+                a.embed = nullptr;
+                a.raw = nullptr;
+                a.w_post = nullptr;
+                a.scalar = 1.0f;
+                a.h_in = tr->inject_dev + (size_t)l * B * H;
+                launch_gemv(ln, "qkv", c, a, m->p_qkv, PRO_NORM, EPI_STORE);
+            }
         }
         {   // q/k norm + RoPE + v norm + KV append + attention (decode.rs:99-157)
             AttnArgs a{};
@@ -987,6 +1009,10 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
             ln.go("tp_pick", tp_pick_kernel, dim3(1), dim3(128), 0, B, m->tp, (const float*)c->tp_scores,
                   (const uint32_t*)c->tp_ids, c->best_ids, c->best_scores);
         }
+        if (tr && ln.status == OXG4_OK &&
+            cudaMemcpyAsync(tr->trace_dev + (size_t)L * B * H, c->hB, sizeof(float) * B * H, cudaMemcpyDeviceToDevice,
+                            m->stream) != cudaSuccess)
+            ln.status = fail(OXG4_CUDA, "Gemma 4 CUDA error: trace copy failed");
         if (kind == STEP_TOPK && top_k > 1) {
             const int chunks = (m->V + kTopkChunk - 1) / kTopkChunk;
             ln.go("topk1", topk_stage1_kernel, dim3(chunks, B), dim3(kTopkThreads), 0, (const float*)c->logits,
@@ -1199,6 +1225,38 @@ extern "C" int32_t oxg4_profile_step(oxg4_model* m, oxg4_cache* c, const uint32_
     m->prof_events.clear();
     advance_host(c, tokens);
     return OXG4_OK;
+}
+
+extern "C" int32_t oxg4_decode_trace(oxg4_model* m, oxg4_cache* c, const uint32_t* tokens, const float* inject,
+                                     float* trace, float* logits) {
+    if (!m || !c || !tokens || !trace || c->m != m) return fail(OXG4_INVALID_ARGUMENT, "null or mismatched handle");
+    TRY(bind_device(m));
+    TRY(check_tokens(c, tokens, true));
+    const int L = m->cfg.num_hidden_layers;
+    const size_t per = (size_t)c->B * m->H;
+    float *d_inject = nullptr, *d_trace = nullptr;
+    CK(cudaMalloc(&d_trace, sizeof(float) * per * (L + 1)));
+    if (inject) {
+        if (cudaMalloc(&d_inject, sizeof(float) * per * L) != cudaSuccess) { cudaFree(d_trace); return fail(OXG4_OOM, "out of device memory"); }
+        cudaMemcpy(d_inject, inject, sizeof(float) * per * L, cudaMemcpyHostToDevice);
+    }
+    int32_t s = stage_inputs(c, tokens, 0, 0);
+    TraceCtx tr{d_inject, d_trace};
+    int n = 0;
+    if (s == OXG4_OK) s = run_step(c, STEP_LOGITS, 1, 1.0f, &n, &tr);      // eager launches, no graph
+    if (s == OXG4_OK && cudaStreamSynchronize(m->stream) != cudaSuccess) s = fail(OXG4_CUDA, "Gemma 4 CUDA error: trace step failed");
+    if (s == OXG4_OK) {
+        m->launches += n;
+        cudaMemcpy(trace, d_trace, sizeof(float) * per * (L + 1), cudaMemcpyDeviceToHost);
+        if (logits) {
+            cudaMemcpy(logits, c->logits, sizeof(float) * (size_t)c->B * m->V, cudaMemcpyDeviceToHost);
+            softcap(logits, (size_t)c->B * m->V, m->cfg.final_logit_softcapping);
+        }
+        advance_host(c, tokens);
+    }
+    cudaFree(d_trace);
+    cudaFree(d_inject);
+    return s;
 }
 
 extern "C" int32_t oxg4_debug_timeline(oxg4_cache* c, unsigned long long* out, int32_t max_entries) {

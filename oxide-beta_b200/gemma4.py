@@ -299,6 +299,18 @@ class Gemma4CudaState:
             return [(int(i), float(s)) for i, s in zip(ids[0], scores[0])]
         return ids, scores
 
+    def decode_trace(self, token, table: Gemma4CudaCacheTable, inject=None, want_logits=True):
+        """One eager step; returns (trace [layers + 1, batch, hidden], logits [batch, vocab] or None).
+        `inject` [layers, batch, hidden] replaces the input hidden state of every layer."""
+        t = _as_u32(np.atleast_1d(token))
+        L, H, B = self.config.num_hidden_layers, self.config.hidden_size, table.batch
+        trace = np.empty((L + 1, B, H), dtype=np.float32)
+        logits = np.empty((B, self.config.vocab_size), dtype=np.float32) if want_logits else None
+        inj = None if inject is None else np.ascontiguousarray(inject, dtype=np.float32).reshape(L, B, H)
+        N.check(N.lib().oxg4_decode_trace(self._h, table._h, _ptr(t), None if inj is None else _ptr(inj),
+                                          _ptr(trace), None if logits is None else _ptr(logits)))
+        return trace, logits
+
     def decode_greedy(self, first_tokens, table: Gemma4CudaCacheTable, steps: int):
         """Device-resident greedy loop: returns (ids [steps, batch], mean device ms per step)."""
         t = _as_u32(np.atleast_1d(first_tokens))
