@@ -17,11 +17,13 @@
 //
 // HBM-bound: bytes per launch = 2 * visible_positions * kv_heads * head_dim * sizeof(KV element).
 #pragma once
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace oxg4 {
 
-constexpr int kAttnThreads = 256;
+constexpr int kAttnThreads = 512;
 constexpr int kAttnWarps = kAttnThreads / 32;
 
 struct AttnArgs {
@@ -99,7 +101,11 @@ template <typename KT> DEVINL float kv_widen(KT v);
 template <> DEVINL float kv_widen<float>(float v) { return v; }
 template <> DEVINL float kv_widen<uint16_t>(uint16_t v) { return __uint_as_float((uint32_t)v << 16); }
 
-template <typename KT, int D, int G>
+// CL = true: the splits of one (sequence, kv head) form a thread-block cluster (gridDim.x <= 8 CTAs);
+// partials stay in shared memory and are merged through distributed shared memory after one cluster
+// barrier. CL = false: partials go through global memory and the last CTA to arrive (atomic ticket)
+// merges them.
+template <typename KT, int D, int G, bool CL>
 __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArgs a) {
     constexpr int EPT = D / 32;
     constexpr int NW = kAttnWarps;
@@ -110,6 +116,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
     float* wm = vcur + D;                    // [NW][G]
     float* wl = wm + NW * G;                 // [NW][G]
     float* wacc = wl + NW * G;               // [NW][G][D]
+    float* cpart = wacc + NW * G * D;        // [G][D + 2] this CTA's partial (cluster variant)
     __shared__ unsigned int s_last;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -301,7 +308,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
             for (int e = 0; e < EPT; ++e) wacc[((size_t)warp * G + g) * D + lane * EPT + e] = acc[g][e];
         }
         __syncthreads();
-        float* my = part + (size_t)s * (G * (D + 2));
+        float* my = CL ? cpart : part + (size_t)s * (G * (D + 2));
         for (int idx = tid; idx < G * D; idx += kAttnThreads) {
             const int g = idx / D, d = idx % D;
             float M = -INFINITY;
@@ -319,6 +326,36 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
         }
     }
 
+    if constexpr (CL) {
+        // ---- cluster merge: every CTA finishes a slice of the outputs from its peers' shared memory ----
+        namespace cg = cooperative_groups;
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();                                    // every CTA of the cluster arrives, with or without work
+        if (active) {
+            const int cs = (int)gridDim.x;
+            const int per = (G * D + cs - 1) / cs;
+            const int hi = min(G * D, (s + 1) * per);
+            for (int idx = s * per + tid; idx < hi; idx += kAttnThreads) {
+                const int g = idx / D, d = idx % D;
+                float M = -INFINITY;
+                for (int sp = 0; sp < n_eff; ++sp)
+                    M = fmaxf(M, cluster.map_shared_rank(cpart, sp)[g * (D + 2) + D]);
+                float A = 0.0f, L = 0.0f;
+                for (int sp = 0; sp < n_eff; ++sp) {
+                    const float* ps = cluster.map_shared_rank(cpart, sp) + g * (D + 2);
+                    const float ms = ps[D];
+                    if (ms == -INFINITY) continue;
+                    const float e = expf(ms - M);
+                    A += e * ps[d];
+                    L += e * ps[D + 1];
+                }
+                a.out[(size_t)b * a.Nq * D + (size_t)(kvh * G + g) * D + d] = A / L;
+            }
+        }
+        cluster.sync();                                    // no CTA leaves while a peer may still read its partial
+        stamp(a.ts, 3);
+        return;
+    }
     // ---- last CTA of this (sequence, kv head) merges the split partials in split order ----
     __threadfence();
     __syncthreads();
@@ -372,7 +409,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
 
 template <int D, int G>
 inline size_t attn_smem_bytes() {
-    return sizeof(float) * (size_t)(G * D + 2 * D + 2 * kAttnWarps * G + kAttnWarps * G * D);
+    return sizeof(float) * (size_t)(G * D + 2 * D + 2 * kAttnWarps * G + kAttnWarps * G * D + G * (D + 2));
 }
 
 }  // namespace oxg4

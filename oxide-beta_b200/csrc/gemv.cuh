@@ -61,6 +61,7 @@ struct GemvArgs {
     // weights of later kernels to pull into L2 while this kernel runs (each CTA takes a slice)
     const void* pf_ptr[2];
     unsigned long long pf_bytes[2];
+    int pf_cap_kb;           // bytes of its own weight block a CTA prefetches into L2 before the dependency wait (KiB)
     unsigned long long* ts;  // optional timeline slots of this launch (4 entries) or null
     // epilogue
     float* out;              // STORE: [B, N]; GATEUP: [B, N/2]; LOGITS: [B, n_total] or null
@@ -176,7 +177,7 @@ __global__ void __launch_bounds__(kSimtThreads, 1) gemv_kernel(const GemvArgs a)
         // this CTA's own block is contiguous in memory (two slabs for gate/up): bulk L2 prefetch
         if (tid < 8 && rows_cta > 0) {
             constexpr size_t PIECE = 32 * 1024;
-            const size_t cap = 256 * 1024;
+            const size_t cap = (size_t)a.pf_cap_kb * 1024;
             if constexpr (EPI == EPI_GATEUP) {
                 const size_t slab = min((size_t)(rows_cta / 2) * row_bytes, cap / 2);
                 const char* g0 = (const char*)a.W0 + (size_t)(row_first / 2) * row_bytes;

@@ -27,6 +27,11 @@ namespace oxg4 {
 
 constexpr int kMmaRowsPerPass = 64;      // rows of the block handled between two combines
 
+// Row stride (elements) of the activation rows in shared memory: K padded so that consecutive rows
+// start 64 bytes apart modulo 128; the eight lanes of an LDS.128 phase (two batch rows x four column
+// groups) then hit eight different 16-byte bank groups instead of colliding.
+__host__ __device__ inline int mma_x_stride(int K) { return K + (((64 - (K * 2) % 128) + 128) % 128) / 2; }
+
 DEVINL void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                            uint32_t b1) {
     asm volatile(
@@ -40,7 +45,7 @@ DEVINL void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
 // fewer than eight row groups it reaches 8 / NG2 chunks ahead, so short blocks (few rows per CTA)
 // keep as many bytes in flight as tall ones. Writes the warp's partial sums to `pc`.
 template <int MB, int NG2>
-DEVINL void mma_pass(const uint16_t* xs, int K, int nb, int nchunk, int warp, int g, int t,
+DEVINL void mma_pass(const uint16_t* xs, int XS, int K, int nb, int nchunk, int warp, int g, int t,
                      const uint16_t* base, size_t gstride, int rows_left, uint4 (&w)[8], bool preloaded,
                      const uint16_t* next_base, int next_rows, bool preload_next, float* pc) {
     constexpr int CA = 8 / NG2;                       // chunks held in the ring
@@ -70,8 +75,8 @@ DEVINL void mma_pass(const uint16_t* xs, int K, int nb, int nchunk, int warp, in
                 const int col = (warp + NW * i) * 32 + t * 8;
                 uint4 xa = make_uint4(0u, 0u, 0u, 0u), xb = make_uint4(0u, 0u, 0u, 0u);
                 if (col < K) {
-                    if (g < nb) xa = *reinterpret_cast<const uint4*>(xs + (size_t)g * K + col);
-                    if (MB == 16 && g + 8 < nb) xb = *reinterpret_cast<const uint4*>(xs + (size_t)(g + 8) * K + col);
+                    if (g < nb) xa = *reinterpret_cast<const uint4*>(xs + (size_t)g * XS + col);
+                    if (MB == 16 && g + 8 < nb) xb = *reinterpret_cast<const uint4*>(xs + (size_t)(g + 8) * XS + col);
                 }
                 const int in = i + CA;                 // the chunk that takes over this ring position
                 const bool more = in < nmy;
@@ -116,8 +121,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvArg
     const int g = lane >> 2, t = lane & 3;
     const int b0 = blockIdx.y * a.bpp;
     const int nb = min(a.bpp, a.B - b0);              // <= MB
-    uint16_t* xs = reinterpret_cast<uint16_t*>(smem_raw);                              // [nb][K]
-    float* red = reinterpret_cast<float*>(smem_raw + (((size_t)nb * K * 2 + 15) & ~(size_t)15));   // [32]
+    const int XS = mma_x_stride(K);
+    uint16_t* xs = reinterpret_cast<uint16_t*>(smem_raw);                              // [nb][XS]
+    float* red = reinterpret_cast<float*>(smem_raw + (((size_t)nb * XS * 2 + 15) & ~(size_t)15));   // [32]
     float* pieces = red + 32;                           // [2][64 rows][16 warps][nb]
     const size_t row_bytes = (size_t)K * 2;
 
@@ -140,7 +146,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvArg
     // ---- pre-dependency section: nothing here reads what the previous kernel wrote ----
     if (tid < 8 && rows_cta > 0) {
         constexpr size_t PIECE = 32 * 1024;
-        const size_t cap = 256 * 1024;
+        const size_t cap = (size_t)a.pf_cap_kb * 1024;
         if constexpr (EPI == EPI_GATEUP) {
             const size_t slab = min((size_t)(rows_cta / 2) * row_bytes, cap / 2);
             const char* g0 = (const char*)a.W0 + (size_t)(row_first / 2) * row_bytes;
@@ -171,7 +177,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvArg
     if constexpr (PRO == PRO_PLAIN) {
         for (int b = 0; b < nb; ++b)
             for (int i = tid; i < K; i += kGemvThreads)
-                xs[(size_t)b * K + i] = (uint16_t)f32_to_bf16_bits(a.in[(size_t)(b0 + b) * K + i]);
+                xs[(size_t)b * XS + i] = (uint16_t)f32_to_bf16_bits(a.in[(size_t)(b0 + b) * K + i]);
     } else {
         const bool writer = (blockIdx.x == 0);
         for (int b = 0; b < nb; ++b) {
@@ -220,7 +226,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvArg
 #pragma unroll
             for (int j = 0; j < kGemvMaxJ; ++j) {
                 const int i = tid + j * kGemvThreads;
-                if (i < K) xs[(size_t)b * K + i] = (uint16_t)f32_to_bf16_bits(hv[j] * r2 * wnorm[j]);
+                if (i < K) xs[(size_t)b * XS + i] = (uint16_t)f32_to_bf16_bits(hv[j] * r2 * wnorm[j]);
             }
         }
     }
@@ -248,15 +254,15 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvArg
         float* pc = pieces + (size_t)(pass & 1) * kMmaRowsPerPass * NW * nb;
         const int ng = (min(rows_left, kMmaRowsPerPass) + 7) >> 3;
         if (ng > 4) {
-            mma_pass<MB, 8>(xs, K, nb, nchunk, warp, g, t, base, gstride, rows_left, w, preloaded, next_base,
+            mma_pass<MB, 8>(xs, XS, K, nb, nchunk, warp, g, t, base, gstride, rows_left, w, preloaded, next_base,
                             next_rows, next_full, pc);
             preloaded = next_full;
         } else if (ng > 2) {
-            mma_pass<MB, 4>(xs, K, nb, nchunk, warp, g, t, base, gstride, rows_left, w, false, next_base, 0, false, pc);
+            mma_pass<MB, 4>(xs, XS, K, nb, nchunk, warp, g, t, base, gstride, rows_left, w, false, next_base, 0, false, pc);
         } else if (ng > 1) {
-            mma_pass<MB, 2>(xs, K, nb, nchunk, warp, g, t, base, gstride, rows_left, w, false, next_base, 0, false, pc);
+            mma_pass<MB, 2>(xs, XS, K, nb, nchunk, warp, g, t, base, gstride, rows_left, w, false, next_base, 0, false, pc);
         } else {
-            mma_pass<MB, 1>(xs, K, nb, nchunk, warp, g, t, base, gstride, rows_left, w, false, next_base, 0, false, pc);
+            mma_pass<MB, 1>(xs, XS, K, nb, nchunk, warp, g, t, base, gstride, rows_left, w, false, next_base, 0, false, pc);
         }
         base = next_base;
         // rows of the pass that no group produced must not be read by the combine: none are, it stops

@@ -96,6 +96,7 @@ struct oxg4_model {
     int num_sms = 148;
     bool use_pdl = true;
     bool far_prefetch = false;
+    int pf_cap_kb = 256;
     bool timeline = false;        // OXG4_TIMELINE: kernels stamp the global timer into the cache's buffer     // pull later kernels' weights into L2 during latency-bound kernels
     bool finalized = false;
     std::map<std::string, Tensor> tensors;
@@ -213,6 +214,7 @@ extern "C" int32_t oxg4_model_create(const oxg4_config* c, int32_t device, oxg4_
     m->tp_rank = c->tp_rank;
     m->use_pdl = getenv("OXG4_DISABLE_PDL") == nullptr;
     m->timeline = getenv("OXG4_TIMELINE") != nullptr;
+    if (const char* e = getenv("OXG4_PREFETCH_KB")) m->pf_cap_kb = std::max(0, atoi(e));
     m->far_prefetch = getenv("OXG4_FAR_PREFETCH") != nullptr;   // measured slower on B200: off by default
     if (cudaSetDevice(device) != cudaSuccess) { delete m; return fail(OXG4_CUDA, "Gemma 4 CUDA error: cudaSetDevice"); }
     cudaDeviceProp prop;
@@ -343,10 +345,14 @@ static int32_t set_mma_attrs() {
 
 template <typename KT, int D>
 static int32_t set_attn_attrs() {
-    TRY(allow_big_smem(attn_decode_kernel<KT, D, 1>));
-    TRY(allow_big_smem(attn_decode_kernel<KT, D, 2>));
-    TRY(allow_big_smem(attn_decode_kernel<KT, D, 4>));
-    TRY(allow_big_smem(attn_decode_kernel<KT, D, 8>));
+    TRY(allow_big_smem(attn_decode_kernel<KT, D, 1, false>));
+    TRY(allow_big_smem(attn_decode_kernel<KT, D, 2, false>));
+    TRY(allow_big_smem(attn_decode_kernel<KT, D, 4, false>));
+    TRY(allow_big_smem(attn_decode_kernel<KT, D, 8, false>));
+    TRY(allow_big_smem(attn_decode_kernel<KT, D, 1, true>));
+    TRY(allow_big_smem(attn_decode_kernel<KT, D, 2, true>));
+    TRY(allow_big_smem(attn_decode_kernel<KT, D, 4, true>));
+    TRY(allow_big_smem(attn_decode_kernel<KT, D, 8, true>));
     return OXG4_OK;
 }
 
@@ -499,6 +505,7 @@ struct oxg4_cache {
     std::vector<int32_t> max_seq, pos_host;
     int pps_full = 0, pps_slide = 0;
     int splits_full = 1, splits_slide = 1, min_split = 32;
+    bool attn_cluster = true;     // merge split-KV partials through a thread-block cluster's shared memory
     std::vector<void*> kpool, vpool;          // per layer
     int64_t kv_bytes = 0;
     int32_t *pt_full = nullptr, *pt_slide = nullptr, *cap_full = nullptr, *cap_slide = nullptr;
@@ -584,8 +591,15 @@ static int32_t cache_build(oxg4_cache* c) {
     const int pairs = std::max(1, m->Nkv * B);
     const int want = std::max(1, (8 * m->num_sms + pairs - 1) / pairs);
     c->min_split = 16;
-    c->splits_full = std::max(1, std::min({want, 64, (maxf + c->min_split - 1) / c->min_split}));
-    c->splits_slide = std::max(1, std::min({want, 64, (maxs + c->min_split - 1) / c->min_split}));
+    c->attn_cluster = getenv("OXG4_ATTN_TICKET") == nullptr;
+    const int cap_splits = c->attn_cluster ? 8 : 64;
+    auto pow2_floor = [](int v) { int p = 1; while (p * 2 <= v) p *= 2; return p; };
+    c->splits_full = std::max(1, std::min({want, cap_splits, (maxf + c->min_split - 1) / c->min_split}));
+    c->splits_slide = std::max(1, std::min({want, cap_splits, (maxs + c->min_split - 1) / c->min_split}));
+    if (c->attn_cluster) {
+        c->splits_full = pow2_floor(c->splits_full);
+        c->splits_slide = pow2_floor(c->splits_slide);
+    }
     const int smax = std::max(c->splits_full, c->splits_slide);
     TRY(dalloc(c, &c->tokens, B));
     TRY(dalloc(c, &c->pos, B));
@@ -703,6 +717,7 @@ extern "C" int32_t oxg4_cache_reset(oxg4_cache* c) {
 struct Launcher {
     oxg4_model* m;
     unsigned long long* ts_base = nullptr;
+    int cluster_x = 0;            // > 0: launch the next kernel with thread-block clusters of this many CTAs along x
     int kernels = 0;
     unsigned long long* ts() const { return (ts_base && kernels < kMaxTimeline) ? ts_base + (size_t)kernels * 4 : nullptr; }
     int32_t status = OXG4_OK;
@@ -721,11 +736,22 @@ struct Launcher {
         cfg.blockDim = block;
         cfg.dynamicSmemBytes = smem;
         cfg.stream = m->stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cudaLaunchAttribute attr[2];
+        int na = 0;
+        if (m->use_pdl && !m->profiling) {
+            attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[na].val.programmaticStreamSerializationAllowed = 1;
+            ++na;
+        }
+        if (cluster_x > 0) {
+            attr[na].id = cudaLaunchAttributeClusterDimension;
+            attr[na].val.clusterDim.x = cluster_x;
+            attr[na].val.clusterDim.y = 1;
+            attr[na].val.clusterDim.z = 1;
+            ++na;
+        }
         cfg.attrs = attr;
-        cfg.numAttrs = (m->use_pdl && !m->profiling) ? 1 : 0;
+        cfg.numAttrs = na;
         cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, args...);
         if (e != cudaSuccess) {
             status = fail(OXG4_CUDA, "Gemma 4 CUDA error: launch of %s failed: %s", kind, cudaGetErrorString(e));
@@ -790,6 +816,7 @@ static void launch_gemv(Launcher& ln, const char* kind, oxg4_cache* c, GemvArgs 
     a.B = B;
     a.eps = m->cfg.rms_norm_eps;
     a.ts = ln.ts();
+    a.pf_cap_kb = m->pf_cap_kb;
     if (pro == PRO_NORM && p.K > std::min(kGemvMaxJ * kGemvThreads, kSimtMaxJ * kSimtThreads)) {
         ln.status = fail(OXG4_UNSUPPORTED, "hidden size above %d is not supported",
                          std::min(kGemvMaxJ * kGemvThreads, kSimtMaxJ * kSimtThreads));
@@ -798,7 +825,7 @@ static void launch_gemv(Launcher& ln, const char* kind, oxg4_cache* c, GemvArgs 
     const size_t limit = 226 * 1024;
     if (m->es == 2 && B > 1) {
         // tensor-core kernel: as many activation rows per pass as shared memory allows (at most 16)
-        auto need = [&](int nb) { return (((size_t)nb * p.K * 2 + 15) & ~(size_t)15) + 128 + (size_t)2 * kMmaRowsPerPass * kGemvWarps * nb * 4; };
+        auto need = [&](int nb) { return (((size_t)nb * mma_x_stride(p.K) * 2 + 15) & ~(size_t)15) + 128 + (size_t)2 * kMmaRowsPerPass * kGemvWarps * nb * 4; };
         int bpp = std::min(B, 16);
         while (bpp > 1 && need(bpp) > limit) --bpp;
         if (need(bpp) > limit) {
@@ -828,13 +855,13 @@ static void launch_gemv(Launcher& ln, const char* kind, oxg4_cache* c, GemvArgs 
 }
 
 template <typename KT>
-static void (*pick_attn(int D, int G))(const AttnArgs) {
-#define PA(DD)                                                     \
-    if (D == DD) {                                                 \
-        if (G == 1) return attn_decode_kernel<KT, DD, 1>;          \
-        if (G == 2) return attn_decode_kernel<KT, DD, 2>;          \
-        if (G == 4) return attn_decode_kernel<KT, DD, 4>;          \
-        if (G == 8) return attn_decode_kernel<KT, DD, 8>;          \
+static void (*pick_attn(int D, int G, bool cl))(const AttnArgs) {
+#define PA(DD)                                                                                     \
+    if (D == DD) {                                                                                 \
+        if (G == 1) return cl ? attn_decode_kernel<KT, DD, 1, true> : attn_decode_kernel<KT, DD, 1, false>; \
+        if (G == 2) return cl ? attn_decode_kernel<KT, DD, 2, true> : attn_decode_kernel<KT, DD, 2, false>; \
+        if (G == 4) return cl ? attn_decode_kernel<KT, DD, 4, true> : attn_decode_kernel<KT, DD, 4, false>; \
+        if (G == 8) return cl ? attn_decode_kernel<KT, DD, 8, true> : attn_decode_kernel<KT, DD, 8, false>; \
     }
     PA(64) PA(128) PA(256)
 #undef PA
@@ -928,9 +955,13 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
                 a.pf_bytes = (unsigned long long)m->I * H * m->es;
             }
             a.ts = ln.ts();
-            auto fn = c->kv_dtype == OXG4_BF16 ? pick_attn<uint16_t>(D, m->G) : pick_attn<float>(D, m->G);
-            const size_t smem = sizeof(float) * (size_t)(m->G * D + 2 * D + 2 * kAttnWarps * m->G + kAttnWarps * m->G * D);
+            const bool cl = c->attn_cluster && a.n_splits <= 8;
+            auto fn = c->kv_dtype == OXG4_BF16 ? pick_attn<uint16_t>(D, m->G, cl) : pick_attn<float>(D, m->G, cl);
+            const size_t smem = sizeof(float) * (size_t)(m->G * D + 2 * D + 2 * kAttnWarps * m->G + kAttnWarps * m->G * D +
+                                                         m->G * (D + 2));
+            ln.cluster_x = cl ? a.n_splits : 0;
             ln.go("attn", fn, dim3(a.n_splits, m->Nkv, B), dim3(kAttnThreads), smem, a);
+            ln.cluster_x = 0;
         }
         {   // O projection (decode.rs:159)
             GemvArgs a{};
