@@ -108,7 +108,7 @@ template <> DEVINL float kv_widen<uint16_t>(uint16_t v) { return __uint_as_float
 template <typename KT, int D, int G, bool CL>
 __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArgs a) {
     constexpr int EPT = D / 32;
-    constexpr int NW = kAttnWarps;
+    const int NW = blockDim.x >> 5;          // 16 warps when few CTAs exist (latency), 4 when many (occupancy)
     extern __shared__ __align__(16) float sm[];
     float* qs = sm;                          // [G][D]
     float* kcur = qs + G * D;                // [D]
@@ -309,7 +309,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
         }
         __syncthreads();
         float* my = CL ? cpart : part + (size_t)s * (G * (D + 2));
-        for (int idx = tid; idx < G * D; idx += kAttnThreads) {
+        for (int idx = tid; idx < G * D; idx += blockDim.x) {
             const int g = idx / D, d = idx % D;
             float M = -INFINITY;
             for (int w = 0; w < NW; ++w) M = fmaxf(M, wm[w * G + g]);
@@ -335,7 +335,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
             const int cs = (int)gridDim.x;
             const int per = (G * D + cs - 1) / cs;
             const int hi = min(G * D, (s + 1) * per);
-            for (int idx = s * per + tid; idx < hi; idx += kAttnThreads) {
+            for (int idx = s * per + tid; idx < hi; idx += blockDim.x) {
                 const int g = idx / D, d = idx % D;
                 float M = -INFINITY;
                 for (int sp = 0; sp < n_eff; ++sp)
@@ -371,7 +371,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
             float* sf = wacc;                         // [n_eff][G] m, then exp(m - M)
             float* sl = wacc + a.n_splits * G;        // [n_eff][G] l
             float* sL = sl + a.n_splits * G;          // [G]
-            for (int idx = tid; idx < n_eff * G; idx += kAttnThreads) {
+            for (int idx = tid; idx < n_eff * G; idx += blockDim.x) {
                 const int sp = idx / G, g = idx % G;
                 sf[idx] = __ldcg(part + (size_t)sp * PS + g * (D + 2) + D);
                 sl[idx] = __ldcg(part + (size_t)sp * PS + g * (D + 2) + D + 1);
@@ -393,7 +393,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
                 if (lane == 0) sL[g] = L;
             }
             __syncthreads();
-            for (int idx = tid; idx < G * D; idx += kAttnThreads) {
+            for (int idx = tid; idx < G * D; idx += blockDim.x) {
                 const int g = idx / D, d = idx % D;
                 const float* ps = part + g * (D + 2) + d;
                 float A = 0.0f;

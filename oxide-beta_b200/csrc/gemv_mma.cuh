@@ -25,7 +25,9 @@
 
 namespace oxg4 {
 
-constexpr int kMmaRowsPerPass = 64;      // rows of the block handled between two combines
+// rows of a CTA's block handled between two combines: 64 with up to 8 activation rows, 32 with up to
+// 16 (twice the accumulators per row group, so half the groups to stay inside 128 registers)
+__host__ __device__ constexpr int mma_rows_per_pass(int mb) { return mb == 16 ? 32 : 64; }
 
 // Row stride (elements) of the activation rows in shared memory: K padded so that consecutive rows
 // start 64 bytes apart modulo 128; the eight lanes of an LDS.128 phase (two batch rows x four column
@@ -115,6 +117,7 @@ template <int MB, int PRO, int EPI>
 __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvArgs a) {
     typedef uint16_t WT;
     constexpr int NW = kGemvWarps;
+    constexpr int RP = mma_rows_per_pass(MB);
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int K = a.K;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -175,9 +178,73 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvArg
 
     // ---- prologue: x[nb][K] (BF16) in shared memory ----
     if constexpr (PRO == PRO_PLAIN) {
-        for (int b = 0; b < nb; ++b)
-            for (int i = tid; i < K; i += kGemvThreads)
-                xs[(size_t)b * XS + i] = (uint16_t)f32_to_bf16_bits(a.in[(size_t)(b0 + b) * K + i]);
+        // four values per thread and step (K is a multiple of 8)
+        const int k4 = K >> 2;
+        for (int idx = tid; idx < nb * k4; idx += kGemvThreads) {
+            const int b = idx / k4, i = (idx - b * k4) << 2;
+            const float4 v = *reinterpret_cast<const float4*>(a.in + (size_t)(b0 + b) * K + i);
+            uint2 pk;
+            pk.x = f32_to_bf16_bits(v.x) | (f32_to_bf16_bits(v.y) << 16);
+            pk.y = f32_to_bf16_bits(v.z) | (f32_to_bf16_bits(v.w) << 16);
+            *reinterpret_cast<uint2*>(xs + (size_t)b * XS + i) = pk;
+        }
+    } else if (nb > 4) {
+        // many activation rows: one warp per row, so no block-wide barrier is paid per row
+        const bool writer = (blockIdx.x == 0);
+        const int k4 = K >> 2;
+        for (int b = warp; b < nb; b += NW) {
+            const size_t ro = (size_t)(b0 + b) * K;
+            uint32_t tok = 0;
+            if (a.embed != nullptr) {
+                tok = a.tokens[b0 + b];
+                if (tok == kInactiveToken) tok = 0;
+            }
+            float r = 0.0f;
+            if (a.embed == nullptr && a.raw != nullptr) {
+                float ss = 0.0f;
+                for (int i4 = lane; i4 < k4; i4 += 32) {
+                    const float4 t4 = *reinterpret_cast<const float4*>(a.raw + ro + 4 * i4);
+                    ss += t4.x * t4.x + t4.y * t4.y + t4.z * t4.z + t4.w * t4.w;
+                }
+                ss = warp_sum(ss);
+                r = 1.0f / sqrtf(ss / (float)K + a.eps);
+            }
+            auto hidden4 = [&](int i4) -> float4 {
+                float4 h;
+                if (a.embed != nullptr) {
+                    const uint2 e = *reinterpret_cast<const uint2*>((const uint16_t*)a.embed + (size_t)tok * K + 4 * i4);
+                    h = make_float4(bf16lo(e.x) * a.embed_scale, bf16hi(e.x) * a.embed_scale,
+                                    bf16lo(e.y) * a.embed_scale, bf16hi(e.y) * a.embed_scale);
+                } else {
+                    h = *reinterpret_cast<const float4*>(a.h_in + ro + 4 * i4);
+                    if (a.raw != nullptr) {
+                        const float4 t4 = *reinterpret_cast<const float4*>(a.raw + ro + 4 * i4);
+                        const float4 w4 = *reinterpret_cast<const float4*>(a.w_post + 4 * i4);
+                        h.x = (h.x + t4.x * r * w4.x) * a.scalar;
+                        h.y = (h.y + t4.y * r * w4.y) * a.scalar;
+                        h.z = (h.z + t4.z * r * w4.z) * a.scalar;
+                        h.w = (h.w + t4.w * r * w4.w) * a.scalar;
+                    }
+                }
+                return h;
+            };
+            float ss2 = 0.0f;
+            for (int i4 = lane; i4 < k4; i4 += 32) {
+                const float4 h = hidden4(i4);
+                if (writer) *reinterpret_cast<float4*>(a.h_out + ro + 4 * i4) = h;
+                ss2 += h.x * h.x + h.y * h.y + h.z * h.z + h.w * h.w;
+            }
+            ss2 = warp_sum(ss2);
+            const float r2 = 1.0f / sqrtf(ss2 / (float)K + a.eps);
+            for (int i4 = lane; i4 < k4; i4 += 32) {
+                const float4 h = hidden4(i4);
+                const float4 w4 = *reinterpret_cast<const float4*>(a.w_norm + 4 * i4);
+                uint2 pk;
+                pk.x = f32_to_bf16_bits(h.x * r2 * w4.x) | (f32_to_bf16_bits(h.y * r2 * w4.y) << 16);
+                pk.y = f32_to_bf16_bits(h.z * r2 * w4.z) | (f32_to_bf16_bits(h.w * r2 * w4.w) << 16);
+                *reinterpret_cast<uint2*>(xs + (size_t)b * XS + 4 * i4) = pk;
+            }
+        }
     } else {
         const bool writer = (blockIdx.x == 0);
         for (int b = 0; b < nb; ++b) {
@@ -245,17 +312,17 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvArg
     int pass = 0;
     bool preloaded = false;
     const WT* base = (rows_cta > 0) ? row_ptr(row_first + g) : (const WT*)a.W0;
-    for (int r0 = 0; r0 < rows_cta; r0 += kMmaRowsPerPass, ++pass) {
+    for (int r0 = 0; r0 < rows_cta; r0 += RP, ++pass) {
         const int rows_left = rows_cta - r0;
-        const int r1 = r0 + kMmaRowsPerPass;
+        const int r1 = r0 + RP;
         const WT* next_base = (r1 < rows_cta) ? row_ptr(row_first + r1 + g) : base;
         const int next_rows = max(0, rows_cta - r1);
-        const bool next_full = next_rows >= kMmaRowsPerPass;
-        float* pc = pieces + (size_t)(pass & 1) * kMmaRowsPerPass * NW * nb;
-        const int ng = (min(rows_left, kMmaRowsPerPass) + 7) >> 3;
-        if (ng > 4) {
-            mma_pass<MB, 8>(xs, XS, K, nb, nchunk, warp, g, t, base, gstride, rows_left, w, preloaded, next_base,
-                            next_rows, next_full, pc);
+        const bool next_full = next_rows >= RP;
+        float* pc = pieces + (size_t)(pass & 1) * RP * NW * nb;
+        const int ng = (min(rows_left, RP) + 7) >> 3;
+        if (RP == 64 && ng > 4) {
+            mma_pass<MB, (RP == 64 ? 8 : 4)>(xs, XS, K, nb, nchunk, warp, g, t, base, gstride, rows_left, w, preloaded,
+                                             next_base, next_rows, next_full, pc);
             preloaded = next_full;
         } else if (ng > 2) {
             mma_pass<MB, 4>(xs, XS, K, nb, nchunk, warp, g, t, base, gstride, rows_left, w, false, next_base, 0, false, pc);
@@ -269,7 +336,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvArg
         // at rows_here below
         __syncthreads();
         // combine in warp order and apply the epilogue
-        const int rows_here = min(kMmaRowsPerPass, rows_left);
+        const int rows_here = min(RP, rows_left);
         auto total = [&](int rl, int b) -> float {
             float s = 0.0f;
 #pragma unroll
@@ -289,11 +356,12 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvArg
                     gelu_mul(total(2 * pl, b), total(2 * pl + 1, b));
             }
         } else {
-            // thread -> (row tid % 64, batch rows tid / 64 and tid / 64 + 8)
-            const int rl = tid & 63;
+            // thread -> (row tid % RP, batch rows tid / RP (+ 8 when RP == 64))
+            constexpr int BH = kGemvThreads / RP;
+            const int rl = tid & (RP - 1);
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int b = (tid >> 6) + 8 * h;
+            for (int h = 0; h < 16 / BH; ++h) {
+                const int b = tid / RP + BH * h;
                 if (rl < rows_here && b < nb) {
                     const float v = total(rl, b);
                     const int vid = a.row_offset + row_first + r0 + rl;
@@ -312,17 +380,20 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvArg
     if constexpr (EPI == EPI_LOGITS) {
         __shared__ unsigned int s_last;
         __syncthreads();
-        Cand* wc = reinterpret_cast<Cand*>(pieces);        // [16 batch rows][64]
+        Cand* wc = reinterpret_cast<Cand*>(pieces);        // [16 batch rows][RP]
+        constexpr int BH = kGemvThreads / RP;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const int b = (tid >> 6) + 8 * h;
-            wc[b * 64 + (tid & 63)] = best[h];
+        for (int h = 0; h < 16 / BH; ++h) {
+            const int b = tid / RP + BH * h;
+            wc[b * RP + (tid & (RP - 1))] = best[h];
         }
         __syncthreads();
         if (warp < nb) {
-            Cand c = wc[warp * 64 + lane];
-            const Cand c2 = wc[warp * 64 + 32 + lane];
-            if (cand_better(c2, c)) c = c2;
+            Cand c = wc[warp * RP + lane];
+            if (RP == 64) {
+                const Cand c2 = wc[warp * RP + 32 + lane];
+                if (cand_better(c2, c)) c = c2;
+            }
             c = warp_best(c);
             if (lane == 0) a.blk_best[(size_t)(b0 + warp) * gridDim.x + blockIdx.x] = c;
         }

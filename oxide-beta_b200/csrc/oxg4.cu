@@ -825,7 +825,7 @@ static void launch_gemv(Launcher& ln, const char* kind, oxg4_cache* c, GemvArgs 
     const size_t limit = 226 * 1024;
     if (m->es == 2 && B > 1) {
         // tensor-core kernel: as many activation rows per pass as shared memory allows (at most 16)
-        auto need = [&](int nb) { return (((size_t)nb * mma_x_stride(p.K) * 2 + 15) & ~(size_t)15) + 128 + (size_t)2 * kMmaRowsPerPass * kGemvWarps * nb * 4; };
+        auto need = [&](int nb) { return (((size_t)nb * mma_x_stride(p.K) * 2 + 15) & ~(size_t)15) + 128 + (size_t)2 * mma_rows_per_pass(nb > 8 ? 16 : 8) * kGemvWarps * nb * 4; };
         int bpp = std::min(B, 16);
         while (bpp > 1 && need(bpp) > limit) --bpp;
         if (need(bpp) > limit) {
@@ -957,10 +957,12 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
             a.ts = ln.ts();
             const bool cl = c->attn_cluster && a.n_splits <= 8;
             auto fn = c->kv_dtype == OXG4_BF16 ? pick_attn<uint16_t>(D, m->G, cl) : pick_attn<float>(D, m->G, cl);
-            const size_t smem = sizeof(float) * (size_t)(m->G * D + 2 * D + 2 * kAttnWarps * m->G + kAttnWarps * m->G * D +
-                                                         m->G * (D + 2));
+            // few CTAs (one sequence): 16 warps each to cut latency; many CTAs: 4 warps each so that several
+            // fit on an SM (the kernel needs ~90 registers per thread)
+            const int aw = (a.n_splits * m->Nkv * B <= m->num_sms) ? kAttnWarps : 4;
+            const size_t smem = sizeof(float) * (size_t)(m->G * D + 2 * D + 2 * aw * m->G + aw * m->G * D + m->G * (D + 2));
             ln.cluster_x = cl ? a.n_splits : 0;
-            ln.go("attn", fn, dim3(a.n_splits, m->Nkv, B), dim3(kAttnThreads), smem, a);
+            ln.go("attn", fn, dim3(a.n_splits, m->Nkv, B), dim3(aw * 32), smem, a);
             ln.cluster_x = 0;
         }
         {   // O projection (decode.rs:159)
