@@ -202,6 +202,14 @@ int32_t oxg4_topk_noalloc(const float* logits_dev, int32_t rows, int32_t vocab, 
 int32_t oxg4_decode_trace(oxg4_model* model, oxg4_cache* cache, const uint32_t* tokens, const float* inject,
                           float* trace, float* logits);
 
+/* Stand-alone run of the tcgen05/TMEM batched projection kernel (csrc/tc_gemm.cuh) for its parity
+ * tests: out[B, N] = x[B, K] . W[N, K]^T with BF16 inputs given as bit patterns, f32 output, the
+ * contract of Cublas::linear_bf16_f32 (crates/oxide-torch-cuda/src/cublas.rs:101-153). 1 <= B <= 64,
+ * K a multiple of 8. ms (may be NULL) receives the device time of one launch. Returns OXG4_TIMEOUT
+ * if one of the kernel's bounded barrier waits ran out. */
+int32_t oxg4_debug_tc_gemm(const uint16_t* w_host, const uint16_t* x_host, int32_t N, int32_t K, int32_t B,
+                           float* out_host, float* ms);
+
 /* Diagnostics (no counterpart in the reference): when the environment variable OXG4_TIMELINE is
  * set before oxg4_model_create, every kernel of a step stamps the GPU's nanosecond timer at entry,
  * after its dependency wait, after its prologue and at exit. Copies the stamps of the most recent

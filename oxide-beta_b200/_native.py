@@ -77,6 +77,8 @@ SYMBOLS = {
     "oxg4_topk_noalloc": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_float, C.c_int32, C.c_void_p,
                                       C.c_void_p, C.c_void_p]),
     "oxg4_decode_trace": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "oxg4_debug_tc_gemm": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
+                                       C.POINTER(C.c_float)]),
     "oxg4_debug_timeline": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32]),
     "oxg4_generate": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64, C.POINTER(GenerationConfigC), C.c_int32,
                                   TOKEN_CALLBACK, C.c_void_p, C.c_void_p, C.POINTER(C.c_int64)]),

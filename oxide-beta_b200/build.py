@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "liboxg4.so")
 SOURCES = ["oxg4.cu"]
-HEADERS = ["common.cuh", "gemv.cuh", "gemv_mma.cuh", "attention.cuh", "sampling.cuh"]
+HEADERS = ["common.cuh", "gemv.cuh", "gemv_mma.cuh", "attention.cuh", "sampling.cuh", "tc_gemm.cuh", "tp.h"]
 
 
 def _newest_source() -> float:

@@ -23,6 +23,7 @@
 #include "gemv.cuh"
 #include "gemv_mma.cuh"
 #include "sampling.cuh"
+#include "tc_gemm.cuh"
 #include "tp.h"
 
 using namespace oxg4;
@@ -1537,4 +1538,101 @@ extern "C" int32_t oxg4_topk_noalloc(const float* logits_dev, int32_t rows, int3
                                                                                         ids_dev, scores_dev);
     CK(cudaGetLastError());
     return OXG4_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// tcgen05 projection: stand-alone entry used by the parity tests of csrc/tc_gemm.cuh
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int32_t encode_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        CK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+        if (!p || q != cudaDriverEntryPointSuccess) return fail(OXG4_CUDA, "Gemma 4 CUDA error: cuTensorMapEncodeTiled is unavailable");
+        fn = (EncodeTiledFn)p;
+    }
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kTcTileK, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(OXG4_CUDA, "Gemma 4 CUDA error: cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return OXG4_OK;
+}
+
+// out[B, N] = x[B, K] . W[N, K]^T on device pointers (BF16 in, f32 out), B <= 64, K a multiple of 8.
+static int32_t tc_gemm_launch(const void* w_dev, const void* x_dev, int N, int K, int B, float* out_dev, int* err_dev,
+                              int num_sms, cudaStream_t st) {
+    if (B < 1 || B > 64 || K % 8 != 0) return fail(OXG4_INVALID_SHAPE, "tcgen05 projection: 1..64 rows and K %% 8 == 0 required");
+    const int bn = B <= 16 ? 16 : (B <= 32 ? 32 : 64);
+    CUtensorMap mw, mx;
+    TRY(encode_bf16_2d(&mw, w_dev, (uint64_t)N, (uint64_t)K, kTcTileM));
+    TRY(encode_bf16_2d(&mx, x_dev, (uint64_t)B, (uint64_t)K, (uint32_t)bn));
+    TcGemmArgs a{N, K, B, out_dev, err_dev};
+    const int tiles = (N + kTcTileM - 1) / kTcTileM;
+    const dim3 grid(std::min(tiles, num_sms));
+    if (bn == 16) {
+        TRY(allow_big_smem(tc_gemm_kernel<16>));
+        tc_gemm_kernel<16><<<grid, kTcThreads, tc_gemm_smem_bytes<16>(), st>>>(mw, mx, a);
+    } else if (bn == 32) {
+        TRY(allow_big_smem(tc_gemm_kernel<32>));
+        tc_gemm_kernel<32><<<grid, kTcThreads, tc_gemm_smem_bytes<32>(), st>>>(mw, mx, a);
+    } else {
+        TRY(allow_big_smem(tc_gemm_kernel<64>));
+        tc_gemm_kernel<64><<<grid, kTcThreads, tc_gemm_smem_bytes<64>(), st>>>(mw, mx, a);
+    }
+    CK(cudaGetLastError());
+    return OXG4_OK;
+}
+
+extern "C" int32_t oxg4_debug_tc_gemm(const uint16_t* w_host, const uint16_t* x_host, int32_t N, int32_t K, int32_t B,
+                                      float* out_host, float* ms_or_null) {
+    if (!w_host || !x_host || !out_host) return fail(OXG4_INVALID_ARGUMENT, "null argument");
+    void *w = nullptr, *x = nullptr;
+    float* o = nullptr;
+    int* e = nullptr;
+    cudaDeviceProp prop;
+    int dev = 0;
+    CK(cudaGetDevice(&dev));
+    CK(cudaGetDeviceProperties(&prop, dev));
+    CK(cudaMalloc(&w, (size_t)N * K * 2));
+    CK(cudaMalloc(&x, (size_t)B * K * 2));
+    CK(cudaMalloc(&o, (size_t)B * N * 4));
+    CK(cudaMalloc(&e, 4));
+    CK(cudaMemcpy(w, w_host, (size_t)N * K * 2, cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(x, x_host, (size_t)B * K * 2, cudaMemcpyHostToDevice));
+    CK(cudaMemset(o, 0xff, (size_t)B * N * 4));
+    CK(cudaMemset(e, 0, 4));
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    int32_t s = tc_gemm_launch(w, x, N, K, B, o, e, prop.multiProcessorCount, 0);       // warm-up + result
+    if (s == OXG4_OK) {
+        cudaEventRecord(e0, 0);
+        s = tc_gemm_launch(w, x, N, K, B, o, e, prop.multiProcessorCount, 0);
+        cudaEventRecord(e1, 0);
+    }
+    int err = 0;
+    if (s == OXG4_OK && cudaDeviceSynchronize() != cudaSuccess) s = fail(OXG4_CUDA, "Gemma 4 CUDA error: tcgen05 projection failed: %s", cudaGetErrorString(cudaGetLastError()));
+    if (s == OXG4_OK) {
+        cudaMemcpy(&err, e, 4, cudaMemcpyDeviceToHost);
+        if (err) s = fail(OXG4_TIMEOUT, "tcgen05 projection: a bounded barrier wait ran out (code %d)", err);
+    }
+    if (s == OXG4_OK) {
+        cudaMemcpy(out_host, o, (size_t)B * N * 4, cudaMemcpyDeviceToHost);
+        float ms = 0;
+        cudaEventElapsedTime(&ms, e0, e1);
+        if (ms_or_null) *ms_or_null = ms;
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    cudaFree(w); cudaFree(x); cudaFree(o); cudaFree(e);
+    return s;
 }
