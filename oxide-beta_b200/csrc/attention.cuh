@@ -27,8 +27,10 @@ constexpr int kAttnThreads = 512;
 constexpr int kAttnWarps = kAttnThreads / 32;
 
 struct AttnArgs {
-    const float* qkv;        // [B, qkv_n] QKV projection output, columns q | k | v
+    const float* qkv;        // [qkv_splits, B, qkv_n] QKV projection output (K-split partials), columns q | k | v
     int qkv_n;
+    int qkv_splits;          // partials to add (1 for the small-batch kernels)
+    uint16_t* out_bf16;      // optional BF16 copy of the output, [B, Nq * D] (input of the tcgen05 O projection)
     int B, Nq, Nkv;
     const float* q_norm;     // [D]
     const float* k_norm;     // [D]
@@ -177,7 +179,9 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
             float ss = 0.0f;
 #pragma unroll
             for (int e = 0; e < EPT; ++e) {
-                const float v = a.qkv[(size_t)b * a.qkv_n + col + lane * EPT + e];
+                float v = 0.0f;
+                for (int sp = 0; sp < a.qkv_splits; ++sp)
+                    v += a.qkv[((size_t)sp * a.B + b) * a.qkv_n + col + lane * EPT + e];
                 t[e] = v;
                 ss += v * v;
             }
@@ -349,7 +353,12 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
                     A += e * ps[d];
                     L += e * ps[D + 1];
                 }
-                a.out[(size_t)b * a.Nq * D + (size_t)(kvh * G + g) * D + d] = A / L;
+                {
+                    const size_t oi = (size_t)b * a.Nq * D + (size_t)(kvh * G + g) * D + d;
+                    const float ov = A / L;
+                    a.out[oi] = ov;
+                    if (a.out_bf16) a.out_bf16[oi] = (uint16_t)f32_to_bf16_bits(ov);
+                }
             }
         }
         cluster.sync();                                    // no CTA leaves while a peer may still read its partial
@@ -399,7 +408,12 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
                 float A = 0.0f;
 #pragma unroll 8
                 for (int sp = 0; sp < n_eff; ++sp) A += sf[sp * G + g] * __ldcg(ps + (size_t)sp * PS);
-                a.out[(size_t)b * a.Nq * D + (size_t)(kvh * G + g) * D + d] = A / sL[g];
+                {
+                    const size_t oi = (size_t)b * a.Nq * D + (size_t)(kvh * G + g) * D + d;
+                    const float ov = A / sL[g];
+                    a.out[oi] = ov;
+                    if (a.out_bf16) a.out_bf16[oi] = (uint16_t)f32_to_bf16_bits(ov);
+                }
             }
         }
         if (tid == 0) a.ticket[b * a.Nkv + kvh] = 0u;

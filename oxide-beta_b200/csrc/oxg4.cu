@@ -23,6 +23,7 @@
 #include "gemv.cuh"
 #include "gemv_mma.cuh"
 #include "sampling.cuh"
+#include "batch_ops.cuh"
 #include "tc_gemm.cuh"
 #include "tp.h"
 
@@ -533,6 +534,12 @@ struct oxg4_cache {
     std::vector<void*> owned;                 // every device allocation, for destroy
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     unsigned long long* ts_buf = nullptr;     // [kMaxTimeline][4] optional device timeline
+    // tcgen05 path (eight or more sequences): BF16 activations, K-split partial outputs, error flag
+    bool use_tc = false;
+    int s_qkv = 1, s_o = 1, s_gu = 1, s_down = 1;
+    uint16_t *x_h = nullptr, *x_a = nullptr, *x_i = nullptr;
+    float *qkv_part = nullptr, *o_part = nullptr, *gu_part = nullptr, *down_part = nullptr;
+    int* tc_err = nullptr;
 };
 constexpr int kMaxTimeline = 1024;
 
@@ -546,6 +553,9 @@ static int32_t dalloc(oxg4_cache* c, T** p, size_t count, bool zero = true) {
     *p = (T*)d;
     return OXG4_OK;
 }
+
+static int32_t tc_gemm_setup();
+static int tc_pick_splits(int tiles, int kblocks, int grid, int B, int n_total, int K);
 
 static int32_t cache_build(oxg4_cache* c) {
     oxg4_model* m = c->m;
@@ -627,6 +637,26 @@ static int32_t cache_build(oxg4_cache* c) {
     TRY(dalloc(c, &c->topk_ids, (size_t)B * 64));
     TRY(dalloc(c, &c->topk_scores, (size_t)B * 64));
     if (m->timeline) TRY(dalloc(c, &c->ts_buf, (size_t)kMaxTimeline * 4));
+    c->use_tc = m->es == 2 && B >= 8 && B <= 64 && getenv("OXG4_DISABLE_TCGEN05") == nullptr;
+    if (c->use_tc) {
+        TRY(tc_gemm_setup());
+        const int sms = m->num_sms;
+        auto tiles = [](int n) { return (n + kTcTileM - 1) / kTcTileM; };
+        auto kbs = [](int k) { return (k + kTcTileK - 1) / kTcTileK; };
+        const int nqkv = m->p_qkv.N, qw = m->Nq * D;
+        c->s_qkv = tc_pick_splits(tiles(nqkv), kbs(H), sms, B, nqkv, H);
+        c->s_o = tc_pick_splits(tiles(H), kbs(qw), sms, B, H, qw);
+        c->s_gu = tc_pick_splits(2 * tiles(m->I), kbs(H), sms, B, 2 * m->I, H);
+        c->s_down = tc_pick_splits(tiles(H), kbs(m->I), sms, B, H, m->I);
+        TRY(dalloc(c, &c->x_h, (size_t)B * H));
+        TRY(dalloc(c, &c->x_a, (size_t)B * qw));
+        TRY(dalloc(c, &c->x_i, (size_t)B * m->I));
+        TRY(dalloc(c, &c->qkv_part, (size_t)c->s_qkv * B * nqkv));
+        TRY(dalloc(c, &c->o_part, (size_t)c->s_o * B * H));
+        TRY(dalloc(c, &c->gu_part, (size_t)c->s_gu * B * 2 * m->I));
+        TRY(dalloc(c, &c->down_part, (size_t)c->s_down * B * H));
+        TRY(dalloc(c, &c->tc_err, 1));
+    }
     CK(cudaMallocHost(&c->h_tokens, sizeof(uint32_t) * B));
     CK(cudaMallocHost(&c->h_ctl, sizeof(StepCtl)));
     CK(cudaMallocHost(&c->h_ids, sizeof(uint32_t) * B * 64));
@@ -713,6 +743,105 @@ extern "C" int32_t oxg4_cache_reset(oxg4_cache* c) {
 }
 
 // ------------------------------------------------------------------------------------------------
+// tcgen05 projection: tensor maps, split choice, launch
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int32_t encode_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        CK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+        if (!p || q != cudaDriverEntryPointSuccess) return fail(OXG4_CUDA, "Gemma 4 CUDA error: cuTensorMapEncodeTiled is unavailable");
+        fn = (EncodeTiledFn)p;
+    }
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kTcTileK, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(OXG4_CUDA, "Gemma 4 CUDA error: cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return OXG4_OK;
+}
+
+// out[B, N] = x[B, K] . W[N, K]^T on device pointers (BF16 in, f32 out), B <= 64, K a multiple of 8.
+// K-splits for a tcgen05 projection: work units = tiles * S should fill the grid in whole rounds;
+// the S partial outputs cost S * B * n * 8 bytes of extra traffic, kept under ~30 % of the weights.
+static int tc_pick_splits(int tiles, int kblocks, int grid, int B, int n_total, int K) {
+    int best = 1;
+    double best_score = -1.0;
+    for (int S = 1; S <= 16 && S <= kblocks / 2 + (kblocks < 2 ? 1 : 0); ++S) {
+        const double units = (double)tiles * S;
+        const double rounds = std::ceil(units / grid);
+        const double eff = units / (rounds * grid);
+        const double extra = S == 1 ? 0.0 : (double)S * B * n_total * 8.0 / ((double)n_total * K * 2.0);
+        if (extra > 0.3) break;
+        const double score = eff / (1.0 + extra);
+        if (score > best_score + 1e-9) { best_score = score; best = S; }
+    }
+    // no split may be empty: an empty unit would hand stale accumulator columns to the epilogue
+    const int kbps = (kblocks + best - 1) / best;
+    return (kblocks + kbps - 1) / kbps;
+}
+
+// out[S, B, n_mats * N] = per-split partials of x[B, K] . W_m[N, K]^T on device pointers (BF16 in, f32 out).
+static int32_t tc_gemm_launch(const void* w_dev, const void* w1_dev, const void* x_dev, int N, int K, int B, int S,
+                              float* out_dev, int ld, int col0, int* err_dev, int num_sms, cudaStream_t st, bool pdl) {
+    if (B < 1 || B > 64 || K % 8 != 0) return fail(OXG4_INVALID_SHAPE, "tcgen05 projection: 1..64 rows and K %% 8 == 0 required");
+    const int bn = B <= 16 ? 16 : (B <= 32 ? 32 : 64);
+    CUtensorMap mw, mw1, mx;
+    TRY(encode_bf16_2d(&mw, w_dev, (uint64_t)N, (uint64_t)K, kTcTileM));
+    TRY(encode_bf16_2d(&mw1, w1_dev ? w1_dev : w_dev, (uint64_t)N, (uint64_t)K, kTcTileM));
+    TRY(encode_bf16_2d(&mx, x_dev, (uint64_t)B, (uint64_t)K, (uint32_t)bn));
+    const int kblocks = (K + kTcTileK - 1) / kTcTileK;
+    TcGemmArgs a{};
+    a.N = N; a.K = K; a.B = B;
+    a.n_mats = w1_dev ? 2 : 1;
+    a.S = S;
+    a.kb_per_split = (kblocks + S - 1) / S;
+    a.out = out_dev;
+    a.ld = ld;
+    a.col0 = col0;
+    a.err = err_dev;
+    const int units = ((N + kTcTileM - 1) / kTcTileM) * a.n_mats * S;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(std::min(units, num_sms));
+    cfg.blockDim = dim3(kTcThreads);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    cudaError_t e;
+    if (bn == 16) {
+        cfg.dynamicSmemBytes = tc_gemm_smem_bytes<16>();
+        e = cudaLaunchKernelEx(&cfg, tc_gemm_kernel<16>, mw, mw1, mx, a);
+    } else if (bn == 32) {
+        cfg.dynamicSmemBytes = tc_gemm_smem_bytes<32>();
+        e = cudaLaunchKernelEx(&cfg, tc_gemm_kernel<32>, mw, mw1, mx, a);
+    } else {
+        cfg.dynamicSmemBytes = tc_gemm_smem_bytes<64>();
+        e = cudaLaunchKernelEx(&cfg, tc_gemm_kernel<64>, mw, mw1, mx, a);
+    }
+    CK(e);
+    return OXG4_OK;
+}
+
+static int32_t tc_gemm_setup() {
+    TRY(allow_big_smem(tc_gemm_kernel<16>));
+    TRY(allow_big_smem(tc_gemm_kernel<32>));
+    TRY(allow_big_smem(tc_gemm_kernel<64>));
+    return OXG4_OK;
+}
+
+
+// ------------------------------------------------------------------------------------------------
 // one decode step
 // ------------------------------------------------------------------------------------------------
 struct Launcher {
@@ -758,6 +887,26 @@ struct Launcher {
             status = fail(OXG4_CUDA, "Gemma 4 CUDA error: launch of %s failed: %s", kind, cudaGetErrorString(e));
             return;
         }
+        if (m->profiling) {
+            cudaEventRecord(e1, m->stream);
+            m->prof_events.push_back({kind, {e0, e1}});
+        }
+        ++kernels;
+    }
+
+    // tcgen05 batched projection (csrc/tc_gemm.cuh): partials [S, B, ld] of x . W^T
+    void tc(const char* kind, oxg4_cache* c, const void* w0, const void* w1, const uint16_t* x, int N, int K, int S,
+            float* out, int ld, int col0) {
+        if (status != OXG4_OK) return;
+        cudaEvent_t e0 = nullptr, e1 = nullptr;
+        if (m->profiling) {
+            cudaEventCreate(&e0);
+            cudaEventCreate(&e1);
+            cudaEventRecord(e0, m->stream);
+        }
+        status = tc_gemm_launch(w0, w1, x, N, K, c->B, S, out, ld, col0, c->tc_err, m->num_sms, m->stream,
+                                m->use_pdl && !m->profiling);
+        if (status != OXG4_OK) return;
         if (m->profiling) {
             cudaEventRecord(e1, m->stream);
             m->prof_events.push_back({kind, {e0, e1}});
@@ -883,8 +1032,107 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
     const int B = c->B, L = m->cfg.num_hidden_layers, H = m->H, D = m->D;
     ln.go("step_begin", step_begin_kernel, dim3(1), dim3(128), 0, B, m->V,
           (const uint32_t*)c->tokens, c->seen, (const StepCtl*)c->ctl);
+    // q/k norm + RoPE + v norm + KV append + attention (decode.rs:99-157)
+    auto launch_attn = [&](int l, const float* qkv, int qkv_splits, uint16_t* out_bf16) {
+        const LayerPlan& p = m->layers[l];
+        AttnArgs a{};
+        a.qkv = qkv;
+        a.qkv_splits = qkv_splits;
+        a.out_bf16 = out_bf16;
+        a.qkv_n = m->p_qkv.N;
+        a.B = B;
+        a.Nq = m->Nq;
+        a.Nkv = m->Nkv;
+        a.q_norm = p.q_norm;
+        a.k_norm = p.k_norm;
+        a.inv_freq = p.inv_freq;
+        a.rotary_half = p.rotary_dim / 2;
+        a.eps = m->cfg.rms_norm_eps;
+        a.pos = c->pos;
+        a.tokens = c->tokens;
+        a.kpool = c->kpool[l];
+        a.vpool = c->vpool[l];
+        a.page_table = p.sliding ? c->pt_slide : c->pt_full;
+        a.pages_per_seq = p.sliding ? c->pps_slide : c->pps_full;
+        a.page_tokens = c->PT;
+        a.cap = p.sliding ? c->cap_slide : c->cap_full;
+        a.n_splits = p.sliding ? c->splits_slide : c->splits_full;
+        a.min_split = c->min_split;
+        a.part = c->attn_part;
+        a.ticket = c->attn_ticket;
+        a.out = c->attn_out;
+        if (m->far_prefetch) {
+            a.pf_ptr = p.wup;
+            a.pf_bytes = (unsigned long long)m->I * H * m->es;
+        }
+        a.ts = ln.ts();
+        const bool cl = c->attn_cluster && a.n_splits <= 8;
+        auto fn = c->kv_dtype == OXG4_BF16 ? pick_attn<uint16_t>(D, m->G, cl) : pick_attn<float>(D, m->G, cl);
+        // few CTAs (one sequence): 16 warps each to cut latency; many CTAs: 4 warps each so that several
+        // fit on an SM (the kernel needs ~90 registers per thread)
+        const int aw = (a.n_splits * m->Nkv * B <= m->num_sms) ? kAttnWarps : 4;
+        const size_t smem = sizeof(float) * (size_t)(m->G * D + 2 * D + 2 * aw * m->G + aw * m->G * D + m->G * (D + 2));
+        ln.cluster_x = cl ? a.n_splits : 0;
+        ln.go("attn", fn, dim3(a.n_splits, m->Nkv, B), dim3(aw * 32), smem, a);
+        ln.cluster_x = 0;
+    };
     for (int l = 0; l < L; ++l) {
         const LayerPlan& p = m->layers[l];
+        if (c->use_tc) {
+            // ---- eight or more sequences: tcgen05 projections fed by TMA, per-row kernels around them ----
+            const int nqkv = m->p_qkv.N, qw = m->Nq * D;
+            auto copy_trace_tc = [&]() {
+                if (tr && ln.status == OXG4_OK &&
+                    cudaMemcpyAsync(tr->trace_dev + (size_t)l * B * H, c->hB, sizeof(float) * B * H,
+                                    cudaMemcpyDeviceToDevice, m->stream) != cudaSuccess)
+                    ln.status = fail(OXG4_CUDA, "Gemma 4 CUDA error: trace copy failed");
+            };
+            RowsNormArgs n{};
+            n.B = B; n.H = H;
+            n.h_in = c->hA; n.h_out = c->hB;
+            n.w_norm = p.input_ln;
+            n.scalar = 1.0f;
+            n.eps = m->cfg.rms_norm_eps;
+            n.x = c->x_h;
+            if (l == 0) {
+                n.embed = (const uint16_t*)m->embed;
+                n.tokens = c->tokens;
+                n.embed_scale = sqrtf((float)H);
+            } else {
+                n.raw = c->down_part;
+                n.raw_splits = c->s_down;
+                n.w_post = m->layers[l - 1].post_ff_ln;
+                n.scalar = m->layers[l - 1].layer_scalar;
+            }
+            ln.go("norm", rows_norm_kernel, dim3(B), dim3(kRowsThreads), 0, n);
+            copy_trace_tc();
+            if (tr && tr->inject_dev) {
+                RowsNormArgs f = n;                      // layer-wise teacher forcing: forced input, nothing pending
+                f.embed = nullptr; f.raw = nullptr; f.w_post = nullptr; f.scalar = 1.0f;
+                f.h_in = tr->inject_dev + (size_t)l * B * H;
+                ln.go("norm", rows_norm_kernel, dim3(B), dim3(kRowsThreads), 0, f);
+            }
+            ln.tc("qkv", c, p.wqkv, nullptr, c->x_h, nqkv, H, c->s_qkv, c->qkv_part, nqkv, 0);
+            launch_attn(l, c->qkv_part, c->s_qkv, c->x_a);
+            ln.tc("o", c, p.wo, nullptr, c->x_a, H, qw, c->s_o, c->o_part, H, 0);
+            ln.allreduce(c->o_part, (size_t)c->s_o * B * H);
+            RowsNormArgs n2{};
+            n2.B = B; n2.H = H;
+            n2.h_in = c->hB; n2.h_out = c->hA;
+            n2.raw = c->o_part; n2.raw_splits = c->s_o;
+            n2.w_post = p.post_attn_ln;
+            n2.scalar = 1.0f;
+            n2.w_norm = p.pre_ff_ln;
+            n2.eps = m->cfg.rms_norm_eps;
+            n2.x = c->x_h;
+            ln.go("norm", rows_norm_kernel, dim3(B), dim3(kRowsThreads), 0, n2);
+            ln.tc("gateup", c, p.wgate, p.wup, c->x_h, m->I, H, c->s_gu, c->gu_part, 2 * m->I, 0);
+            ln.go("geglu", geglu_rows_kernel, dim3((m->I + kRowsThreads - 1) / kRowsThreads, B), dim3(kRowsThreads), 0, B,
+                  m->I, (const float*)c->gu_part, c->s_gu, c->x_i);
+            ln.tc("down", c, p.wdown, nullptr, c->x_i, H, m->I, c->s_down, c->down_part, H, 0);
+            ln.allreduce(c->down_part, (size_t)c->s_down * B * H);
+            continue;
+        }
         {   // input norm + QKV projection (decode.rs:61-98); also closes the previous layer
             GemvArgs a{};
             a.W0 = p.wqkv;
@@ -926,46 +1174,7 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
                 launch_gemv(ln, "qkv", c, a, m->p_qkv, PRO_NORM, EPI_STORE);
             }
         }
-        {   // q/k norm + RoPE + v norm + KV append + attention (decode.rs:99-157)
-            AttnArgs a{};
-            a.qkv = c->qkv_raw;
-            a.qkv_n = m->p_qkv.N;
-            a.B = B;
-            a.Nq = m->Nq;
-            a.Nkv = m->Nkv;
-            a.q_norm = p.q_norm;
-            a.k_norm = p.k_norm;
-            a.inv_freq = p.inv_freq;
-            a.rotary_half = p.rotary_dim / 2;
-            a.eps = m->cfg.rms_norm_eps;
-            a.pos = c->pos;
-            a.tokens = c->tokens;
-            a.kpool = c->kpool[l];
-            a.vpool = c->vpool[l];
-            a.page_table = p.sliding ? c->pt_slide : c->pt_full;
-            a.pages_per_seq = p.sliding ? c->pps_slide : c->pps_full;
-            a.page_tokens = c->PT;
-            a.cap = p.sliding ? c->cap_slide : c->cap_full;
-            a.n_splits = p.sliding ? c->splits_slide : c->splits_full;
-            a.min_split = c->min_split;
-            a.part = c->attn_part;
-            a.ticket = c->attn_ticket;
-            a.out = c->attn_out;
-            if (m->far_prefetch) {
-                a.pf_ptr = p.wup;
-                a.pf_bytes = (unsigned long long)m->I * H * m->es;
-            }
-            a.ts = ln.ts();
-            const bool cl = c->attn_cluster && a.n_splits <= 8;
-            auto fn = c->kv_dtype == OXG4_BF16 ? pick_attn<uint16_t>(D, m->G, cl) : pick_attn<float>(D, m->G, cl);
-            // few CTAs (one sequence): 16 warps each to cut latency; many CTAs: 4 warps each so that several
-            // fit on an SM (the kernel needs ~90 registers per thread)
-            const int aw = (a.n_splits * m->Nkv * B <= m->num_sms) ? kAttnWarps : 4;
-            const size_t smem = sizeof(float) * (size_t)(m->G * D + 2 * D + 2 * aw * m->G + aw * m->G * D + m->G * (D + 2));
-            ln.cluster_x = cl ? a.n_splits : 0;
-            ln.go("attn", fn, dim3(a.n_splits, m->Nkv, B), dim3(aw * 32), smem, a);
-            ln.cluster_x = 0;
-        }
+        launch_attn(l, c->qkv_raw, 1, nullptr);
         {   // O projection (decode.rs:159)
             GemvArgs a{};
             a.W0 = p.wo;
@@ -1009,7 +1218,35 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
             ln.allreduce(c->down_raw, (size_t)B * H);
         }
     }
-    if (kind != STEP_PREFILL) {
+    if (kind != STEP_PREFILL && c->use_tc) {
+        RowsNormArgs n{};
+        n.B = B; n.H = H;
+        n.h_in = c->hA; n.h_out = c->hB;
+        n.raw = c->down_part; n.raw_splits = c->s_down;
+        n.w_post = m->layers[L - 1].post_ff_ln;
+        n.scalar = m->layers[L - 1].layer_scalar;
+        n.w_norm = m->final_norm;
+        n.eps = m->cfg.rms_norm_eps;
+        n.x = c->x_h;
+        ln.go("norm", rows_norm_kernel, dim3(B), dim3(kRowsThreads), 0, n);
+        if (tr && ln.status == OXG4_OK &&
+            cudaMemcpyAsync(tr->trace_dev + (size_t)L * B * H, c->hB, sizeof(float) * B * H, cudaMemcpyDeviceToDevice,
+                            m->stream) != cudaSuccess)
+            ln.status = fail(OXG4_CUDA, "Gemma 4 CUDA error: trace copy failed");
+        if (m->tp > 1 && cudaMemsetAsync(c->logits, 0, sizeof(float) * (size_t)B * m->V, m->stream) != cudaSuccess)
+            ln.status = fail(OXG4_CUDA, "Gemma 4 CUDA error: cudaMemsetAsync failed");
+        ln.tc("lmhead", c, (const char*)m->embed + (size_t)m->v0 * H * m->es, nullptr, c->x_h, m->Vloc, H, 1, c->logits,
+              m->V, m->v0);
+        ln.allreduce(c->logits, (size_t)B * m->V);
+        // top-k over the full logits (k = 1 is the arg-max the greedy loop feeds back)
+        const int chunks = (m->V + kTopkChunk - 1) / kTopkChunk;
+        const int k = (kind == STEP_TOPK) ? top_k : 1;
+        ln.go("topk1", topk_stage1_kernel, dim3(chunks, B), dim3(kTopkThreads), 0, (const float*)c->logits, m->V,
+              (const uint8_t*)c->seen, penalty, k, c->topk_stage);
+        ln.go("topk2", topk_stage2_kernel, dim3(1, B), dim3(kTopkThreads), (size_t)chunks * k * 8,
+              (const Cand*)c->topk_stage, chunks * k, k, k == 1 ? c->best_ids : c->topk_ids,
+              k == 1 ? c->best_scores : c->topk_scores);
+    } else if (kind != STEP_PREFILL) {
         // post-FF norm + residual + layer_scalar of the last layer, final norm, tied LM head with
         // fused arg-max (decode.rs:495-508, kernel_module.rs:1988-2075)
         GemvArgs a{};
@@ -1130,6 +1367,18 @@ static void advance_host(oxg4_cache* c, const uint32_t* tokens, int steps = 1) {
         if (tokens[b] != kInactiveToken) c->pos_host[b] += steps;
 }
 
+// the tcgen05 kernels raise a device flag instead of hanging when one of their bounded waits runs out
+static int32_t check_tc(oxg4_cache* c) {
+    if (!c->use_tc) return OXG4_OK;
+    int err = 0;
+    CK(cudaMemcpy(&err, c->tc_err, sizeof err, cudaMemcpyDeviceToHost));
+    if (err) {
+        cudaMemset(c->tc_err, 0, sizeof err);
+        return fail(OXG4_TIMEOUT, "tcgen05 projection: a bounded barrier wait ran out (code %d)", err);
+    }
+    return OXG4_OK;
+}
+
 static void softcap(float* v, size_t n, float cap) {     // mod.rs:573-579
     if (cap > 0.0f)
         for (size_t i = 0; i < n; ++i) v[i] = tanhf(v[i] / cap) * cap;
@@ -1142,6 +1391,7 @@ extern "C" int32_t oxg4_prefill_token(oxg4_model* m, oxg4_cache* c, const uint32
     TRY(stage_inputs(c, tokens, 0, 0));
     TRY(launch_step(c, STEP_PREFILL, 0, 1.0f));
     CK(cudaStreamSynchronize(m->stream));
+    TRY(check_tc(c));
     advance_host(c, tokens);
     return OXG4_OK;
 }
@@ -1154,6 +1404,7 @@ extern "C" int32_t oxg4_decode_logits(oxg4_model* m, oxg4_cache* c, const uint32
     TRY(launch_step(c, STEP_LOGITS, 1, 1.0f));
     CK(cudaMemcpyAsync(logits, c->logits, sizeof(float) * (size_t)c->B * m->V, cudaMemcpyDeviceToHost, m->stream));
     CK(cudaStreamSynchronize(m->stream));
+    TRY(check_tc(c));
     softcap(logits, (size_t)c->B * m->V, m->cfg.final_logit_softcapping);
     advance_host(c, tokens);
     return OXG4_OK;
@@ -1173,6 +1424,7 @@ extern "C" int32_t oxg4_decode_topk(oxg4_model* m, oxg4_cache* c, const uint32_t
     CK(cudaMemcpyAsync(c->h_ids, src_i, sizeof(uint32_t) * c->B * top_k, cudaMemcpyDeviceToHost, m->stream));
     CK(cudaMemcpyAsync(c->h_scores, src_s, sizeof(float) * c->B * top_k, cudaMemcpyDeviceToHost, m->stream));
     CK(cudaStreamSynchronize(m->stream));
+    TRY(check_tc(c));
     memcpy(ids, c->h_ids, sizeof(uint32_t) * c->B * top_k);
     memcpy(scores, c->h_scores, sizeof(float) * c->B * top_k);
     softcap(scores, (size_t)c->B * top_k, m->cfg.final_logit_softcapping);
@@ -1228,6 +1480,7 @@ extern "C" int32_t oxg4_decode_greedy(oxg4_model* m, oxg4_cache* c, const uint32
     CK(cudaEventRecord(c->ev1, m->stream));
     CK(cudaMemcpyAsync(out_ids, c->history, sizeof(uint32_t) * (size_t)steps * c->B, cudaMemcpyDeviceToHost, m->stream));
     CK(cudaStreamSynchronize(m->stream));
+    TRY(check_tc(c));
     float ms = 0;
     CK(cudaEventElapsedTime(&ms, c->ev0, c->ev1));
     if (ms_per_step) *ms_per_step = ms / steps;
@@ -1246,6 +1499,7 @@ extern "C" int32_t oxg4_profile_step(oxg4_model* m, oxg4_cache* c, const uint32_
     m->profiling = false;
     if (s != OXG4_OK) return s;
     CK(cudaStreamSynchronize(m->stream));
+    TRY(check_tc(c));
     m->profile.clear();
     for (auto& pe : m->prof_events) {
         float ms = 0;
@@ -1543,58 +1797,10 @@ extern "C" int32_t oxg4_topk_noalloc(const float* logits_dev, int32_t rows, int3
 // ------------------------------------------------------------------------------------------------
 // tcgen05 projection: stand-alone entry used by the parity tests of csrc/tc_gemm.cuh
 // ------------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static int32_t encode_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        CK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
-        if (!p || q != cudaDriverEntryPointSuccess) return fail(OXG4_CUDA, "Gemma 4 CUDA error: cuTensorMapEncodeTiled is unavailable");
-        fn = (EncodeTiledFn)p;
-    }
-    const cuuint64_t dims[2] = {cols, rows};
-    const cuuint64_t strides[1] = {cols * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)kTcTileK, box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(OXG4_CUDA, "Gemma 4 CUDA error: cuTensorMapEncodeTiled failed (%d)", (int)r);
-    return OXG4_OK;
-}
-
-// out[B, N] = x[B, K] . W[N, K]^T on device pointers (BF16 in, f32 out), B <= 64, K a multiple of 8.
-static int32_t tc_gemm_launch(const void* w_dev, const void* x_dev, int N, int K, int B, float* out_dev, int* err_dev,
-                              int num_sms, cudaStream_t st) {
-    if (B < 1 || B > 64 || K % 8 != 0) return fail(OXG4_INVALID_SHAPE, "tcgen05 projection: 1..64 rows and K %% 8 == 0 required");
-    const int bn = B <= 16 ? 16 : (B <= 32 ? 32 : 64);
-    CUtensorMap mw, mx;
-    TRY(encode_bf16_2d(&mw, w_dev, (uint64_t)N, (uint64_t)K, kTcTileM));
-    TRY(encode_bf16_2d(&mx, x_dev, (uint64_t)B, (uint64_t)K, (uint32_t)bn));
-    TcGemmArgs a{N, K, B, out_dev, err_dev};
-    const int tiles = (N + kTcTileM - 1) / kTcTileM;
-    const dim3 grid(std::min(tiles, num_sms));
-    if (bn == 16) {
-        TRY(allow_big_smem(tc_gemm_kernel<16>));
-        tc_gemm_kernel<16><<<grid, kTcThreads, tc_gemm_smem_bytes<16>(), st>>>(mw, mx, a);
-    } else if (bn == 32) {
-        TRY(allow_big_smem(tc_gemm_kernel<32>));
-        tc_gemm_kernel<32><<<grid, kTcThreads, tc_gemm_smem_bytes<32>(), st>>>(mw, mx, a);
-    } else {
-        TRY(allow_big_smem(tc_gemm_kernel<64>));
-        tc_gemm_kernel<64><<<grid, kTcThreads, tc_gemm_smem_bytes<64>(), st>>>(mw, mx, a);
-    }
-    CK(cudaGetLastError());
-    return OXG4_OK;
-}
-
 extern "C" int32_t oxg4_debug_tc_gemm(const uint16_t* w_host, const uint16_t* x_host, int32_t N, int32_t K, int32_t B,
                                       float* out_host, float* ms_or_null) {
     if (!w_host || !x_host || !out_host) return fail(OXG4_INVALID_ARGUMENT, "null argument");
+    TRY(tc_gemm_setup());
     void *w = nullptr, *x = nullptr;
     float* o = nullptr;
     int* e = nullptr;
@@ -1602,21 +1808,23 @@ extern "C" int32_t oxg4_debug_tc_gemm(const uint16_t* w_host, const uint16_t* x_
     int dev = 0;
     CK(cudaGetDevice(&dev));
     CK(cudaGetDeviceProperties(&prop, dev));
+    const int sms = prop.multiProcessorCount;
+    const int S = tc_pick_splits((N + kTcTileM - 1) / kTcTileM, (K + kTcTileK - 1) / kTcTileK, sms, B, N, K);
     CK(cudaMalloc(&w, (size_t)N * K * 2));
     CK(cudaMalloc(&x, (size_t)B * K * 2));
-    CK(cudaMalloc(&o, (size_t)B * N * 4));
+    CK(cudaMalloc(&o, (size_t)S * B * N * 4));
     CK(cudaMalloc(&e, 4));
     CK(cudaMemcpy(w, w_host, (size_t)N * K * 2, cudaMemcpyHostToDevice));
     CK(cudaMemcpy(x, x_host, (size_t)B * K * 2, cudaMemcpyHostToDevice));
-    CK(cudaMemset(o, 0xff, (size_t)B * N * 4));
+    CK(cudaMemset(o, 0xff, (size_t)S * B * N * 4));
     CK(cudaMemset(e, 0, 4));
     cudaEvent_t e0, e1;
     cudaEventCreate(&e0);
     cudaEventCreate(&e1);
-    int32_t s = tc_gemm_launch(w, x, N, K, B, o, e, prop.multiProcessorCount, 0);       // warm-up + result
+    int32_t s = tc_gemm_launch(w, nullptr, x, N, K, B, S, o, N, 0, e, sms, 0, false);       // warm-up + result
     if (s == OXG4_OK) {
         cudaEventRecord(e0, 0);
-        s = tc_gemm_launch(w, x, N, K, B, o, e, prop.multiProcessorCount, 0);
+        s = tc_gemm_launch(w, nullptr, x, N, K, B, S, o, N, 0, e, sms, 0, false);
         cudaEventRecord(e1, 0);
     }
     int err = 0;
@@ -1626,7 +1834,13 @@ extern "C" int32_t oxg4_debug_tc_gemm(const uint16_t* w_host, const uint16_t* x_
         if (err) s = fail(OXG4_TIMEOUT, "tcgen05 projection: a bounded barrier wait ran out (code %d)", err);
     }
     if (s == OXG4_OK) {
-        cudaMemcpy(out_host, o, (size_t)B * N * 4, cudaMemcpyDeviceToHost);
+        std::vector<float> part((size_t)S * B * N);
+        cudaMemcpy(part.data(), o, part.size() * 4, cudaMemcpyDeviceToHost);
+        for (size_t i2 = 0; i2 < (size_t)B * N; ++i2) {
+            float t = 0.0f;
+            for (int sp = 0; sp < S; ++sp) t += part[(size_t)sp * B * N + i2];      // split order, as the consumers do
+            out_host[i2] = t;
+        }
         float ms = 0;
         cudaEventElapsedTime(&ms, e0, e1);
         if (ms_or_null) *ms_or_null = ms;

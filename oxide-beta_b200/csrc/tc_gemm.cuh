@@ -33,8 +33,12 @@ constexpr int kTcStages = 6;
 constexpr uint32_t kTcSpinLimit = 2u * 1000u * 1000u;   // bounded mbarrier polling
 
 struct TcGemmArgs {
-    int N, K, B;             // weight rows, columns, activation rows (B <= BN)
-    float* out;              // [B, N]
+    int N, K, B;             // rows of ONE weight matrix, columns, activation rows (B <= BN)
+    int n_mats;              // 1, or 2 when gate and up are streamed by one launch (second tensor map)
+    int S;                   // K-splits: a work unit is (128-row tile, split); S partial outputs are added later
+    int kb_per_split;        // 64-column blocks per split
+    float* out;              // [S, B, ld]; matrix m occupies columns col0 + m * N ..
+    int ld, col0;            // row stride of `out` (>= n_mats * N) and first column written
     int* err;                // device flag, set non-zero if a bounded wait ran out
 };
 
@@ -94,7 +98,8 @@ DEVINL uint32_t umma_idesc_bf16(int M, int N) {
 
 template <int BN>
 __global__ void __launch_bounds__(kTcThreads, 1)
-tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TcGemmArgs a) {
+tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w1,
+               const __grid_constant__ CUtensorMap map_x, const TcGemmArgs a) {
     static_assert(BN == 16 || BN == 32 || BN == 64, "activation rows per tile");
     constexpr uint32_t A_BYTES = kTcTileM * kTcTileK * 2;     // 16 KiB
     constexpr uint32_t B_BYTES = BN * kTcTileK * 2;
@@ -107,8 +112,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __shared__ volatile int failed;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n_tiles = (a.N + kTcTileM - 1) / kTcTileM;
-    const int kblocks = (a.K + kTcTileK - 1) / kTcTileK;
+    const int tiles_per_mat = (a.N + kTcTileM - 1) / kTcTileM;
+    const int n_tiles = tiles_per_mat * a.n_mats * a.S;          // work units: (matrix, tile, split)
+    const int kblocks_all = (a.K + kTcTileK - 1) / kTcTileK;
+    // unit u -> split s = u % S, tile index (over both matrices) u / S
+    auto kb_begin = [&](int u) { return (u % a.S) * a.kb_per_split; };
+    auto kb_end = [&](int u) { return min(kblocks_all, (u % a.S + 1) * a.kb_per_split); };
 
     if (tid == 0) {
         for (int s = 0; s < kTcStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -133,13 +142,16 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // ---- TMA producer ----
         uint32_t it = 0;
         for (int t = blockIdx.x; t < n_tiles && !failed; t += gridDim.x) {
-            for (int kb = 0; kb < kblocks; ++kb, ++it) {
+            const int tg = t / a.S;                               // tile over both matrices
+            const bool second = tg >= tiles_per_mat;
+            const int trow = (second ? tg - tiles_per_mat : tg) * kTcTileM;
+            for (int kb = kb_begin(t); kb < kb_end(t); ++kb, ++it) {
                 const int s = it % kTcStages;
                 const uint32_t ph = (it / kTcStages) & 1;
                 if (it >= (uint32_t)kTcStages && !mbar_wait(&empty[s], ph ^ 1)) { failed = 1; atomicExch(a.err, 1); break; }
                 unsigned char* sa = tiles + (size_t)s * STAGE;
                 mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-                tma_load_2d(sa, &map_w, kb * kTcTileK, t * kTcTileM, &full[s]);
+                tma_load_2d(sa, second ? &map_w1 : &map_w, kb * kTcTileK, trow, &full[s]);
                 tma_load_2d(sa + A_BYTES, &map_x, kb * kTcTileK, 0, &full[s]);
             }
         }
@@ -150,7 +162,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (int t = blockIdx.x; t < n_tiles && !failed; t += gridDim.x, ++tile_i) {
             if (tile_i > 0 && !mbar_wait(&acc_empty, (tile_i - 1) & 1)) { failed = 1; atomicExch(a.err, 2); break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            for (int kb = 0; kb < kblocks; ++kb, ++it) {
+            const int kb0 = kb_begin(t);
+            for (int kb = kb0; kb < kb_end(t); ++kb, ++it) {
                 const int s = it % kTcStages;
                 const uint32_t ph = (it / kTcStages) & 1;
                 if (!mbar_wait(&full[s], ph)) { failed = 1; atomicExch(a.err, 3); break; }
@@ -159,7 +172,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const uint64_t da = umma_smem_desc(sa), db = umma_smem_desc(sa + A_BYTES);
 #pragma unroll
                 for (int k = 0; k < kTcTileK / 16; ++k) {
-                    const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+                    const uint32_t accumulate = (kb > kb0 || k > 0) ? 1u : 0u;
                     // advance 16 BF16 = 32 bytes inside the swizzle atom: +2 in units of 16 bytes
                     asm volatile(
                         "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
@@ -183,7 +196,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++tile_i) {
             if (!mbar_wait(&acc_full, tile_i & 1)) { if (lane == 0) atomicExch(a.err, 4); break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int row = t * kTcTileM + quad * 32 + lane;
+            const int tg = t / a.S, sp = t % a.S;
+            const bool second = tg >= tiles_per_mat;
+            const int row = (second ? tg - tiles_per_mat : tg) * kTcTileM + quad * 32 + lane;
+            float* dst = a.out + (size_t)sp * a.B * a.ld + a.col0 + (second ? a.N : 0);
 #pragma unroll
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 uint32_t v[16];
@@ -197,7 +213,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 if (row < a.N) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
-                        if (c0 + j < a.B) a.out[(size_t)(c0 + j) * a.N + row] = __uint_as_float(v[j]);
+                        if (c0 + j < a.B) dst[(size_t)(c0 + j) * a.ld + row] = __uint_as_float(v[j]);
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
