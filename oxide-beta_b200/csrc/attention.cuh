@@ -96,6 +96,37 @@ template <> struct KVec<float, 2> {
     }
 };
 
+// A lane's slice of one K or V row as loaded (packed), converted only when it is consumed, so that
+// the next positions' loads can be in flight in few registers.
+template <typename KT, int EPT> struct KRaw {
+    static constexpr int NWORDS = EPT * (int)sizeof(KT) / 4;
+    uint32_t w[NWORDS];
+};
+template <typename KT, int EPT> DEVINL void kraw_load(const KT* p, KRaw<KT, EPT>& r) {
+    constexpr int NWD = KRaw<KT, EPT>::NWORDS;
+    if constexpr (NWD == 8) {
+        const uint4 x = ldg_stream16(p), y = ldg_stream16((const char*)p + 16);
+        r.w[0] = x.x; r.w[1] = x.y; r.w[2] = x.z; r.w[3] = x.w; r.w[4] = y.x; r.w[5] = y.y; r.w[6] = y.z; r.w[7] = y.w;
+    } else if constexpr (NWD == 4) {
+        const uint4 x = ldg_stream16(p);
+        r.w[0] = x.x; r.w[1] = x.y; r.w[2] = x.z; r.w[3] = x.w;
+    } else if constexpr (NWD == 2) {
+        const uint2 x = ldg_stream8(p);
+        r.w[0] = x.x; r.w[1] = x.y;
+    } else {
+        r.w[0] = ldg_stream4(p);
+    }
+}
+template <typename KT, int EPT> DEVINL void kraw_cvt(const KRaw<KT, EPT>& r, float (&o)[EPT]) {
+    if constexpr (sizeof(KT) == 2) {
+#pragma unroll
+        for (int i = 0; i < EPT / 2; ++i) { o[2 * i] = bf16lo(r.w[i]); o[2 * i + 1] = bf16hi(r.w[i]); }
+    } else {
+#pragma unroll
+        for (int i = 0; i < EPT; ++i) o[i] = __uint_as_float(r.w[i]);
+    }
+}
+
 template <typename KT> DEVINL KT kv_store_cvt(float v);
 template <> DEVINL float kv_store_cvt<float>(float v) { return v; }
 template <> DEVINL uint16_t kv_store_cvt<uint16_t>(float v) { return (uint16_t)f32_to_bf16_bits(v); }
@@ -103,7 +134,7 @@ template <typename KT> DEVINL float kv_widen(KT v);
 template <> DEVINL float kv_widen<float>(float v) { return v; }
 template <> DEVINL float kv_widen<uint16_t>(uint16_t v) { return __uint_as_float((uint32_t)v << 16); }
 
-// CL = true: the splits of one (sequence, kv head) form a thread-block cluster (gridDim.x <= 8 CTAs);
+// CL = true: the splits of one (sequence, kv head) form a thread-block cluster (gridDim.x <= 16 CTAs);
 // partials stay in shared memory and are merged through distributed shared memory after one cluster
 // barrier. CL = false: partials go through global memory and the last CTA to arrive (atomic ticket)
 // merges them.
@@ -245,7 +276,6 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
         const KT* kpool = (const KT*)a.kpool;
         const KT* vpool = (const KT*)a.vpool;
         const int32_t* pt = a.page_table + (size_t)b * a.pages_per_seq;
-
         auto row_offset = [&](int p) -> size_t {
             const int slot = p % cap;
             return (((size_t)pt[slot / a.page_tokens] * a.Nkv + kvh) * a.page_tokens +
@@ -267,41 +297,38 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
                 m[g] = mn;
             }
         };
-
+        typedef KRaw<KT, EPT> Raw;
+        auto issue = [&](int p, Raw& kr, Raw& vr) {            // loads only; the current token comes from shared memory
+            if (p < end && p != pos) {
+                const size_t off = row_offset(p);
+                kraw_load<KT, EPT>(kpool + off, kr);
+                kraw_load<KT, EPT>(vpool + off, vr);
+            }
+        };
+        auto use = [&](int p, const Raw& kr, const Raw& vr) {
+            if (p >= end) return;
+            float kf[EPT], vf[EPT];
+            if (p == pos) {
+#pragma unroll
+                for (int e = 0; e < EPT; ++e) { kf[e] = kcur[lane * EPT + e]; vf[e] = vcur[lane * EPT + e]; }
+            } else {
+                kraw_cvt<KT, EPT>(kr, kf);
+                kraw_cvt<KT, EPT>(vr, vf);
+            }
+            consume(kf, vf);
+        };
+        // two positions per step, the next step's loads issued before this step's arithmetic
+        Raw k0, v0, k1, v1;
         int p = begin + warp;
-        for (; p + NW < end; p += 2 * NW) {
-            float k0[EPT], v0[EPT], k1[EPT], v1[EPT];
-            const int p1 = p + NW;
-            if (p == pos) {
-#pragma unroll
-                for (int e = 0; e < EPT; ++e) { k0[e] = kcur[lane * EPT + e]; v0[e] = vcur[lane * EPT + e]; }
-            } else {
-                const size_t off = row_offset(p);
-                KVec<KT, EPT>::load(kpool + off, k0);
-                KVec<KT, EPT>::load(vpool + off, v0);
-            }
-            if (p1 == pos) {
-#pragma unroll
-                for (int e = 0; e < EPT; ++e) { k1[e] = kcur[lane * EPT + e]; v1[e] = vcur[lane * EPT + e]; }
-            } else {
-                const size_t off = row_offset(p1);
-                KVec<KT, EPT>::load(kpool + off, k1);
-                KVec<KT, EPT>::load(vpool + off, v1);
-            }
-            consume(k0, v0);
-            consume(k1, v1);
-        }
-        for (; p < end; p += NW) {
-            float k0[EPT], v0[EPT];
-            if (p == pos) {
-#pragma unroll
-                for (int e = 0; e < EPT; ++e) { k0[e] = kcur[lane * EPT + e]; v0[e] = vcur[lane * EPT + e]; }
-            } else {
-                const size_t off = row_offset(p);
-                KVec<KT, EPT>::load(kpool + off, k0);
-                KVec<KT, EPT>::load(vpool + off, v0);
-            }
-            consume(k0, v0);
+        issue(p, k0, v0);
+        issue(p + NW, k1, v1);
+        for (; p < end; p += 2 * NW) {
+            Raw nk0, nv0, nk1, nv1;
+            issue(p + 2 * NW, nk0, nv0);
+            issue(p + 3 * NW, nk1, nv1);
+            use(p, k0, v0);
+            use(p + NW, k1, v1);
+            k0 = nk0; v0 = nv0; k1 = nk1; v1 = nv1;
         }
 
         // merge the warps of this CTA (fixed warp order)
@@ -423,7 +450,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
 
 template <int D, int G>
 inline size_t attn_smem_bytes() {
-    return sizeof(float) * (size_t)(G * D + 2 * D + 2 * kAttnWarps * G + kAttnWarps * G * D + G * (D + 2));
+    return sizeof(float) * (size_t)(G * D + 2 * D + 2 * kAttnWarps * G + kAttnWarps * G * D + G * (D + 2));   // + page table
 }
 
 }  // namespace oxg4

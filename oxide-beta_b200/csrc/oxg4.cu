@@ -355,6 +355,10 @@ static int32_t set_attn_attrs() {
     TRY(allow_big_smem(attn_decode_kernel<KT, D, 2, true>));
     TRY(allow_big_smem(attn_decode_kernel<KT, D, 4, true>));
     TRY(allow_big_smem(attn_decode_kernel<KT, D, 8, true>));
+    CK(cudaFuncSetAttribute(attn_decode_kernel<KT, D, 1, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    CK(cudaFuncSetAttribute(attn_decode_kernel<KT, D, 2, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    CK(cudaFuncSetAttribute(attn_decode_kernel<KT, D, 4, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    CK(cudaFuncSetAttribute(attn_decode_kernel<KT, D, 8, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
     return OXG4_OK;
 }
 
@@ -603,7 +607,10 @@ static int32_t cache_build(oxg4_cache* c) {
     const int want = std::max(1, (8 * m->num_sms + pairs - 1) / pairs);
     c->min_split = 16;
     c->attn_cluster = getenv("OXG4_ATTN_TICKET") == nullptr;
-    const int cap_splits = c->attn_cluster ? 8 : 64;
+    // clusters of 16 CTAs (non-portable size) only while one CTA per SM is enough for the whole step
+    int cluster_max = 16;
+    if (const char* e = getenv("OXG4_ATTN_CLUSTER_MAX")) cluster_max = std::max(1, std::min(16, atoi(e)));
+    const int cap_splits = c->attn_cluster ? (pairs * 16 <= m->num_sms ? cluster_max : std::min(cluster_max, 8)) : 64;
     auto pow2_floor = [](int v) { int p = 1; while (p * 2 <= v) p *= 2; return p; };
     c->splits_full = std::max(1, std::min({want, cap_splits, (maxf + c->min_split - 1) / c->min_split}));
     c->splits_slide = std::max(1, std::min({want, cap_splits, (maxs + c->min_split - 1) / c->min_split}));
@@ -1066,7 +1073,7 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
             a.pf_bytes = (unsigned long long)m->I * H * m->es;
         }
         a.ts = ln.ts();
-        const bool cl = c->attn_cluster && a.n_splits <= 8;
+        const bool cl = c->attn_cluster && a.n_splits <= 16;
         auto fn = c->kv_dtype == OXG4_BF16 ? pick_attn<uint16_t>(D, m->G, cl) : pick_attn<float>(D, m->G, cl);
         // few CTAs (one sequence): 16 warps each to cut latency; many CTAs: 4 warps each so that several
         // fit on an SM (the kernel needs ~90 registers per thread)
