@@ -287,7 +287,7 @@ def main():
                 "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
                 "bytes_per_launch": parts["gateup_launch"], "ms_per_launch": gu_ms,
                 "step_bytes": step_bytes, "step_achieved": step_bytes / (ms_step * 1e-3) / 1e9,
-                "step_frac": step_bytes / (ms_step * 1e-3) / 1e9 / peak,
+                "step_frac": step_bytes / (ms_step * 1e-3) / 1e9 / (peak * tp),
                 "kernel_ms": {k: round(v, 5) for k, v in prof.items()}}
 
     if rank != 0:

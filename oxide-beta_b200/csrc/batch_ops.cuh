@@ -75,6 +75,18 @@ __global__ void __launch_bounds__(kRowsThreads) rows_norm_kernel(const RowsNormA
         a.x[ro + i] = (uint16_t)f32_to_bf16_bits(a.h_out[ro + i] * r2 * a.w_norm[i]);
 }
 
+// out[i] = sum_s part[s][i] in split order (tensor parallelism: one compact buffer goes through the
+// all-reduce instead of every K-split partial)
+__global__ void __launch_bounds__(kRowsThreads) sum_splits_kernel(const float* part, int splits, size_t n, float* out) {
+    pdl_wait();
+    pdl_launch();
+    const size_t i = (size_t)blockIdx.x * kRowsThreads + threadIdx.x;
+    if (i >= n) return;
+    float t = 0.0f;
+    for (int s = 0; s < splits; ++s) t += part[(size_t)s * n + i];
+    out[i] = t;
+}
+
 // x[b, i] = bf16(gelu_tanh(sum_s gu[s, b, i]) * sum_s gu[s, b, I + i]); grid (ceil(I / 256), B)
 __global__ void __launch_bounds__(kRowsThreads)
 geglu_rows_kernel(int B, int I, const float* gu, int splits, uint16_t* x) {

@@ -1106,8 +1106,8 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
                 n.tokens = c->tokens;
                 n.embed_scale = sqrtf((float)H);
             } else {
-                n.raw = c->down_part;
-                n.raw_splits = c->s_down;
+                n.raw = m->tp > 1 ? c->down_raw : c->down_part;
+                n.raw_splits = m->tp > 1 ? 1 : c->s_down;
                 n.w_post = m->layers[l - 1].post_ff_ln;
                 n.scalar = m->layers[l - 1].layer_scalar;
             }
@@ -1122,11 +1122,17 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
             ln.tc("qkv", c, p.wqkv, nullptr, c->x_h, nqkv, H, c->s_qkv, c->qkv_part, nqkv, 0);
             launch_attn(l, c->qkv_part, c->s_qkv, c->x_a);
             ln.tc("o", c, p.wo, nullptr, c->x_a, H, qw, c->s_o, c->o_part, H, 0);
-            ln.allreduce(c->o_part, (size_t)c->s_o * B * H);
+            const size_t bh = (size_t)B * H;
+            const dim3 sum_grid((unsigned)((bh + kRowsThreads - 1) / kRowsThreads));
+            if (m->tp > 1) {      // row-split projection: add the K-splits locally, then the ranks
+                ln.go("sum", sum_splits_kernel, sum_grid, dim3(kRowsThreads), 0, (const float*)c->o_part, c->s_o, bh, c->o_raw);
+                ln.allreduce(c->o_raw, bh);
+            }
             RowsNormArgs n2{};
             n2.B = B; n2.H = H;
             n2.h_in = c->hB; n2.h_out = c->hA;
-            n2.raw = c->o_part; n2.raw_splits = c->s_o;
+            n2.raw = m->tp > 1 ? c->o_raw : c->o_part;
+            n2.raw_splits = m->tp > 1 ? 1 : c->s_o;
             n2.w_post = p.post_attn_ln;
             n2.scalar = 1.0f;
             n2.w_norm = p.pre_ff_ln;
@@ -1137,7 +1143,11 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
             ln.go("geglu", geglu_rows_kernel, dim3((m->I + kRowsThreads - 1) / kRowsThreads, B), dim3(kRowsThreads), 0, B,
                   m->I, (const float*)c->gu_part, c->s_gu, c->x_i);
             ln.tc("down", c, p.wdown, nullptr, c->x_i, H, m->I, c->s_down, c->down_part, H, 0);
-            ln.allreduce(c->down_part, (size_t)c->s_down * B * H);
+            if (m->tp > 1) {
+                ln.go("sum", sum_splits_kernel, sum_grid, dim3(kRowsThreads), 0, (const float*)c->down_part, c->s_down, bh,
+                      c->down_raw);
+                ln.allreduce(c->down_raw, bh);
+            }
             continue;
         }
         {   // input norm + QKV projection (decode.rs:61-98); also closes the previous layer
@@ -1229,7 +1239,8 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
         RowsNormArgs n{};
         n.B = B; n.H = H;
         n.h_in = c->hA; n.h_out = c->hB;
-        n.raw = c->down_part; n.raw_splits = c->s_down;
+        n.raw = m->tp > 1 ? c->down_raw : c->down_part;
+        n.raw_splits = m->tp > 1 ? 1 : c->s_down;
         n.w_post = m->layers[L - 1].post_ff_ln;
         n.scalar = m->layers[L - 1].layer_scalar;
         n.w_norm = m->final_norm;

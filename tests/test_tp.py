@@ -115,31 +115,31 @@ WORKER_GPU = textwrap.dedent("""
         ids = [pkg.Gemma4CudaState.tp_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
         tp.tp_init(ids[0])
-        B = 3
-        lens = [5, 9, 20]
-        prompts = [syn.prompt_ids(cfg["vocab_size"], n, seed=40 + b) for b, n in enumerate(lens)]
-        table = tp.new_cache_table([40] * B, batch=B, page_tokens=8, kv_dtype=kv)
-        logits = tp.prefill_prompt(np.concatenate(prompts), table, lens=lens)
-        toks = logits.argmax(-1).astype(np.uint32)
-        out, _ = tp.decode_greedy(toks, table, 10)
-        last = tp.decode_token(out[-1], table)
-        top = tp.decode_topk(last.argmax(-1).astype(np.uint32), table, 5, 1.2, True)
-        if rank == 0:
-            one = pkg.Gemma4CudaState.load(pkg.Gemma4TextConfig(cfg), weights, 0, wd)
-            t1 = one.new_cache_table([40] * B, batch=B, page_tokens=8, kv_dtype=kv)
-            l1 = one.prefill_prompt(np.concatenate(prompts), t1, lens=lens)
-            if tol is not None:
-                assert np.abs(l1 - logits).max() <= tol, np.abs(l1 - logits).max()
-                o1, _ = one.decode_greedy(l1.argmax(-1).astype(np.uint32), t1, 10)
-                assert np.array_equal(o1, out)
-                last1 = one.decode_token(o1[-1], t1)
-                assert np.abs(last1 - last).max() <= tol
-                top1 = one.decode_topk(last1.argmax(-1).astype(np.uint32), t1, 5, 1.2, True)
-                assert np.array_equal(top1[0], top[0]) and np.abs(top1[1] - top[1]).max() <= tol
-            else:
-                assert np.abs(l1 - logits).max() <= 2e-2, np.abs(l1 - logits).max()
-            print("tp parity ok", dtype, float(np.abs(l1 - logits).max()))
-        del table, tp
+        for B, lens in ((3, [5, 9, 20]), (9, [3, 4, 5, 6, 7, 8, 9, 10, 11])):       # 9 rows: tcgen05 projections
+          prompts = [syn.prompt_ids(cfg["vocab_size"], n, seed=40 + b) for b, n in enumerate(lens)]
+          table = tp.new_cache_table([40] * B, batch=B, page_tokens=8, kv_dtype=kv)
+          logits = tp.prefill_prompt(np.concatenate(prompts), table, lens=lens)
+          toks = logits.argmax(-1).astype(np.uint32)
+          out, _ = tp.decode_greedy(toks, table, 10)
+          last = tp.decode_token(out[-1], table)
+          top = tp.decode_topk(last.argmax(-1).astype(np.uint32), table, 5, 1.2, True)
+          if rank == 0:
+              one = pkg.Gemma4CudaState.load(pkg.Gemma4TextConfig(cfg), weights, 0, wd)
+              t1 = one.new_cache_table([40] * B, batch=B, page_tokens=8, kv_dtype=kv)
+              l1 = one.prefill_prompt(np.concatenate(prompts), t1, lens=lens)
+              if tol is not None:
+                  assert np.abs(l1 - logits).max() <= tol, np.abs(l1 - logits).max()
+                  o1, _ = one.decode_greedy(l1.argmax(-1).astype(np.uint32), t1, 10)
+                  assert np.array_equal(o1, out)
+                  last1 = one.decode_token(o1[-1], t1)
+                  assert np.abs(last1 - last).max() <= tol
+                  top1 = one.decode_topk(last1.argmax(-1).astype(np.uint32), t1, 5, 1.2, True)
+                  assert np.array_equal(top1[0], top[0]) and np.abs(top1[1] - top[1]).max() <= tol
+              else:
+                  assert np.abs(l1 - logits).max() <= 2e-2, np.abs(l1 - logits).max()
+              print("tp parity ok", dtype, float(np.abs(l1 - logits).max()))
+        del table
+        del tp
         dist.barrier()
     dist.destroy_process_group()
 """)
@@ -152,4 +152,4 @@ def test_tp2_matches_single_gpu():
         pytest.skip("needs 2 GPUs")
     r = _torchrun(WORKER_GPU, 2, extra_env={"NCCL_NVLS_ENABLE": "0"}, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-6000:]
-    assert r.stdout.count("tp parity ok") == 2
+    assert r.stdout.count("tp parity ok") == 4
