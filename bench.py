@@ -175,6 +175,8 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return
+        # torchrun exports OMP_NUM_THREADS=1 to every rank; the CPU reference uses all host cores
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
         sample_prompt = 32
         steps = min(args.steps, 16)
         wu = min(warmup, 3)
