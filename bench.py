@@ -127,6 +127,7 @@ class ClockSampler:
 def cpu_oracle_run(cfg, weights_iter, prompt, steps, warmup):
     """Times the CPU oracle: ingests `prompt`, then `warmup` + `steps` greedy decode steps."""
     from oracle import oracle as orc
+    orc.set_num_threads(os.cpu_count() or 1)      # torchrun exports OMP_NUM_THREADS=1
     m = orc.OracleModel(cfg, orc.REF_BF16, kv_bf16=True)
     for name, a in weights_iter:
         m.set_weight(name, a)

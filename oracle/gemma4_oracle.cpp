@@ -751,6 +751,14 @@ int orc_decode_trace(void* model, void* cache, uint32_t token, const float* inje
     return 0;
 }
 
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int orc_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -292,5 +292,9 @@ class OracleCache:
         return ids[:k].copy(), scores[:k].copy()
 
 
+def set_num_threads(n: int):
+    lib().orc_set_num_threads(C.c_int(n))
+
+
 def num_threads() -> int:
     return lib().orc_num_threads()
