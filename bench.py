@@ -257,10 +257,13 @@ def main():
         tok = np.array([r[0][0]], dtype=np.uint32) if B == 1 else r[0][:, 0].copy()
     e2e_steps = min(args.steps, total_steps - 3)
     t0 = time.perf_counter()
+    stamps = [t0]
     for _ in range(e2e_steps):
         r = state.decode_topk(tok, table, 1, 1.0, True)
         tok = np.array([r[0][0]], dtype=np.uint32) if B == 1 else r[0][:, 0].copy()
-    e2e_s = time.perf_counter() - t0
+        stamps.append(time.perf_counter())
+    e2e_s = stamps[-1] - t0
+    inter_token_ms = sorted(1000.0 * (b_ - a_) for a_, b_ in zip(stamps[:-1], stamps[1:]))
     clocks = sampler.stop()
 
     if dist:
@@ -310,7 +313,8 @@ def main():
                    "l2": "per-step inputs (weights + KV) exceed the 126 MB L2; no flush",
                    "load_s": round(load_s, 2), "prefill_s": round(prefill_s, 2)},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * B + 16, "d2h_bytes_per_step": 8 * B,
-                "steps": e2e_steps},
+                "steps": e2e_steps, "p50_inter_token_ms": inter_token_ms[len(inter_token_ms) // 2],
+                "p95_inter_token_ms": inter_token_ms[int(len(inter_token_ms) * 0.95)]},
         "gpu_launches": int(launches_timed),
         "clocks": clocks,
         "roofline": roofline,
