@@ -230,6 +230,12 @@ def main():
     total_steps = warmup + args.steps
     max_seq = [n + 2 * total_steps + 8 for n in lens]
     table = state.new_cache_table(max_seq, batch=B, kv_dtype=pkg.BF16)
+    tp_exchange = "nccl"
+    if tp > 1 and 8 <= B <= 64 and os.environ.get("OXG4_TP_PEER"):
+        handles = [None] * world           # opt-in: the O/down sums travel through peer memory instead of NCCL
+        dist.all_gather_object(handles, table.tp_export())
+        table.tp_connect(handles)
+        tp_exchange = "peer-memory"
     prompts = [syn.prompt_ids(cfg["vocab_size"], n, seed=1 + b) for b, n in enumerate(lens)]
     t_pre = time.perf_counter()
     logits = state.prefill_prompt(np.concatenate(prompts), table, lens=lens)
@@ -287,8 +293,12 @@ def main():
     peak, peak_kind = peaks()
     step_bytes, parts = algorithmic_bytes(cfg, B, contexts)
     gu_ms = prof.get("gateup", float("nan"))
+    parts["gateup_launch"] //= tp          # a rank streams its shard of the projection
     achieved = parts["gateup_launch"] / (gu_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "gemv_kernel<bf16, PRO_NORM, EPI_GATEUP> (gate/up projection)",
+    roofline = {"bound": "hbm", "kernel": ("gemv_kernel<bf16, PRO_NORM, EPI_GATEUP>" if B == 1 else
+                           "gemv_mma_kernel<PRO_NORM, EPI_GATEUP>" if B < 8 else
+                           "tc_gemm_kernel (tcgen05, gate and up maps)" if B <= 64 else
+                           "gemv_mma_kernel<PRO_NORM, EPI_GATEUP>") + " (gate/up projection)",
                 "achieved": achieved, "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
                 "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
                 "bytes_per_launch": parts["gateup_launch"], "ms_per_launch": gu_ms,
@@ -296,9 +306,10 @@ def main():
                 "step_frac": step_bytes / (ms_step * 1e-3) / 1e9 / (peak * tp),
                 "kernel_ms": {k: round(v, 5) for k, v in prof.items()}}
 
+    if dist:
+        dist.barrier()                     # no rank frees its cache table while a peer may still read it
     if rank != 0:
-        if dist:
-            dist.destroy_process_group()
+        dist.destroy_process_group()
         return
     out = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
@@ -308,7 +319,7 @@ def main():
                                                  if (args.layers or args.vocab) else ""),
                    "batch": B, "prompt": lens[0] if len(set(lens)) == 1 else "ragged",
                    "context_at_timing": contexts[0], "kv_dtype": "bf16", "page_tokens": 256,
-                   "parallelism": "single GPU" if world == 1 else (f"tp{tp} (NCCL all-reduce after O and down)"
+                   "parallelism": "single GPU" if world == 1 else (f"tp{tp} (sums after O and down: {tp_exchange})"
                                                                    if tp > 1 else f"{world} independent replicas"),
                    "l2": "per-step inputs (weights + KV) exceed the 126 MB L2; no flush",
                    "load_s": round(load_s, 2), "prefill_s": round(prefill_s, 2)},

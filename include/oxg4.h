@@ -114,6 +114,15 @@ int32_t oxg4_tp_shard(const char* name, int64_t rows, int64_t cols, int32_t tp_r
                       int32_t heads, int32_t kv_heads, int32_t head_dim, int32_t intermediate, int64_t* out4);
 int32_t oxg4_model_tp_init(oxg4_model* model, const void* unique_id_128_bytes);
 
+/* Peer-memory exchange for tensor parallelism (no counterpart in the reference). With tp_size > 1 and
+ * 8..64 sequences the sums after the O and down projections can travel through buffers that the
+ * ranks map into each other with CUDA IPC instead of NCCL calls: every rank exports the handle of its
+ * cache table's exchange block, the host program gathers the tp_size handles (64 bytes each, in rank
+ * order) and every rank connects. Until connected (or with OXG4_TP_NCCL set) the NCCL path is used. All
+ * ranks must make the same sequence of step calls. */
+int32_t oxg4_cache_tp_export(oxg4_cache* cache, void* handle_out_64_bytes);
+int32_t oxg4_cache_tp_connect(oxg4_cache* cache, const void* handles_tp_size_x_64_bytes);
+
 /* ---- KV cache: new_cache_table (gemma4_cuda/cache.rs:31-95) -------------------------------------- */
 
 /* `max_seq[b]` is the longest sequence (prompt + generated) sequence b may reach. Sliding layers

@@ -58,6 +58,8 @@ SYMBOLS = {
     "oxg4_tp_shard": (C.c_int32, [C.c_char_p, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                   C.c_int32, C.POINTER(C.c_int64)]),
     "oxg4_model_tp_init": (C.c_int32, [C.c_void_p, C.c_void_p]),
+    "oxg4_cache_tp_export": (C.c_int32, [C.c_void_p, C.c_void_p]),
+    "oxg4_cache_tp_connect": (C.c_int32, [C.c_void_p, C.c_void_p]),
     "oxg4_cache_create": (C.c_int32, [C.c_void_p, C.c_int32, C.POINTER(C.c_int32), C.c_int32, C.c_int32,
                                       C.POINTER(C.c_void_p)]),
     "oxg4_cache_destroy": (None, [C.c_void_p]),

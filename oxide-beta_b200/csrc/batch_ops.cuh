@@ -15,6 +15,33 @@
 namespace oxg4 {
 
 constexpr int kRowsThreads = 256;
+constexpr int kMaxTp = 8;
+constexpr unsigned int kPeerSpinLimit = 4u * 1000u * 1000u;     // bounded polling of a peer flag (a few ms)
+
+// Tensor parallelism over peer memory: the all-reduce after a row-split projection is not a kernel of
+// its own. Every rank PUSHES its partial [B, H] into slot `rank` of every rank's gather buffer (plain
+// peer stores over NVLink: no round trip per element) and then raises a sequence number in every
+// rank's flag array; the kernel that consumes the sum waits, with a bound, until its own flags carry
+// the expected number from all ranks and adds the tp partials from LOCAL memory in rank order, so
+// every rank computes the same bits. No multicast, no TMA from peer memory.
+struct PeerExchange {
+    int tp, rank;
+    float* push[kMaxTp];             // push[r]: slot `rank` of rank r's gather buffer for this kind, as mapped on THIS GPU
+    const float* gathered;           // local gather buffer [tp][B * H]
+    unsigned int* flags[kMaxTp];     // flags[r]: rank r's flag array [kMaxTp] for this kind, as mapped on THIS GPU
+    unsigned int* seq;               // local: number of exchanges of this kind completed by the local producer
+    unsigned int* ticket;            // local: producer CTAs still to finish
+    int* status;                     // local: set non-zero when a bounded wait ran out
+};
+
+DEVINL unsigned int ld_acquire_sys(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+DEVINL void st_release_sys(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 
 struct RowsNormArgs {
     int B, H;
@@ -30,6 +57,7 @@ struct RowsNormArgs {
     float embed_scale;
     float eps;
     uint16_t* x;             // [B, H] BF16 activations for the next projection
+    PeerExchange px;         // px.tp > 1: `raw` is the local gather buffer; wait for every rank's push first
 };
 
 __global__ void __launch_bounds__(kRowsThreads) rows_norm_kernel(const RowsNormArgs a) {
@@ -44,10 +72,21 @@ __global__ void __launch_bounds__(kRowsThreads) rows_norm_kernel(const RowsNormA
         tok = a.tokens[b];
         if (tok == kInactiveToken) tok = 0;
     } else if (a.raw != nullptr) {
+        if (a.px.tp > 1) {
+            // wait (bounded) until every rank has published this exchange
+            if (tid < a.px.tp) {
+                const unsigned int want = *a.px.seq;
+                const unsigned int* f = a.px.flags[a.px.rank] + tid;
+                unsigned int it = 0;
+                while (ld_acquire_sys(f) < want && ++it < kPeerSpinLimit) {}
+                if (it >= kPeerSpinLimit) atomicExch(a.px.status, 1);
+            }
+            __syncthreads();
+        }
         float ss[1] = {0.0f};
         for (int i = tid; i < H; i += kRowsThreads) {
             float t = 0.0f;
-            for (int s = 0; s < a.raw_splits; ++s) t += a.raw[((size_t)s * a.B + b) * H + i];
+            for (int s = 0; s < a.raw_splits; ++s) t += __ldcg(a.raw + ((size_t)s * a.B + b) * H + i);
             ss[0] += t * t;
         }
         block_sum<1>(ss, red);
@@ -58,7 +97,7 @@ __global__ void __launch_bounds__(kRowsThreads) rows_norm_kernel(const RowsNormA
         float h = a.h_in[ro + i];
         if (a.raw != nullptr) {
             float t = 0.0f;
-            for (int s = 0; s < a.raw_splits; ++s) t += a.raw[((size_t)s * a.B + b) * H + i];
+            for (int s = 0; s < a.raw_splits; ++s) t += __ldcg(a.raw + ((size_t)s * a.B + b) * H + i);
             h = (h + t * r * a.w_post[i]) * a.scalar;
         }
         return h;
@@ -77,14 +116,38 @@ __global__ void __launch_bounds__(kRowsThreads) rows_norm_kernel(const RowsNormA
 
 // out[i] = sum_s part[s][i] in split order (tensor parallelism: one compact buffer goes through the
 // all-reduce instead of every K-split partial)
-__global__ void __launch_bounds__(kRowsThreads) sum_splits_kernel(const float* part, int splits, size_t n, float* out) {
+__global__ void __launch_bounds__(kRowsThreads)
+sum_splits_kernel(const float* part, int splits, size_t n, float* out, const PeerExchange px) {
+    __shared__ unsigned int s_last;
     pdl_wait();
     pdl_launch();
     const size_t i = (size_t)blockIdx.x * kRowsThreads + threadIdx.x;
-    if (i >= n) return;
-    float t = 0.0f;
-    for (int s = 0; s < splits; ++s) t += part[(size_t)s * n + i];
-    out[i] = t;
+    if (i < n) {
+        float t = 0.0f;
+        for (int s = 0; s < splits; ++s) t += part[(size_t)s * n + i];
+        if (px.tp > 1) {
+            for (int r = 0; r < px.tp; ++r) px.push[r][i] = t;
+        } else {
+            out[i] = t;
+        }
+    }
+    if (px.tp > 1) {
+        // the last CTA to finish publishes the exchange to every rank (its own flag array included)
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) s_last = (atomicAdd(px.ticket, 1u) == gridDim.x - 1) ? 1u : 0u;
+        __syncthreads();
+        if (s_last) {
+            __threadfence_system();
+            if (threadIdx.x == 0) {
+                *px.ticket = 0u;
+                const unsigned int seq = *px.seq + 1u;
+                *px.seq = seq;
+                __threadfence_system();
+                for (int r = 0; r < px.tp; ++r) st_release_sys(px.flags[r] + px.rank, seq);
+            }
+        }
+    }
 }
 
 // x[b, i] = bf16(gelu_tanh(sum_s gu[s, b, i]) * sum_s gu[s, b, I + i]); grid (ceil(I / 256), B)

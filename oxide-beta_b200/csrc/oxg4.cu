@@ -544,6 +544,12 @@ struct oxg4_cache {
     uint16_t *x_h = nullptr, *x_a = nullptr, *x_i = nullptr;
     float *qkv_part = nullptr, *o_part = nullptr, *gu_part = nullptr, *down_part = nullptr;
     int* tc_err = nullptr;
+    // peer-memory exchange for tensor parallelism (two kinds: after O, after down)
+    void* px_block = nullptr;                 // [2][tp][B*H] floats + [2][kMaxTp] flags, shared with the peers through CUDA IPC
+    void* px_peer_base[kMaxTp] = {};          // peers' blocks as mapped here (own entry = px_block)
+    unsigned int* px_local = nullptr;         // seq[2], ticket[2], status
+    bool peer_ready = false;
+    PeerExchange px[2];
 };
 constexpr int kMaxTimeline = 1024;
 
@@ -663,6 +669,12 @@ static int32_t cache_build(oxg4_cache* c) {
         TRY(dalloc(c, &c->gu_part, (size_t)c->s_gu * B * 2 * m->I));
         TRY(dalloc(c, &c->down_part, (size_t)c->s_down * B * H));
         TRY(dalloc(c, &c->tc_err, 1));
+        if (m->tp > 1) {
+            const size_t bytes = sizeof(float) * 2 * (size_t)m->tp * B * H + sizeof(unsigned int) * 2 * kMaxTp;
+            CK(cudaMalloc(&c->px_block, bytes));          // own allocation: its IPC handle is exported
+            CK(cudaMemset(c->px_block, 0, bytes));
+            TRY(dalloc(c, &c->px_local, 8));
+        }
     }
     CK(cudaMallocHost(&c->h_tokens, sizeof(uint32_t) * B));
     CK(cudaMallocHost(&c->h_ctl, sizeof(StepCtl)));
@@ -682,6 +694,9 @@ extern "C" void oxg4_cache_destroy(oxg4_cache* c) {
         if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
         if (g.second.graph) cudaGraphDestroy(g.second.graph);
     }
+    for (int r = 0; r < kMaxTp; ++r)
+        if (c->px_peer_base[r] && c->px_peer_base[r] != c->px_block) cudaIpcCloseMemHandle(c->px_peer_base[r]);
+    if (c->px_block) cudaFree(c->px_block);
     for (void* p : c->owned) cudaFree(p);
     if (c->h_tokens) cudaFreeHost(c->h_tokens);
     if (c->h_ctl) cudaFreeHost(c->h_ctl);
@@ -718,6 +733,56 @@ extern "C" int32_t oxg4_cache_create(oxg4_model* m, int32_t batch, const int32_t
         return s;
     }
     *out = c;
+    return OXG4_OK;
+}
+
+extern "C" int32_t oxg4_cache_tp_export(oxg4_cache* c, void* handle_out_64) {
+    if (!c || !handle_out_64) return fail(OXG4_INVALID_ARGUMENT, "null argument");
+    if (!c->px_block) return fail(OXG4_UNSUPPORTED, "this cache table has no peer exchange buffer (needs tp_size > 1 and 8..64 sequences)");
+    TRY(bind_device(c->m));
+    cudaIpcMemHandle_t h;
+    CK(cudaIpcGetMemHandle(&h, c->px_block));
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    memcpy(handle_out_64, &h, 64);
+    return OXG4_OK;
+}
+
+extern "C" int32_t oxg4_cache_tp_connect(oxg4_cache* c, const void* handles) {
+    if (!c || !handles) return fail(OXG4_INVALID_ARGUMENT, "null argument");
+    if (!c->px_block) return fail(OXG4_UNSUPPORTED, "this cache table has no peer exchange buffer");
+    if (c->peer_ready) return OXG4_OK;
+    oxg4_model* m = c->m;
+    TRY(bind_device(m));
+    for (int r = 0; r < m->tp; ++r) {
+        if (r == m->tp_rank) { c->px_peer_base[r] = c->px_block; continue; }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const char*)handles + (size_t)r * 64, 64);
+        void* p = nullptr;
+        CK(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+        c->px_peer_base[r] = p;
+    }
+    const size_t bh = (size_t)c->B * m->H;
+    for (int kind = 0; kind < 2; ++kind) {
+        PeerExchange& x = c->px[kind];
+        x.tp = m->tp;
+        x.rank = m->tp_rank;
+        for (int r = 0; r < m->tp; ++r) {
+            char* base = (char*)c->px_peer_base[r];
+            x.push[r] = (float*)base + ((size_t)kind * m->tp + m->tp_rank) * bh;
+            x.flags[r] = (unsigned int*)(base + sizeof(float) * 2 * m->tp * bh) + (size_t)kind * kMaxTp;
+        }
+        x.gathered = (const float*)c->px_block + (size_t)kind * m->tp * bh;
+        x.seq = c->px_local + kind;
+        x.ticket = c->px_local + 2 + kind;
+        x.status = (int*)(c->px_local + 4);
+    }
+    c->peer_ready = getenv("OXG4_TP_NCCL") == nullptr;
+    // graphs captured before the connection used the NCCL path
+    for (auto& g : c->graphs) {
+        if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
+        if (g.second.graph) cudaGraphDestroy(g.second.graph);
+    }
+    c->graphs.clear();
     return OXG4_OK;
 }
 
@@ -1106,8 +1171,9 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
                 n.tokens = c->tokens;
                 n.embed_scale = sqrtf((float)H);
             } else {
-                n.raw = m->tp > 1 ? c->down_raw : c->down_part;
-                n.raw_splits = m->tp > 1 ? 1 : c->s_down;
+                n.raw = m->tp > 1 ? (c->peer_ready ? c->px[1].gathered : c->down_raw) : c->down_part;
+                n.raw_splits = m->tp > 1 ? (c->peer_ready ? m->tp : 1) : c->s_down;
+                if (m->tp > 1 && c->peer_ready) n.px = c->px[1];
                 n.w_post = m->layers[l - 1].post_ff_ln;
                 n.scalar = m->layers[l - 1].layer_scalar;
             }
@@ -1124,15 +1190,21 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
             ln.tc("o", c, p.wo, nullptr, c->x_a, H, qw, c->s_o, c->o_part, H, 0);
             const size_t bh = (size_t)B * H;
             const dim3 sum_grid((unsigned)((bh + kRowsThreads - 1) / kRowsThreads));
+            PeerExchange none{};
+            none.tp = 1;
+            const float* xo = c->peer_ready ? c->px[0].gathered : c->o_raw;        // what the next norm reads
+            const int xs = c->peer_ready ? m->tp : 1;                              // partials to add there
             if (m->tp > 1) {      // row-split projection: add the K-splits locally, then the ranks
-                ln.go("sum", sum_splits_kernel, sum_grid, dim3(kRowsThreads), 0, (const float*)c->o_part, c->s_o, bh, c->o_raw);
-                ln.allreduce(c->o_raw, bh);
+                ln.go("sum", sum_splits_kernel, sum_grid, dim3(kRowsThreads), 0, (const float*)c->o_part, c->s_o, bh, c->o_raw,
+                      c->peer_ready ? c->px[0] : none);
+                if (!c->peer_ready) ln.allreduce(c->o_raw, bh);
             }
             RowsNormArgs n2{};
             n2.B = B; n2.H = H;
             n2.h_in = c->hB; n2.h_out = c->hA;
-            n2.raw = m->tp > 1 ? c->o_raw : c->o_part;
-            n2.raw_splits = m->tp > 1 ? 1 : c->s_o;
+            n2.raw = m->tp > 1 ? xo : c->o_part;
+            n2.raw_splits = m->tp > 1 ? xs : c->s_o;
+            n2.px = (m->tp > 1 && c->peer_ready) ? c->px[0] : none;
             n2.w_post = p.post_attn_ln;
             n2.scalar = 1.0f;
             n2.w_norm = p.pre_ff_ln;
@@ -1145,8 +1217,8 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
             ln.tc("down", c, p.wdown, nullptr, c->x_i, H, m->I, c->s_down, c->down_part, H, 0);
             if (m->tp > 1) {
                 ln.go("sum", sum_splits_kernel, sum_grid, dim3(kRowsThreads), 0, (const float*)c->down_part, c->s_down, bh,
-                      c->down_raw);
-                ln.allreduce(c->down_raw, bh);
+                      c->down_raw, c->peer_ready ? c->px[1] : none);
+                if (!c->peer_ready) ln.allreduce(c->down_raw, bh);
             }
             continue;
         }
@@ -1239,8 +1311,9 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
         RowsNormArgs n{};
         n.B = B; n.H = H;
         n.h_in = c->hA; n.h_out = c->hB;
-        n.raw = m->tp > 1 ? c->down_raw : c->down_part;
-        n.raw_splits = m->tp > 1 ? 1 : c->s_down;
+        n.raw = m->tp > 1 ? (c->peer_ready ? c->px[1].gathered : c->down_raw) : c->down_part;
+        n.raw_splits = m->tp > 1 ? (c->peer_ready ? m->tp : 1) : c->s_down;
+        if (m->tp > 1 && c->peer_ready) n.px = c->px[1];
         n.w_post = m->layers[L - 1].post_ff_ln;
         n.scalar = m->layers[L - 1].layer_scalar;
         n.w_norm = m->final_norm;
@@ -1393,6 +1466,13 @@ static int32_t check_tc(oxg4_cache* c) {
     if (err) {
         cudaMemset(c->tc_err, 0, sizeof err);
         return fail(OXG4_TIMEOUT, "tcgen05 projection: a bounded barrier wait ran out (code %d)", err);
+    }
+    if (c->peer_ready) {
+        CK(cudaMemcpy(&err, c->px_local + 4, sizeof err, cudaMemcpyDeviceToHost));
+        if (err) {
+            cudaMemset(c->px_local + 4, 0, sizeof err);
+            return fail(OXG4_TIMEOUT, "tensor-parallel exchange: a peer did not publish its partial sums in time");
+        }
     }
     return OXG4_OK;
 }

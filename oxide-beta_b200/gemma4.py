@@ -164,6 +164,17 @@ class Gemma4CudaCacheTable:
     def reset(self):
         N.check(N.lib().oxg4_cache_reset(self._h))
 
+    def tp_export(self) -> bytes:
+        """64-byte CUDA IPC handle of this table's tensor-parallel exchange block."""
+        buf = C.create_string_buffer(64)
+        N.check(N.lib().oxg4_cache_tp_export(self._h, buf))
+        return buf.raw
+
+    def tp_connect(self, handles: Sequence[bytes]):
+        """`handles`: every rank's tp_export() result, in rank order."""
+        blob = b"".join(handles)
+        N.check(N.lib().oxg4_cache_tp_connect(self._h, C.c_char_p(blob)))
+
 
 class Gemma4CudaState:
     """Owner of an oxg4_model handle (persistent device weights + decode plan)."""

@@ -115,9 +115,14 @@ WORKER_GPU = textwrap.dedent("""
         ids = [pkg.Gemma4CudaState.tp_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
         tp.tp_init(ids[0])
-        for B, lens in ((3, [5, 9, 20]), (9, [3, 4, 5, 6, 7, 8, 9, 10, 11])):       # 9 rows: tcgen05 projections
+        nine = [3, 4, 5, 6, 7, 8, 9, 10, 11]                                        # 9 rows: tcgen05 projections
+        for B, lens, peer in ((3, [5, 9, 20], False), (9, nine, False), (9, nine, True)):
           prompts = [syn.prompt_ids(cfg["vocab_size"], n, seed=40 + b) for b, n in enumerate(lens)]
           table = tp.new_cache_table([40] * B, batch=B, page_tokens=8, kv_dtype=kv)
+          if peer and dtype == "bf16":          # sums over peer memory instead of NCCL all-reduces
+              handles = [None] * world
+              dist.all_gather_object(handles, table.tp_export())
+              table.tp_connect(handles)
           logits = tp.prefill_prompt(np.concatenate(prompts), table, lens=lens)
           toks = logits.argmax(-1).astype(np.uint32)
           out, _ = tp.decode_greedy(toks, table, 10)
@@ -138,7 +143,8 @@ WORKER_GPU = textwrap.dedent("""
               else:
                   assert np.abs(l1 - logits).max() <= 2e-2, np.abs(l1 - logits).max()
               print("tp parity ok", dtype, float(np.abs(l1 - logits).max()))
-        del table
+          dist.barrier()                        # no rank frees a table that a peer may still read
+          del table
         del tp
         dist.barrier()
     dist.destroy_process_group()
@@ -152,4 +158,4 @@ def test_tp2_matches_single_gpu():
         pytest.skip("needs 2 GPUs")
     r = _torchrun(WORKER_GPU, 2, extra_env={"NCCL_NVLS_ENABLE": "0"}, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-6000:]
-    assert r.stdout.count("tp parity ok") == 4
+    assert r.stdout.count("tp parity ok") == 6
