@@ -134,15 +134,23 @@ template <typename KT> DEVINL float kv_widen(KT v);
 template <> DEVINL float kv_widen<float>(float v) { return v; }
 template <> DEVINL float kv_widen<uint16_t>(uint16_t v) { return __uint_as_float((uint32_t)v << 16); }
 
-// CL = true: the splits of one (sequence, kv head) form a thread-block cluster (gridDim.x <= 16 CTAs);
-// partials stay in shared memory and are merged through distributed shared memory after one cluster
-// barrier. CL = false: partials go through global memory and the last CTA to arrive (atomic ticket)
-// merges them.
-template <typename KT, int D, int G, bool CL>
-__global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArgs a) {
+// Block-wide barrier policies: the whole CTA, or the first 512 threads of a CTA whose remaining warp does
+// other work (the persistent decode kernel keeps one warp for TMA).
+struct BarCta {
+    DEVINL void operator()() const { __syncthreads(); }
+};
+struct BarFirst512 {
+    DEVINL void operator()() const { asm volatile("bar.sync 1, 512;" ::: "memory"); }
+};
+
+// One CTA's share of a launch: split `s` of kv head `kvh` of sequence `b`, computed by the `nthreads`
+// threads that call it (tid = threadIdx.x < nthreads). `sm` is attn_smem_floats() floats of shared memory.
+// PDL: wait for the preceding kernel after the constant loads (stand-alone kernel only).
+template <typename KT, int D, int G, bool CL, bool PDL, typename BAR>
+DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, const int b, const int nthreads,
+                     const BAR bar) {
     constexpr int EPT = D / 32;
-    const int NW = blockDim.x >> 5;          // 16 warps when few CTAs exist (latency), 4 when many (occupancy)
-    extern __shared__ __align__(16) float sm[];
+    const int NW = nthreads >> 5;            // 16 warps when few CTAs exist (latency), 4 when many (occupancy)
     float* qs = sm;                          // [G][D]
     float* kcur = qs + G * D;                // [D]
     float* vcur = kcur + D;                  // [D]
@@ -153,7 +161,6 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
     __shared__ unsigned int s_last;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int s = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int half = D / 2;
 
     if (tid == 0 && a.pf_bytes) {
@@ -176,8 +183,10 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
         fr[e] = a.inv_freq[d % (D / 2)];
     }
     stamp(a.ts, 0);
-    pdl_wait();
-    pdl_launch();
+    if constexpr (PDL) {
+        pdl_wait();
+        pdl_launch();
+    }
     stamp(a.ts, 1);
 
     const bool active = a.tokens[b] != kInactiveToken;
@@ -212,7 +221,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
             for (int e = 0; e < EPT; ++e) {
                 float v = 0.0f;
                 for (int sp = 0; sp < a.qkv_splits; ++sp)
-                    v += a.qkv[((size_t)sp * a.B + b) * a.qkv_n + col + lane * EPT + e];
+                    v += __ldcg(a.qkv + ((size_t)sp * a.B + b) * a.qkv_n + col + lane * EPT + e);
                 t[e] = v;
                 ss += v * v;
             }
@@ -257,7 +266,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
                 }
             }
         }
-        __syncthreads();
+        bar();
         stamp(a.ts, 2);
 
         float q[G][EPT];
@@ -338,9 +347,9 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
 #pragma unroll
             for (int e = 0; e < EPT; ++e) wacc[((size_t)warp * G + g) * D + lane * EPT + e] = acc[g][e];
         }
-        __syncthreads();
+        bar();
         float* my = CL ? cpart : part + (size_t)s * (G * (D + 2));
-        for (int idx = tid; idx < G * D; idx += blockDim.x) {
+        for (int idx = tid; idx < G * D; idx += nthreads) {
             const int g = idx / D, d = idx % D;
             float M = -INFINITY;
             for (int w = 0; w < NW; ++w) M = fmaxf(M, wm[w * G + g]);
@@ -366,7 +375,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
             const int cs = (int)gridDim.x;
             const int per = (G * D + cs - 1) / cs;
             const int hi = min(G * D, (s + 1) * per);
-            for (int idx = s * per + tid; idx < hi; idx += blockDim.x) {
+            for (int idx = s * per + tid; idx < hi; idx += nthreads) {
                 const int g = idx / D, d = idx % D;
                 float M = -INFINITY;
                 for (int sp = 0; sp < n_eff; ++sp)
@@ -394,10 +403,10 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
     }
     // ---- last CTA of this (sequence, kv head) merges the split partials in split order ----
     __threadfence();
-    __syncthreads();
+    bar();
     if (tid == 0)
         s_last = (atomicAdd(&a.ticket[b * a.Nkv + kvh], 1u) == (unsigned)a.n_splits - 1u) ? 1u : 0u;
-    __syncthreads();
+    bar();
     if (s_last) {
         __threadfence();
         if (active) {
@@ -407,12 +416,12 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
             float* sf = wacc;                         // [n_eff][G] m, then exp(m - M)
             float* sl = wacc + a.n_splits * G;        // [n_eff][G] l
             float* sL = sl + a.n_splits * G;          // [G]
-            for (int idx = tid; idx < n_eff * G; idx += blockDim.x) {
+            for (int idx = tid; idx < n_eff * G; idx += nthreads) {
                 const int sp = idx / G, g = idx % G;
                 sf[idx] = __ldcg(part + (size_t)sp * PS + g * (D + 2) + D);
                 sl[idx] = __ldcg(part + (size_t)sp * PS + g * (D + 2) + D + 1);
             }
-            __syncthreads();
+            bar();
             if (warp < G) {
                 const int g = warp;
                 float M = -INFINITY;
@@ -428,8 +437,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
                 L = warp_sum(L);
                 if (lane == 0) sL[g] = L;
             }
-            __syncthreads();
-            for (int idx = tid; idx < G * D; idx += blockDim.x) {
+            bar();
+            for (int idx = tid; idx < G * D; idx += nthreads) {
                 const int g = idx / D, d = idx % D;
                 const float* ps = part + g * (D + 2) + d;
                 float A = 0.0f;
@@ -446,6 +455,16 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArg
         if (tid == 0) a.ticket[b * a.Nkv + kvh] = 0u;
     }
     stamp(a.ts, 3);
+}
+
+// CL = true: the splits of one (sequence, kv head) form a thread-block cluster (gridDim.x <= 16 CTAs);
+// partials stay in shared memory and are merged through distributed shared memory after one cluster
+// barrier. CL = false: partials go through global memory and the last CTA to arrive (atomic ticket)
+// merges them.
+template <typename KT, int D, int G, bool CL>
+__global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArgs a) {
+    extern __shared__ __align__(16) float attn_sm[];
+    attn_cta<KT, D, G, CL, true>(a, attn_sm, blockIdx.x, blockIdx.y, blockIdx.z, blockDim.x, BarCta{});
 }
 
 template <int D, int G>

@@ -25,6 +25,7 @@
 #include "sampling.cuh"
 #include "batch_ops.cuh"
 #include "tc_gemm.cuh"
+#include "decode_mega.cuh"
 #include "tp.h"
 
 using namespace oxg4;
@@ -98,6 +99,12 @@ struct oxg4_model {
     int num_sms = 148;
     bool use_pdl = true;
     bool far_prefetch = false;
+    // persistent decode kernel (one sequence, BF16 weights): geometry fixed by the model's shapes
+    bool mega_ok = false;
+    MegaLayer* mega_layers = nullptr;
+    int mega_R[4] = {1, 1, 1, 1}, mega_stage_bytes = 0, mega_stages = 0, mega_x_bytes = 0, mega_slot_floats = 0;
+    size_t mega_smem = 0;
+    int mega_pf_ahead = 8;
     int pf_cap_kb = 256;
     bool timeline = false;        // OXG4_TIMELINE: kernels stamp the global timer into the cache's buffer     // pull later kernels' weights into L2 during latency-bound kernels
     bool finalized = false;
@@ -362,6 +369,95 @@ static int32_t set_attn_attrs() {
     return OXG4_OK;
 }
 
+template <typename KT>
+static void (*pick_mega(int D, int G))(const MegaArgs) {
+#define PM(DD)                                                \
+    if (D == DD) {                                            \
+        if (G == 1) return decode_mega_kernel<KT, DD, 1>;     \
+        if (G == 2) return decode_mega_kernel<KT, DD, 2>;     \
+        if (G == 4) return decode_mega_kernel<KT, DD, 4>;     \
+        if (G == 8) return decode_mega_kernel<KT, DD, 8>;     \
+    }
+    PM(64) PM(128) PM(256)
+#undef PM
+    return nullptr;
+}
+
+// Geometry of the persistent decode kernel for this model, or mega_ok = false when a shape does not fit.
+static int32_t mega_setup(oxg4_model* m) {
+    m->mega_ok = false;
+    // opt-in while it is slower than the per-projection kernels on the workloads measured so far
+    if (m->es != 2 || m->tp != 1 || !getenv("OXG4_MEGA") || getenv("OXG4_DISABLE_MEGA")) return OXG4_OK;
+    const int H = m->H, D = m->D, L = m->cfg.num_hidden_layers;
+    auto fn16 = pick_mega<uint16_t>(D, m->G);
+    auto fn32 = pick_mega<float>(D, m->G);
+    if (!fn16 || !fn32) return OXG4_OK;
+    int coop = 0;
+    CK(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, m->device));
+    if (!coop) return OXG4_OK;
+    const int K[4] = {H, m->Nq * D, H, m->I};
+    if (H > kMegaMaxJ * kMegaConsumers) return OXG4_OK;
+    int stage_max = 24 * 1024;
+    if (const char* e = getenv("OXG4_MEGA_STAGE_KB")) stage_max = std::max(4, std::min(96, atoi(e))) * 1024;
+    int stage = 0, kmax = 0;
+    for (int k = 0; k < 4; ++k) {
+        // R rows per piece, each cut into nseg interleaved segments that become the 16 rows of the mma A operand
+        if (K[k] % 16 != 0) return OXG4_OK;
+        int R = 16;
+        auto fits = [&](int r) { return (K[k] / 16) % mega_nseg(r) == 0 && r * (K[k] * 2 + 16) <= stage_max; };
+        while (R > 1 && !fits(R)) R /= 2;
+        if (!fits(R)) return OXG4_OK;
+        m->mega_R[k] = R;
+        stage = std::max(stage, R * (K[k] * 2 + 16));
+        kmax = std::max(kmax, K[k]);
+    }
+    stage = (stage + 127) & ~127;
+    const int attn_floats = m->G * D + 2 * D + 2 * kMegaConsumerWarps * m->G + kMegaConsumerWarps * m->G * D + m->G * (D + 2);
+    int xb = std::max(((kmax + 255) & ~255) * 2, attn_floats * 4);
+    xb = (xb + 127) & ~127;
+    const int rows[4] = {m->p_qkv.N, H, m->I, H};
+    int slot_floats = 16;
+    for (int k = 0; k < 4; ++k) {
+        const int cnt = (rows[k] + m->num_sms - 1) / m->num_sms;
+        slot_floats = std::max(slot_floats, cnt * (k == 2 ? 2 : 1));
+    }
+    cudaFuncAttributes fa;
+    CK(cudaFuncGetAttributes(&fa, (const void*)fn16));
+    const int budget = 227 * 1024 - (int)fa.sharedSizeBytes - 256;
+    const int fixed = xb + H * 4 + slot_floats * 4;
+    int ns = (budget - fixed) / stage;
+    if (const char* e = getenv("OXG4_MEGA_STAGES")) ns = std::min(ns, atoi(e));
+    ns = std::min(ns, kMegaMaxStages);
+    if (ns < 2) return OXG4_OK;
+    while (ns & (ns - 1)) ns &= ns - 1;            // the kernel masks the piece counter: a power of two
+    if (const char* e = getenv("OXG4_MEGA_PF")) m->mega_pf_ahead = std::max(0, std::min(64, atoi(e)));
+    m->mega_stage_bytes = stage;
+    m->mega_stages = ns;
+    m->mega_x_bytes = xb;
+    m->mega_slot_floats = slot_floats;
+    m->mega_smem = (size_t)ns * stage + fixed;
+    TRY(allow_big_smem(fn16));
+    TRY(allow_big_smem(fn32));
+    int occ = 0;
+    CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn16, kMegaThreads, m->mega_smem));
+    if (occ < 1) return OXG4_OK;
+    std::vector<MegaLayer> hl(L);
+    for (int l = 0; l < L; ++l) {
+        const LayerPlan& p = m->layers[l];
+        MegaLayer& g = hl[l];
+        g.wqkv = p.wqkv; g.wo = p.wo; g.wgate = p.wgate; g.wup = p.wup; g.wdown = p.wdown;
+        g.input_ln = p.input_ln; g.post_attn_ln = p.post_attn_ln; g.pre_ff_ln = p.pre_ff_ln;
+        g.post_ff_ln = p.post_ff_ln; g.q_norm = p.q_norm; g.k_norm = p.k_norm; g.inv_freq = p.inv_freq;
+        g.layer_scalar = p.layer_scalar;
+        g.sliding = p.sliding ? 1 : 0;
+        g.rotary_half = p.rotary_dim / 2;
+    }
+    CK(cudaMalloc(&m->mega_layers, sizeof(MegaLayer) * L));
+    CK(cudaMemcpy(m->mega_layers, hl.data(), sizeof(MegaLayer) * L, cudaMemcpyHostToDevice));
+    m->mega_ok = true;
+    return OXG4_OK;
+}
+
 extern "C" int32_t oxg4_model_finalize(oxg4_model* m) {
     if (!m) return fail(OXG4_INVALID_ARGUMENT, "null model");
     if (m->finalized) return OXG4_OK;
@@ -440,6 +536,7 @@ extern "C" int32_t oxg4_model_finalize(oxg4_model* m) {
     TRY((set_attn_attrs<uint16_t, 64>())); TRY((set_attn_attrs<uint16_t, 128>())); TRY((set_attn_attrs<uint16_t, 256>()));
     TRY((set_attn_attrs<float, 64>())); TRY((set_attn_attrs<float, 128>())); TRY((set_attn_attrs<float, 256>()));
     TRY(allow_big_smem(topk_stage2_kernel));
+    TRY(mega_setup(m));
     CK(cudaDeviceSynchronize());
     m->finalized = true;
     return OXG4_OK;
@@ -539,6 +636,11 @@ struct oxg4_cache {
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     unsigned long long* ts_buf = nullptr;     // [kMaxTimeline][4] optional device timeline
     // tcgen05 path (eight or more sequences): BF16 activations, K-split partial outputs, error flag
+    bool use_mega = false;                    // one sequence, BF16 weights: the whole layer stack is one persistent kernel
+    MegaKv* mega_kv = nullptr;
+    MegaSync* mega_sync = nullptr;
+    int* mega_status = nullptr;               // pinned, mapped: the kernel writes it only when it gives up
+    int mega_splits_full = 1, mega_splits_slide = 1;
     bool use_tc = false;
     int s_qkv = 1, s_o = 1, s_gu = 1, s_down = 1;
     uint16_t *x_h = nullptr, *x_a = nullptr, *x_i = nullptr;
@@ -624,7 +726,22 @@ static int32_t cache_build(oxg4_cache* c) {
         c->splits_full = pow2_floor(c->splits_full);
         c->splits_slide = pow2_floor(c->splits_slide);
     }
-    const int smax = std::max(c->splits_full, c->splits_slide);
+    int smax = std::max(c->splits_full, c->splits_slide);
+    c->use_mega = m->mega_ok && B == 1;
+    if (c->use_mega) {
+        // attention inside the persistent kernel: (split, kv head) units over all CTAs, merged by ticket
+        const int per = std::max(1, m->num_sms / m->Nkv);
+        c->mega_splits_full = std::max(1, std::min(per, (maxf + c->min_split - 1) / c->min_split));
+        c->mega_splits_slide = std::max(1, std::min(per, (maxs + c->min_split - 1) / c->min_split));
+        smax = std::max({smax, c->mega_splits_full, c->mega_splits_slide});
+        std::vector<MegaKv> hk(L);
+        for (int l = 0; l < L; ++l) { hk[l].k = c->kpool[l]; hk[l].v = c->vpool[l]; }
+        TRY(dalloc(c, &c->mega_kv, (size_t)L));
+        CK(cudaMemcpy(c->mega_kv, hk.data(), sizeof(MegaKv) * L, cudaMemcpyHostToDevice));
+        TRY(dalloc(c, &c->mega_sync, 1));
+        CK(cudaHostAlloc(&c->mega_status, sizeof(int), cudaHostAllocMapped));
+        *c->mega_status = 0;
+    }
     TRY(dalloc(c, &c->tokens, B));
     TRY(dalloc(c, &c->pos, B));
     TRY(dalloc(c, &c->seen, (size_t)B * m->V));
@@ -697,6 +814,7 @@ extern "C" void oxg4_cache_destroy(oxg4_cache* c) {
     for (int r = 0; r < kMaxTp; ++r)
         if (c->px_peer_base[r] && c->px_peer_base[r] != c->px_block) cudaIpcCloseMemHandle(c->px_peer_base[r]);
     if (c->px_block) cudaFree(c->px_block);
+    if (c->mega_status) cudaFreeHost(c->mega_status);
     for (void* p : c->owned) cudaFree(p);
     if (c->h_tokens) cudaFreeHost(c->h_tokens);
     if (c->h_ctl) cudaFreeHost(c->h_ctl);
@@ -920,6 +1038,7 @@ struct Launcher {
     oxg4_model* m;
     unsigned long long* ts_base = nullptr;
     int cluster_x = 0;            // > 0: launch the next kernel with thread-block clusters of this many CTAs along x
+    bool coop = false;            // launch the next kernel cooperatively (all CTAs resident at once), without PDL
     int kernels = 0;
     unsigned long long* ts() const { return (ts_base && kernels < kMaxTimeline) ? ts_base + (size_t)kernels * 4 : nullptr; }
     int32_t status = OXG4_OK;
@@ -940,7 +1059,11 @@ struct Launcher {
         cfg.stream = m->stream;
         cudaLaunchAttribute attr[2];
         int na = 0;
-        if (m->use_pdl && !m->profiling) {
+        if (coop) {
+            attr[na].id = cudaLaunchAttributeCooperative;
+            attr[na].val.cooperative = 1;
+            ++na;
+        } else if (m->use_pdl && !m->profiling) {
             attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
             attr[na].val.programmaticStreamSerializationAllowed = 1;
             ++na;
@@ -1148,7 +1271,44 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
         ln.go("attn", fn, dim3(a.n_splits, m->Nkv, B), dim3(aw * 32), smem, a);
         ln.cluster_x = 0;
     };
-    for (int l = 0; l < L; ++l) {
+    const bool mega = c->use_mega && tr == nullptr;
+    if (mega) {
+        // ---- one sequence, BF16 weights: every layer in one persistent cooperative kernel ----
+        MegaArgs g{};
+        g.layers = m->mega_layers;
+        g.kv = c->mega_kv;
+        g.L = L; g.H = H; g.I = m->I; g.Nq = m->Nq; g.Nkv = m->Nkv; g.qkv_n = m->p_qkv.N;
+        for (int k = 0; k < 4; ++k) g.R[k] = m->mega_R[k];
+        g.stage_bytes = m->mega_stage_bytes;
+        g.n_stages = m->mega_stages;
+        g.pf_ahead = m->mega_pf_ahead;
+        g.x_bytes = m->mega_x_bytes;
+        g.slot_floats = m->mega_slot_floats;
+        g.embed = (const uint16_t*)m->embed;
+        g.tokens = c->tokens;
+        g.embed_scale = sqrtf((float)H);
+        g.eps = m->cfg.rms_norm_eps;
+        g.qkv_raw = c->qkv_raw; g.attn_out = c->attn_out; g.o_raw = c->o_raw; g.gu_raw = c->gu_raw;
+        g.down_raw = c->down_raw; g.h_out = c->hA;
+        g.pos = c->pos;
+        g.pt_full = c->pt_full; g.pt_slide = c->pt_slide; g.cap_full = c->cap_full; g.cap_slide = c->cap_slide;
+        g.pps_full = c->pps_full; g.pps_slide = c->pps_slide;
+        g.page_tokens = c->PT;
+        g.splits_full = c->mega_splits_full; g.splits_slide = c->mega_splits_slide;
+        g.min_split = c->min_split;
+        g.part = c->attn_part;
+        g.ticket = c->attn_ticket;
+        g.sync = c->mega_sync;
+        g.status = c->mega_status;
+        g.ts = (ln.ts() && 15 * L + 2 + 4 * (ln.kernels + 4) <= kMaxTimeline * 4) ? ln.ts() : nullptr;
+        if (ln.status == OXG4_OK && cudaMemsetAsync(c->mega_sync, 0, sizeof(MegaSync), m->stream) != cudaSuccess)
+            ln.status = fail(OXG4_CUDA, "Gemma 4 CUDA error: cudaMemsetAsync failed");
+        auto fn = c->kv_dtype == OXG4_BF16 ? pick_mega<uint16_t>(D, m->G) : pick_mega<float>(D, m->G);
+        ln.coop = true;
+        ln.go("mega", fn, dim3(m->num_sms), dim3(kMegaThreads), m->mega_smem, g);
+        ln.coop = false;
+    }
+    for (int l = 0; l < L && !mega; ++l) {
         const LayerPlan& p = m->layers[l];
         if (c->use_tc) {
             // ---- eight or more sequences: tcgen05 projections fed by TMA, per-row kernels around them ----
@@ -1460,6 +1620,11 @@ static void advance_host(oxg4_cache* c, const uint32_t* tokens, int steps = 1) {
 
 // the tcgen05 kernels raise a device flag instead of hanging when one of their bounded waits runs out
 static int32_t check_tc(oxg4_cache* c) {
+    if (c->use_mega && *(volatile int*)c->mega_status != 0) {      // mapped host word, read after a stream sync
+        const int code = *c->mega_status;
+        *c->mega_status = 0;
+        return fail(OXG4_TIMEOUT, "persistent decode kernel: a bounded wait ran out (code %d)", code);
+    }
     if (!c->use_tc) return OXG4_OK;
     int err = 0;
     CK(cudaMemcpy(&err, c->tc_err, sizeof err, cudaMemcpyDeviceToHost));
