@@ -52,6 +52,7 @@ struct AttnArgs {
     const void* pf_ptr;
     unsigned long long pf_bytes;
     unsigned long long* ts;  // optional timeline slots of this launch (4 entries) or null
+    unsigned long long* ts_mid;  // optional: one more stamp, taken when the CTA's own partial is complete
 };
 
 template <typename KT, int EPT> struct KVec;
@@ -146,7 +147,7 @@ struct BarFirst512 {
 // One CTA's share of a launch: split `s` of kv head `kvh` of sequence `b`, computed by the `nthreads`
 // threads that call it (tid = threadIdx.x < nthreads). `sm` is attn_smem_floats() floats of shared memory.
 // PDL: wait for the preceding kernel after the constant loads (stand-alone kernel only).
-template <typename KT, int D, int G, bool CL, bool PDL, typename BAR>
+template <typename KT, int D, int G, bool CL, bool PDL, bool DEEP, typename BAR>
 DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, const int b, const int nthreads,
                      const BAR bar) {
     constexpr int EPT = D / 32;
@@ -158,6 +159,7 @@ DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, c
     float* wl = wm + NW * G;                 // [NW][G]
     float* wacc = wl + NW * G;               // [NW][G][D]
     float* cpart = wacc + NW * G * D;        // [G][D + 2] this CTA's partial (cluster variant)
+    float* rope = cpart + G * (D + 2);       // [D] cos (first half) and sin (second half) of pos * inv_freq
     __shared__ unsigned int s_last;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -174,21 +176,18 @@ DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, c
         }
     }
     // model constants for this lane's slice of a head: fetched before the dependency wait
-    float wq[EPT], wk[EPT], fr[EPT];
+    float wq[EPT], wk[EPT];
 #pragma unroll
     for (int e = 0; e < EPT; ++e) {
         const int d = lane * EPT + e;
         wq[e] = a.q_norm[d];
         wk[e] = a.k_norm[d];
-        fr[e] = a.inv_freq[d % (D / 2)];
     }
-    stamp(a.ts, 0);
-    if constexpr (PDL) {
-        pdl_wait();
-        pdl_launch();
-    }
-    stamp(a.ts, 1);
-
+    // Step state (token, position, ring capacity, page table) is written by the step's first kernel or the
+    // previous step's last one. Every kernel of the step waits for its predecessor BEFORE it lets its
+    // successor start, so when this code runs, everything but the immediately preceding kernel (the QKV
+    // projection) has completed: the step state may be read, and the rotation factors computed, ahead
+    // of the dependency wait.
     const bool active = a.tokens[b] != kInactiveToken;
     const int pos = a.pos[b];
     const int cap = a.cap[b];
@@ -197,16 +196,32 @@ DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, c
     const int n_eff = min(a.n_splits, (n + a.min_split - 1) / a.min_split);
     const bool has_work = active && s < n_eff;
     float* part = a.part + (((size_t)b * a.Nkv + kvh) * a.n_splits) * (size_t)(G * (D + 2));
+    size_t cur_off = 0;
+    if (has_work) {
+        const int slot_cur = pos % cap;
+        cur_off = (((size_t)a.page_table[(size_t)b * a.pages_per_seq + slot_cur / a.page_tokens] * a.Nkv + kvh) *
+                       a.page_tokens + (slot_cur % a.page_tokens)) * (size_t)D;
+        // rotation factors of this position, one cosf or sinf per thread instead of 2 * D / 32 per lane
+        for (int i = tid; i < D; i += nthreads) {
+            const int fi = i % half;
+            if (fi < a.rotary_half) {
+                const float angle = (float)pos * a.inv_freq[fi];
+                rope[i] = i < half ? cosf(angle) : sinf(angle);
+            }
+        }
+    }
+    stamp(a.ts, 0);
+    if constexpr (PDL) {
+        pdl_wait();
+        pdl_launch();
+    }
+    stamp(a.ts, 1);
 
     if (has_work) {
         const int begin = lo + (int)(((long long)n * s) / n_eff);
         const int end = lo + (int)(((long long)n * (s + 1)) / n_eff);
         const bool owner = (s == n_eff - 1);        // the range that contains `pos`
-        const int slot_cur = pos % cap;
-        const size_t cur_off =
-            (((size_t)a.page_table[(size_t)b * a.pages_per_seq + slot_cur / a.page_tokens] * a.Nkv + kvh) *
-                 a.page_tokens + (slot_cur % a.page_tokens)) * (size_t)D;
-
+        bar();                                      // the rotation factors are in shared memory
         // tasks 0..G-1: query heads (norm + rope); task G: key (norm + rope + append);
         // task G+1: value (unit norm + append). One warp per task.
         const int n_tasks = owner ? G + 2 : G;
@@ -239,10 +254,9 @@ DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, c
                     const int fi = d % half;
                     float v = dst[d];
                     if (fi < a.rotary_half) {
-                        const float angle = (float)pos * fr[e];
                         const float pv = dst[d < half ? d + half : d - half];
                         const float rotated = d < half ? -pv : pv;
-                        v = v * cosf(angle) + rotated * sinf(angle);
+                        v = v * rope[fi] + rotated * rope[half + fi];
                     }
                     o[e] = v;
                 }
@@ -326,18 +340,21 @@ DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, c
             }
             consume(kf, vf);
         };
-        // two positions per step, the next step's loads issued before this step's arithmetic
-        Raw k0, v0, k1, v1;
+        // PD positions per step, the next step's loads issued before this step's arithmetic: 2 * PD rows of
+        // K and of V in flight per warp (PD = 4 when one sequence has the whole GPU and latency is all that counts)
+        constexpr int PD = DEEP ? 4 : 2;
+        Raw kr[PD], vr[PD];
         int p = begin + warp;
-        issue(p, k0, v0);
-        issue(p + NW, k1, v1);
-        for (; p < end; p += 2 * NW) {
-            Raw nk0, nv0, nk1, nv1;
-            issue(p + 2 * NW, nk0, nv0);
-            issue(p + 3 * NW, nk1, nv1);
-            use(p, k0, v0);
-            use(p + NW, k1, v1);
-            k0 = nk0; v0 = nv0; k1 = nk1; v1 = nv1;
+#pragma unroll
+        for (int q = 0; q < PD; ++q) issue(p + q * NW, kr[q], vr[q]);
+        for (; p < end; p += PD * NW) {
+            Raw nk[PD], nv[PD];
+#pragma unroll
+            for (int q = 0; q < PD; ++q) issue(p + (PD + q) * NW, nk[q], nv[q]);
+#pragma unroll
+            for (int q = 0; q < PD; ++q) use(p + q * NW, kr[q], vr[q]);
+#pragma unroll
+            for (int q = 0; q < PD; ++q) { kr[q] = nk[q]; vr[q] = nv[q]; }
         }
 
         // merge the warps of this CTA (fixed warp order)
@@ -402,6 +419,7 @@ DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, c
         return;
     }
     // ---- last CTA of this (sequence, kv head) merges the split partials in split order ----
+    stamp(a.ts_mid, 0);
     __threadfence();
     bar();
     if (tid == 0)
@@ -442,8 +460,15 @@ DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, c
                 const int g = idx / D, d = idx % D;
                 const float* ps = part + g * (D + 2) + d;
                 float A = 0.0f;
-#pragma unroll 8
-                for (int sp = 0; sp < n_eff; ++sp) A += sf[sp * G + g] * __ldcg(ps + (size_t)sp * PS);
+                // sixteen independent loads in flight per round trip to L2
+                for (int s0 = 0; s0 < n_eff; s0 += 16) {
+                    float v[16];
+#pragma unroll
+                    for (int q = 0; q < 16; ++q) v[q] = (s0 + q < n_eff) ? __ldcg(ps + (size_t)(s0 + q) * PS) : 0.0f;
+#pragma unroll
+                    for (int q = 0; q < 16; ++q)
+                        if (s0 + q < n_eff) A += sf[(s0 + q) * G + g] * v[q];
+                }
                 {
                     const size_t oi = (size_t)b * a.Nq * D + (size_t)(kvh * G + g) * D + d;
                     const float ov = A / sL[g];
@@ -461,15 +486,15 @@ DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, c
 // partials stay in shared memory and are merged through distributed shared memory after one cluster
 // barrier. CL = false: partials go through global memory and the last CTA to arrive (atomic ticket)
 // merges them.
-template <typename KT, int D, int G, bool CL>
+template <typename KT, int D, int G, bool CL, bool DEEP = false>
 __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArgs a) {
     extern __shared__ __align__(16) float attn_sm[];
-    attn_cta<KT, D, G, CL, true>(a, attn_sm, blockIdx.x, blockIdx.y, blockIdx.z, blockDim.x, BarCta{});
+    attn_cta<KT, D, G, CL, true, DEEP>(a, attn_sm, blockIdx.x, blockIdx.y, blockIdx.z, blockDim.x, BarCta{});
 }
 
 template <int D, int G>
 inline size_t attn_smem_bytes() {
-    return sizeof(float) * (size_t)(G * D + 2 * D + 2 * kAttnWarps * G + kAttnWarps * G * D + G * (D + 2));   // + page table
+    return sizeof(float) * (size_t)(G * D + 2 * D + 2 * kAttnWarps * G + kAttnWarps * G * D + G * (D + 2) + D);   // + page table
 }
 
 }  // namespace oxg4

@@ -39,7 +39,7 @@ namespace oxg4 {
 constexpr int kMegaConsumerWarps = 16;
 constexpr int kMegaConsumers = kMegaConsumerWarps * 32;      // 512: attention.cuh's BarFirst512 counts on it
 constexpr int kMegaThreads = kMegaConsumers + 32;            // + the producer warp
-constexpr int kMegaMaxStages = 16;
+constexpr int kMegaStages = kMegaConsumerWarps;             // one ring stage per consumer warp
 constexpr int kMegaMaxJ = 11;                                 // hidden size <= 11 * 512
 constexpr unsigned int kMegaSpinLimit = 1u << 22;             // grid-barrier polls before giving up
 
@@ -55,15 +55,26 @@ struct MegaKv {               // per-layer cache pools (device array, per cache 
 struct MegaSync {
     unsigned int arrived;     // grid barrier counter (zeroed before every launch)
     unsigned int abort;       // non-zero: a bounded wait ran out somewhere
+    unsigned int first;       // which wait gave up first: 1 grid barrier, 2 producer (stage not released), 3 consumer (piece not delivered)
+    unsigned int info[3];     // of that wait: CTA, piece or barrier number, warp
 };
+DEVINL void mega_fail(MegaSync* sy, int* status, unsigned int code, unsigned int cta, unsigned int n, unsigned int w) {
+    if (atomicCAS(&sy->first, 0u, code) == 0u) {
+        sy->info[0] = cta;
+        sy->info[1] = n;
+        sy->info[2] = w;
+        *(volatile int*)status = (int)(code | (cta << 4) | (n << 12) | (w << 26));
+    }
+    atomicExch(&sy->abort, 1u);
+}
 
 struct MegaArgs {
     const MegaLayer* layers;
     const MegaKv* kv;
     int L, H, I, Nq, Nkv, qkv_n;
-    int R[4];                 // rows per piece: QKV, O, gate/up, down
-    int stage_bytes, n_stages;
-    int pf_ahead;             // pieces the L2 prefetch runs in front of the ring (0: off)
+    int R[4], F[4];           // rows per piece and fractions per row: QKV, O, gate/up, down
+    int stage_bytes;
+    int pf_kb;                // KiB of the next matrix kind's share a CTA prefetches into L2 (0: off)
     int x_bytes;              // shared bytes of the activation / attention scratch region
     int slot_floats;          // shared floats for the partial sums
     const uint16_t* embed;
@@ -136,29 +147,32 @@ DEVINL float cons_sum(float v, float* red) {
 // B has eight columns).
 __host__ DEVINL int mega_nseg(int R) { return R >= 16 ? 1 : (16 / R > 8 ? 8 : 16 / R); }
 
-// A CTA's share of one matrix kind.
+// A CTA's share of one matrix kind. A piece is R whole rows, or (R == 1, F > 1) one of the F contiguous
+// fractions of a row that is too long for a stage.
 struct MegaShare {
     int r0, cnt;              // first row (pair for gate/up) and number of rows (pairs)
-    int R, np;                // rows per piece, pieces (gate/up: gate and up pieces alternate)
+    int R, F, np;             // rows per piece, fractions per row, pieces (gate/up: gate and up row blocks alternate)
 };
-DEVINL MegaShare mega_share(int rows, int R, bool pairs) {
+DEVINL MegaShare mega_share(int rows, int R, int F, bool pairs) {
     MegaShare s;
     block_range(rows, gridDim.x, blockIdx.x, s.r0, s.cnt);
     s.R = R;
-    s.np = (s.cnt + R - 1) / R * (pairs ? 2 : 1);
+    s.F = F;
+    s.np = (s.cnt + R - 1) / R * F * (pairs ? 2 : 1);
     return s;
 }
 
 template <typename KT, int D, int G>
 __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const MegaArgs a) {
     extern __shared__ __align__(128) unsigned char mega_smem[];
-    __shared__ __align__(8) uint64_t full[kMegaMaxStages], empty[kMegaMaxStages];
+    __shared__ __align__(8) uint64_t full[kMegaStages], empty[kMegaStages];
     __shared__ float red[kMegaConsumerWarps];
     __shared__ float scratch[kMegaConsumerWarps * 16];
     __shared__ volatile int dead;              // a consumer of this CTA gave up (written only before a consumer barrier)
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int H = a.H, NS = a.n_stages;
+    const int H = a.H;
+    constexpr int NS = kMegaStages;
     unsigned char* ring = mega_smem;                                         // [NS][stage_bytes]
     unsigned char* xreg = ring + (size_t)NS * a.stage_bytes;                 // activations (BF16) / attention scratch
     float* h_s = reinterpret_cast<float*>(xreg + a.x_bytes);                 // [H] residual stream
@@ -176,68 +190,80 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
     __syncthreads();
 
     // matrix kinds: 0 QKV [qkv_n, H], 1 O [H, Nq*D], 2 gate/up [I, H] x 2, 3 down [H, I]
-    const MegaShare sh0 = mega_share(a.qkv_n, a.R[0], false);
-    const MegaShare sh1 = mega_share(H, a.R[1], false);
-    const MegaShare sh2 = mega_share(a.I, a.R[2], true);
-    const MegaShare sh3 = mega_share(H, a.R[3], false);
+    const MegaShare sh0 = mega_share(a.qkv_n, a.R[0], a.F[0], false);
+    const MegaShare sh1 = mega_share(H, a.R[1], a.F[1], false);
+    const MegaShare sh2 = mega_share(a.I, a.R[2], a.F[2], true);
+    const MegaShare sh3 = mega_share(H, a.R[3], a.F[3], false);
 
     if (warp == kMegaConsumerWarps) {
         // ================= producer: the CTA's share of the whole step's weight stream =================
+        // One thread issues everything, so the work per piece is kept to a wait, an expect and one bulk copy
+        // per row: all addressing is incremental.
         if (lane == 0) {
             unsigned int it = 0, st = 0, par = 0;
             bool ok = true;
-            // position in the CTA's weight stream: layer, matrix kind (0 QKV, 1 O, 2 gate/up, 3 down), piece
-            struct Cursor { int l, kind, j; };
-            auto share = [&](int kind) -> const MegaShare& { return kind == 0 ? sh0 : (kind == 1 ? sh1 : (kind == 2 ? sh2 : sh3)); };
-            auto settle = [&](Cursor& c) {               // skip matrix kinds of which this CTA owns no row
-                while (c.l < a.L && c.j >= share(c.kind).np) {
-                    c.j = 0;
-                    if (++c.kind == 4) { c.kind = 0; ++c.l; }
+            // `blocks` row blocks of `rows_left` rows in all, each block as s.F pieces (one per row fraction)
+            auto stream = [&](const char* base, const MegaShare& s, const int K) {
+                const uint32_t rowb = (uint32_t)K * 2u;
+                const uint32_t fb = rowb / (uint32_t)s.F;                  // bytes of one row fraction
+                const char* src = base + (size_t)s.r0 * rowb;
+                for (int left = s.cnt; left > 0 && ok; left -= s.R, src += (size_t)s.R * rowb) {
+                    const int nrows = min(s.R, left);
+                    for (int f = 0; f < s.F; ++f) {
+                        if (dead || !mega_wait(&empty[st], par ^ 1u, &dead, &a.sync->abort)) { ok = false; return; }
+                        mbar_expect_tx(&full[st], (uint32_t)nrows * fb);
+                        unsigned char* dst = ring + (size_t)st * a.stage_bytes;
+                        const char* sp = src + (size_t)f * fb;
+                        for (int r = 0; r < nrows; ++r, dst += fb + 16u, sp += rowb)   // rows land 16 bytes apart (see consume)
+                            bulk_load(dst, sp, fb, &full[st]);
+                        ++it;
+                        if (++st == (unsigned)NS) { st = 0; par ^= 1u; }
+                    }
                 }
             };
-            auto locate = [&](const Cursor& c, const char*& src, int& nrows, int& K) {
-                const MegaLayer& ly = a.layers[c.l];
-                const MegaShare& s = share(c.kind);
-                K = c.kind == 1 ? a.Nq * D : (c.kind == 3 ? a.I : H);
-                const void* base = c.kind == 0 ? ly.wqkv : (c.kind == 1 ? ly.wo : (c.kind == 3 ? ly.wdown : ((c.j & 1) ? ly.wup : ly.wgate)));
-                const int jr = c.kind == 2 ? (c.j >> 1) : c.j;
-                nrows = min(s.R, s.cnt - jr * s.R);
-                src = (const char*)base + (size_t)(s.r0 + jr * s.R) * K * 2;
-            };
-            Cursor cur{0, 0, 0}, pfc{0, 0, 0};
-            settle(cur);
-            settle(pfc);
-            unsigned int pf_it = 0;                     // pieces whose L2 prefetch has been issued
-            while (cur.l < a.L) {
-                // keep the L2 prefetch `pf_ahead` pieces in front of the ring: long stalls of the consumers
-                // (attention, barriers) then cost no HBM time, the ring refills from L2 afterwards
-                while (pfc.l < a.L && pf_it < it + (unsigned)a.pf_ahead) {
-                    const char* psrc;
-                    int pn, pK;
-                    locate(pfc, psrc, pn, pK);
-                    if (pf_it >= it) prefetch_l2_bulk(psrc, (size_t)pn * pK * 2);
-                    ++pf_it;
-                    ++pfc.j;
-                    settle(pfc);
+            // gate and up row blocks alternate, so that a pair's two dot products finish close together
+            auto stream2 = [&](const char* g0, const char* u0, const MegaShare& s, const int K) {
+                const uint32_t rowb = (uint32_t)K * 2u;
+                const uint32_t fb = rowb / (uint32_t)s.F;
+                size_t off = (size_t)s.r0 * rowb;
+                for (int left = s.cnt; left > 0 && ok; left -= s.R, off += (size_t)s.R * rowb) {
+                    const int nrows = min(s.R, left);
+                    for (int which = 0; which < 2; ++which) {
+                        const char* src = (which ? u0 : g0) + off;
+                        for (int f = 0; f < s.F; ++f) {
+                            if (dead || !mega_wait(&empty[st], par ^ 1u, &dead, &a.sync->abort)) { ok = false; return; }
+                            mbar_expect_tx(&full[st], (uint32_t)nrows * fb);
+                            unsigned char* dst = ring + (size_t)st * a.stage_bytes;
+                            const char* sp = src + (size_t)f * fb;
+                            for (int r = 0; r < nrows; ++r, dst += fb + 16u, sp += rowb) bulk_load(dst, sp, fb, &full[st]);
+                            ++it;
+                            if (++st == (unsigned)NS) { st = 0; par ^= 1u; }
+                        }
+                    }
                 }
-                // bounded wait for the consumers to release the stage
-                if (dead || !mega_wait(&empty[st], par ^ 1u, &dead, &a.sync->abort)) { ok = false; break; }
-                const char* src;
-                int nrows, K;
-                locate(cur, src, nrows, K);
-                const size_t rowb = (size_t)K * 2;
-                mbar_expect_tx(&full[st], (uint32_t)(nrows * rowb));
-                unsigned char* dst = ring + (size_t)st * a.stage_bytes;
-                for (int r = 0; r < nrows; ++r)           // rows land 16 bytes apart from back to back (see consume)
-                    bulk_load(dst + (size_t)r * (rowb + 16), src + (size_t)r * rowb, (uint32_t)rowb, &full[st]);
-                ++it;
-                if (++st == (unsigned)NS) { st = 0; par ^= 1u; }
-                ++cur.j;
-                settle(cur);
+            };
+            // L2 prefetch of the start of a share (at most pf_kb KiB), issued one matrix kind ahead: while the
+            // consumers sit in a barrier, a prologue or attention, HBM keeps working and the ring refills from L2
+            auto warm = [&](const char* base, const MegaShare& s, const int K, size_t cap) {
+                const size_t bytes = min((size_t)s.cnt * K * 2, cap);
+                const char* p0 = base + (size_t)s.r0 * K * 2;
+                for (size_t off = 0; off < bytes; off += 32768) prefetch_l2_bulk(p0 + off, min((size_t)32768, bytes - off));
+            };
+            const size_t cap = (size_t)a.pf_kb * 1024;
+            for (int l = 0; l < a.L && ok; ++l) {
+                const MegaLayer& ly = a.layers[l];
+                if (cap) warm((const char*)ly.wo, sh1, a.Nq * D, cap);
+                stream((const char*)ly.wqkv, sh0, H);
+                if (cap) { warm((const char*)ly.wgate, sh2, H, cap / 2); warm((const char*)ly.wup, sh2, H, cap / 2); }
+                stream((const char*)ly.wo, sh1, a.Nq * D);
+                if (cap) warm((const char*)ly.wdown, sh3, a.I, cap);
+                stream2((const char*)ly.wgate, (const char*)ly.wup, sh2, H);
+                if (cap && l + 1 < a.L) warm((const char*)a.layers[l + 1].wqkv, sh0, H, cap);
+                stream((const char*)ly.wdown, sh3, a.I);
             }
             if (!ok) {
+                if (!dead && !ld_relaxed_gpu(&a.sync->abort)) mega_fail(a.sync, a.status, 2u, blockIdx.x, it, 16u);
                 atomicExch(&a.sync->abort, 1u);
-                *(volatile int*)a.status = 2;
                 // copies in flight land in this CTA's shared memory: wait (bounded) until they have
                 const unsigned int issued = it;
                 const unsigned int first = issued > (unsigned)NS ? issued - NS : 0u;
@@ -263,8 +289,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
             while (ld_acquire_gpu(&a.sync->arrived) < target) {
                 if (++polls > kMegaSpinLimit || ((polls & 255u) == 0u && ld_relaxed_gpu(&a.sync->abort))) {
                     dead = 1;
-                    atomicExch(&a.sync->abort, 1u);
-                    *(volatile int*)a.status = 1;
+                    if (polls > kMegaSpinLimit) mega_fail(a.sync, a.status, 1u, blockIdx.x, gen, 0u);
                     break;
                 }
             }
@@ -276,25 +301,28 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
     };
 
     // dot products of xs[0..K) with this CTA's rows of one matrix kind on the tensor cores (mma.sync
-    // m16n8k16). A piece holds R weight rows and belongs to ONE warp (piece P of the step's stream goes to
-    // warp P % 16), so up to n_stages pieces are being multiplied at once and nothing is reduced across
-    // warps. Each row is cut into nseg = 16 / R interleaved segments (k-step q of segment sg is k-step
-    // q * nseg + sg of the row) and (row r, segment sg) is row r * nseg + sg of the 16-row A operand, so all
-    // of A is real weight data; column n of B is segment n of the activation vector and the useful outputs
-    // are C[r * nseg + sg][sg].
+    // m16n8k16). The ring has one stage per consumer warp: piece P of the step's stream lands in stage
+    // P % 16 and is multiplied by warp P % 16, so sixteen pieces are in work at once and nothing is reduced
+    // across warps. Each row (fraction) of a piece is cut into nseg = 16 / R interleaved segments (k-step
+    // q of segment sg is k-step q * nseg + sg) and (row r, segment sg) is row r * nseg + sg of the 16-row A
+    // operand, so all of A is real weight data; column n of B is segment n of the activation vector and
+    // the useful outputs are C[r * nseg + sg][sg].
     unsigned int pcount = 0;              // pieces of the stream consumed so far (same in every consumer thread)
     long long dbg_wait = 0, dbg_work = 0; // cycles warp 0 spent waiting for the ring / computing (timeline runs only)
+    const uint32_t my_stage = smem_u32(ring + (size_t)warp * a.stage_bytes);
     auto consume = [&](const int K, const MegaShare s, const bool gateup) {
-        const int R = s.R;
+        const int R = s.R, F = s.F;
         const int nseg = mega_nseg(R);
-        const int ksteps = (K >> 4) / nseg;                  // k-steps per segment
-        const uint32_t rstride = (uint32_t)K * 2u + 16u;     // rows sit 16 bytes apart from back to back: conflict-free ldmatrix
+        const int Kf = K / F;                                // elements of one row (fraction) of a piece
+        const int ksteps = (Kf >> 4) / nseg;                 // k-steps per segment
+        const uint32_t rstride = (uint32_t)Kf * 2u + 16u;    // rows sit 16 bytes apart from back to back: conflict-free ldmatrix
         const int g = lane >> 2, t = lane & 3;
         // ldmatrix.x4: lane l addresses row (l & 7) of matrix (l >> 3): A rows 0-7 / 8-15, k 0-7 / 8-15
         int arow = (lane & 7) + 8 * ((lane >> 3) & 1);
         if (nseg * R <= 8) arow &= 7;                        // a single row per piece: A rows 8..15 are not used
         const int a_r = arow / nseg, a_sg = arow % nseg;     // A row i is (row i / nseg, segment i % nseg)
         const uint32_t kstep_bytes = (uint32_t)nseg * 32u;
+        const uint32_t lane_off = (uint32_t)a_sg * 32u + (uint32_t)(lane >> 4) * 16u;
         // B operand: column g is segment g of the activations
         const bool bval = g < nseg;
         const uint32_t* xb = reinterpret_cast<const uint32_t*>(xs) + (bval ? g : 0) * 8 + t;
@@ -309,24 +337,21 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
         bool ok = alive;                  // this warp still follows the ring protocol
         int j = (int)((warp - (p0 & 15u)) & 15u);            // this warp's first piece of the phase
         for (; j < s.np; j += kMegaConsumerWarps) {
-            const unsigned int P = p0 + (unsigned)j;
-            const unsigned int st = P & (unsigned)(NS - 1);
-            const uint32_t par = (P / (unsigned)NS) & 1u;
+            const uint32_t par = ((p0 + (unsigned)j) >> 4) & 1u;      // the stage's fillings alternate parity
             const long long tw0 = a.ts ? clock64() : 0;
-            if (ok && !mega_wait(&full[st], par, &dead, &a.sync->abort)) {
+            if (ok && !mega_wait(&full[warp], par, &dead, &a.sync->abort)) {
                 ok = false;
                 dead = 1;
-                atomicExch(&a.sync->abort, 1u);
-                *(volatile int*)a.status = 3;
+                if (!ld_relaxed_gpu(&a.sync->abort)) mega_fail(a.sync, a.status, 3u, blockIdx.x, p0 + (unsigned)j, (unsigned)warp);
             }
             const long long tw1 = a.ts ? clock64() : 0;
             if (!ok) continue;
-            const int jr = gateup ? (j >> 1) : j;
+            const int blk = j / F, f = j - blk * F;
+            const int jr = gateup ? (blk >> 1) : blk;
             const int nrows = min(R, s.cnt - jr * R);
             float c0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, c1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            uint32_t addr = smem_u32(ring + (size_t)st * a.stage_bytes) + (uint32_t)min(a_r, nrows - 1) * rstride +
-                            (uint32_t)a_sg * 32u + (uint32_t)(lane >> 4) * 16u;
-            const uint32_t* xp = xb;
+            uint32_t addr = my_stage + (uint32_t)min(a_r, nrows - 1) * rstride + lane_off;
+            const uint32_t* xp = xb + f * (Kf >> 1);
             int ks = 0;
             for (; ks + 4 <= ksteps; ks += 4, addr += 4u * kstep_bytes, xp += 4 * xstep) {
                 uint32_t w[4][4], b[4][2];
@@ -351,18 +376,17 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
                 const uint32_t b0 = bval ? xp[0] : 0u, b1 = bval ? xp[4] : 0u;
                 mma_bf16_16816(c0, w0, w1, w2, w3, b0, b1);
             }
-            // the stage has been read: hand it back before the little reduction below
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[st]);
             // accumulator layout: [0] (row g, col 2t)  [1] (g, 2t+1)  [2] (g+8, 2t)  [3] (g+8, 2t+1)
             if (take_lo) scr[g] = (slo & 1) ? c0[1] + c1[1] : c0[0] + c1[0];
             if (take_hi) scr[g + 8] = (shi & 1) ? c0[3] + c1[3] : c0[2] + c1[2];
             __syncwarp();
+            // the accumulators depend on every ldmatrix of the piece: the stage can go back now
+            if (lane == 0) mbar_arrive(&empty[warp]);
             if (lane < nrows) {
                 float tot = 0.0f;
                 for (int sg = 0; sg < nseg; ++sg) tot += scr[lane * nseg + sg];
                 const int rloc = jr * R + lane;
-                slots[gateup ? 2 * rloc + (j & 1) : rloc] = tot;
+                slots[(gateup ? 2 * rloc + (blk & 1) : rloc) * F + f] = tot;
             }
             __syncwarp();
             if (a.ts) { dbg_wait += tw1 - tw0; dbg_work += clock64() - tw1; }
@@ -370,9 +394,13 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
         cons_sync();
         alive = !dead;
     };
-    auto row_total = [&](int rc) -> float { return slots[rc]; };
+    auto row_total = [&](int rc, int F) -> float {           // the fractions of a row, in order
+        float tot = slots[rc * F];
+        for (int f = 1; f < F; ++f) tot += slots[rc * F + f];
+        return tot;
+    };
     auto store_rows = [&](const MegaShare s, float* out) {
-        for (int r = tid; r < s.cnt; r += kMegaConsumers) out[s.r0 + r] = row_total(r);
+        for (int r = tid; r < s.cnt; r += kMegaConsumers) out[s.r0 + r] = row_total(r, s.F);
     };
     // xs = bf16(in[0..K))   (K a multiple of 4; `in` was written by other CTAs before the last grid barrier)
     auto load_plain = [&](const float* in, int K) {
@@ -512,9 +540,11 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
             at.pages_per_seq = ly.sliding ? a.pps_slide : a.pps_full;
             at.cap = ly.sliding ? a.cap_slide : a.cap_full;
             at.n_splits = ly.sliding ? a.splits_slide : a.splits_full;
+            at.ts = a.ts ? a.ts + 15 * a.L + 2 + 4 * l : nullptr;
+            at.ts_mid = at.ts ? at.ts : nullptr;       // slot 0 (entry) doubles as 'partial complete'
             const int units = at.n_splits * a.Nkv;
             for (int u = blockIdx.x; u < units; u += gridDim.x) {
-                attn_cta<KT, D, G, false, false>(at, reinterpret_cast<float*>(xreg), u % at.n_splits, u / at.n_splits, 0,
+                attn_cta<KT, D, G, false, false, false>(at, reinterpret_cast<float*>(xreg), u % at.n_splits, u / at.n_splits, 0,
                                                  kMegaConsumers, BarFirst512{});
                 cons_sync();
             }
@@ -536,7 +566,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
         consume(H, sh2, true);
         if (alive) {
             for (int r = tid; r < sh2.cnt; r += kMegaConsumers)
-                a.gu_raw[sh2.r0 + r] = gelu_mul(row_total(2 * r), row_total(2 * r + 1));
+                a.gu_raw[sh2.r0 + r] = gelu_mul(row_total(2 * r, sh2.F), row_total(2 * r + 1, sh2.F));
         }
         mark();
         grid_barrier();

@@ -102,9 +102,9 @@ struct oxg4_model {
     // persistent decode kernel (one sequence, BF16 weights): geometry fixed by the model's shapes
     bool mega_ok = false;
     MegaLayer* mega_layers = nullptr;
-    int mega_R[4] = {1, 1, 1, 1}, mega_stage_bytes = 0, mega_stages = 0, mega_x_bytes = 0, mega_slot_floats = 0;
+    int mega_R[4] = {1, 1, 1, 1}, mega_F[4] = {1, 1, 1, 1}, mega_stage_bytes = 0, mega_x_bytes = 0, mega_slot_floats = 0;
     size_t mega_smem = 0;
-    int mega_pf_ahead = 8;
+    int mega_pf_kb = 192;
     int pf_cap_kb = 256;
     bool timeline = false;        // OXG4_TIMELINE: kernels stamp the global timer into the cache's buffer     // pull later kernels' weights into L2 during latency-bound kernels
     bool finalized = false;
@@ -362,6 +362,14 @@ static int32_t set_attn_attrs() {
     TRY(allow_big_smem(attn_decode_kernel<KT, D, 2, true>));
     TRY(allow_big_smem(attn_decode_kernel<KT, D, 4, true>));
     TRY(allow_big_smem(attn_decode_kernel<KT, D, 8, true>));
+    TRY(allow_big_smem(attn_decode_kernel<KT, D, 1, true, true>));
+    TRY(allow_big_smem(attn_decode_kernel<KT, D, 2, true, true>));
+    TRY(allow_big_smem(attn_decode_kernel<KT, D, 4, true, true>));
+    TRY(allow_big_smem(attn_decode_kernel<KT, D, 8, true, true>));
+    CK(cudaFuncSetAttribute(attn_decode_kernel<KT, D, 1, true, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    CK(cudaFuncSetAttribute(attn_decode_kernel<KT, D, 2, true, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    CK(cudaFuncSetAttribute(attn_decode_kernel<KT, D, 4, true, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    CK(cudaFuncSetAttribute(attn_decode_kernel<KT, D, 8, true, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
     CK(cudaFuncSetAttribute(attn_decode_kernel<KT, D, 1, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
     CK(cudaFuncSetAttribute(attn_decode_kernel<KT, D, 2, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
     CK(cudaFuncSetAttribute(attn_decode_kernel<KT, D, 4, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
@@ -397,45 +405,46 @@ static int32_t mega_setup(oxg4_model* m) {
     if (!coop) return OXG4_OK;
     const int K[4] = {H, m->Nq * D, H, m->I};
     if (H > kMegaMaxJ * kMegaConsumers) return OXG4_OK;
-    int stage_max = 24 * 1024;
-    if (const char* e = getenv("OXG4_MEGA_STAGE_KB")) stage_max = std::max(4, std::min(96, atoi(e))) * 1024;
-    int stage = 0, kmax = 0;
-    for (int k = 0; k < 4; ++k) {
-        // R rows per piece, each cut into nseg interleaved segments that become the 16 rows of the mma A operand
-        if (K[k] % 16 != 0) return OXG4_OK;
-        int R = 16;
-        auto fits = [&](int r) { return (K[k] / 16) % mega_nseg(r) == 0 && r * (K[k] * 2 + 16) <= stage_max; };
-        while (R > 1 && !fits(R)) R /= 2;
-        if (!fits(R)) return OXG4_OK;
-        m->mega_R[k] = R;
-        stage = std::max(stage, R * (K[k] * 2 + 16));
-        kmax = std::max(kmax, K[k]);
-    }
-    stage = (stage + 127) & ~127;
-    const int attn_floats = m->G * D + 2 * D + 2 * kMegaConsumerWarps * m->G + kMegaConsumerWarps * m->G * D + m->G * (D + 2);
-    int xb = std::max(((kmax + 255) & ~255) * 2, attn_floats * 4);
+    // shared memory: activations / attention scratch, the residual stream, one result slot per row (fraction),
+    // and what is left is cut into sixteen ring stages
+    int kmax = 0;
+    for (int k = 0; k < 4; ++k) kmax = std::max(kmax, K[k]);
+    const int attn_floats = m->G * D + 2 * D + 2 * kMegaConsumerWarps * m->G + kMegaConsumerWarps * m->G * D + m->G * (D + 2) + D;
+    int xb = std::max(kmax * 2, attn_floats * 4);
     xb = (xb + 127) & ~127;
     const int rows[4] = {m->p_qkv.N, H, m->I, H};
     int slot_floats = 16;
-    for (int k = 0; k < 4; ++k) {
-        const int cnt = (rows[k] + m->num_sms - 1) / m->num_sms;
-        slot_floats = std::max(slot_floats, cnt * (k == 2 ? 2 : 1));
-    }
+    for (int k = 0; k < 4; ++k)
+        slot_floats = std::max(slot_floats, ((rows[k] + m->num_sms - 1) / m->num_sms) * (k == 2 ? 2 : 1) * 8);   // F <= 8
     cudaFuncAttributes fa;
     CK(cudaFuncGetAttributes(&fa, (const void*)fn16));
     const int budget = 227 * 1024 - (int)fa.sharedSizeBytes - 256;
     const int fixed = xb + H * 4 + slot_floats * 4;
-    int ns = (budget - fixed) / stage;
-    if (const char* e = getenv("OXG4_MEGA_STAGES")) ns = std::min(ns, atoi(e));
-    ns = std::min(ns, kMegaMaxStages);
-    if (ns < 2) return OXG4_OK;
-    while (ns & (ns - 1)) ns &= ns - 1;            // the kernel masks the piece counter: a power of two
-    if (const char* e = getenv("OXG4_MEGA_PF")) m->mega_pf_ahead = std::max(0, std::min(64, atoi(e)));
+    int stage_max = ((budget - fixed) / kMegaStages) & ~127;
+    if (const char* e = getenv("OXG4_MEGA_STAGE_KB")) stage_max = std::min(stage_max, std::max(1, atoi(e)) * 1024);
+    int stage = 0;
+    for (int k = 0; k < 4; ++k) {
+        // R whole rows per piece, each cut into nseg interleaved segments that become the 16 rows of the mma
+        // A operand; a row that does not fit a stage goes in F contiguous fractions (R = 1)
+        if (K[k] % 16 != 0) return OXG4_OK;
+        int R = 16, F = 1;
+        auto fits = [&](int r, int f) {
+            const int kf = K[k] / f;
+            return K[k] % f == 0 && kf % 16 == 0 && (kf / 16) % mega_nseg(r) == 0 && r * (kf * 2 + 16) <= stage_max;
+        };
+        while (R > 1 && !fits(R, 1)) R /= 2;
+        while (F < 8 && !fits(R, F)) F *= 2;
+        if (!fits(R, F)) return OXG4_OK;
+        m->mega_R[k] = R;
+        m->mega_F[k] = F;
+        stage = std::max(stage, R * (K[k] / F * 2 + 16));
+    }
+    stage = (stage + 127) & ~127;
+    if (const char* e = getenv("OXG4_MEGA_PF_KB")) m->mega_pf_kb = std::max(0, std::min(4096, atoi(e)));
     m->mega_stage_bytes = stage;
-    m->mega_stages = ns;
     m->mega_x_bytes = xb;
     m->mega_slot_floats = slot_floats;
-    m->mega_smem = (size_t)ns * stage + fixed;
+    m->mega_smem = (size_t)kMegaStages * stage + fixed;
     TRY(allow_big_smem(fn16));
     TRY(allow_big_smem(fn32));
     int occ = 0;
@@ -1200,16 +1209,16 @@ static void launch_gemv(Launcher& ln, const char* kind, oxg4_cache* c, GemvArgs 
 }
 
 template <typename KT>
-static void (*pick_attn(int D, int G, bool cl))(const AttnArgs) {
-#define PA(DD)                                                                                     \
-    if (D == DD) {                                                                                 \
-        if (G == 1) return cl ? attn_decode_kernel<KT, DD, 1, true> : attn_decode_kernel<KT, DD, 1, false>; \
-        if (G == 2) return cl ? attn_decode_kernel<KT, DD, 2, true> : attn_decode_kernel<KT, DD, 2, false>; \
-        if (G == 4) return cl ? attn_decode_kernel<KT, DD, 4, true> : attn_decode_kernel<KT, DD, 4, false>; \
-        if (G == 8) return cl ? attn_decode_kernel<KT, DD, 8, true> : attn_decode_kernel<KT, DD, 8, false>; \
+static void (*pick_attn(int D, int G, bool cl, bool deep))(const AttnArgs) {
+#define PA1(DD, GG)                                                                       \
+    if (D == DD && G == GG) {                                                             \
+        if (cl && deep) return attn_decode_kernel<KT, DD, GG, true, true>;                \
+        return cl ? attn_decode_kernel<KT, DD, GG, true> : attn_decode_kernel<KT, DD, GG, false>; \
     }
+#define PA(DD) PA1(DD, 1) PA1(DD, 2) PA1(DD, 4) PA1(DD, 8)
     PA(64) PA(128) PA(256)
 #undef PA
+#undef PA1
     return nullptr;
 }
 
@@ -1262,11 +1271,12 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
         }
         a.ts = ln.ts();
         const bool cl = c->attn_cluster && a.n_splits <= 16;
-        auto fn = c->kv_dtype == OXG4_BF16 ? pick_attn<uint16_t>(D, m->G, cl) : pick_attn<float>(D, m->G, cl);
         // few CTAs (one sequence): 16 warps each to cut latency; many CTAs: 4 warps each so that several
         // fit on an SM (the kernel needs ~90 registers per thread)
         const int aw = (a.n_splits * m->Nkv * B <= m->num_sms) ? kAttnWarps : 4;
-        const size_t smem = sizeof(float) * (size_t)(m->G * D + 2 * D + 2 * aw * m->G + aw * m->G * D + m->G * (D + 2));
+        const bool deep = cl && aw == kAttnWarps;      // more K/V rows in flight per warp when latency is all that counts
+        auto fn = c->kv_dtype == OXG4_BF16 ? pick_attn<uint16_t>(D, m->G, cl, deep) : pick_attn<float>(D, m->G, cl, deep);
+        const size_t smem = sizeof(float) * (size_t)(m->G * D + 2 * D + 2 * aw * m->G + aw * m->G * D + m->G * (D + 2) + D);
         ln.cluster_x = cl ? a.n_splits : 0;
         ln.go("attn", fn, dim3(a.n_splits, m->Nkv, B), dim3(aw * 32), smem, a);
         ln.cluster_x = 0;
@@ -1278,10 +1288,9 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
         g.layers = m->mega_layers;
         g.kv = c->mega_kv;
         g.L = L; g.H = H; g.I = m->I; g.Nq = m->Nq; g.Nkv = m->Nkv; g.qkv_n = m->p_qkv.N;
-        for (int k = 0; k < 4; ++k) g.R[k] = m->mega_R[k];
+        for (int k = 0; k < 4; ++k) { g.R[k] = m->mega_R[k]; g.F[k] = m->mega_F[k]; }
         g.stage_bytes = m->mega_stage_bytes;
-        g.n_stages = m->mega_stages;
-        g.pf_ahead = m->mega_pf_ahead;
+        g.pf_kb = m->mega_pf_kb;
         g.x_bytes = m->mega_x_bytes;
         g.slot_floats = m->mega_slot_floats;
         g.embed = (const uint16_t*)m->embed;
@@ -1300,7 +1309,7 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
         g.ticket = c->attn_ticket;
         g.sync = c->mega_sync;
         g.status = c->mega_status;
-        g.ts = (ln.ts() && 15 * L + 2 + 4 * (ln.kernels + 4) <= kMaxTimeline * 4) ? ln.ts() : nullptr;
+        g.ts = (ln.ts() && 19 * L + 2 + 4 * (ln.kernels + 4) <= kMaxTimeline * 4) ? ln.ts() : nullptr;
         if (ln.status == OXG4_OK && cudaMemsetAsync(c->mega_sync, 0, sizeof(MegaSync), m->stream) != cudaSuccess)
             ln.status = fail(OXG4_CUDA, "Gemma 4 CUDA error: cudaMemsetAsync failed");
         auto fn = c->kv_dtype == OXG4_BF16 ? pick_mega<uint16_t>(D, m->G) : pick_mega<float>(D, m->G);
@@ -1623,7 +1632,7 @@ static int32_t check_tc(oxg4_cache* c) {
     if (c->use_mega && *(volatile int*)c->mega_status != 0) {      // mapped host word, read after a stream sync
         const int code = *c->mega_status;
         *c->mega_status = 0;
-        return fail(OXG4_TIMEOUT, "persistent decode kernel: a bounded wait ran out (code %d)", code);
+        return fail(OXG4_TIMEOUT, "persistent decode kernel: a bounded wait ran out (kind %d: 1 grid barrier, 2 stage not released, 3 piece not delivered, 4 shared stage not released; CTA %d, piece/barrier %d, warp %d)", code & 15, (code >> 4) & 255, (code >> 12) & 16383, (code >> 26) & 31);
     }
     if (!c->use_tc) return OXG4_OK;
     int err = 0;
