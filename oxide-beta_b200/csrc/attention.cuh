@@ -18,6 +18,7 @@
 // HBM-bound: bytes per launch = 2 * visible_positions * kv_heads * head_dim * sizeof(KV element).
 #pragma once
 #include <cooperative_groups.h>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -161,6 +162,7 @@ DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, c
     float* cpart = wacc + NW * G * D;        // [G][D + 2] this CTA's partial (cluster variant)
     float* rope = cpart + G * (D + 2);       // [D] cos (first half) and sin (second half) of pos * inv_freq
     __shared__ unsigned int s_last;
+    __shared__ float s_scale[16 * 8], s_l[16 * 8], s_M[8];   // merge scratch: up to 16 warps or cluster splits x 8 heads
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int half = D / 2;
@@ -197,6 +199,33 @@ DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, c
     const bool has_work = active && s < n_eff;
     float* part = a.part + (((size_t)b * a.Nkv + kvh) * a.n_splits) * (size_t)(G * (D + 2));
     size_t cur_off = 0;
+    // this CTA's range of positions, and the loads of its first step: K/V rows of earlier positions were
+    // written by earlier steps, so they can be in flight while the QKV projection finishes and while the
+    // prologue below runs
+    const int begin = has_work ? lo + (int)(((long long)n * s) / n_eff) : 0;
+    const int end = has_work ? lo + (int)(((long long)n * (s + 1)) / n_eff) : 0;
+    constexpr int PD = DEEP ? 4 : 2;
+    typedef KRaw<KT, EPT> Raw;
+    const KT* kpool = (const KT*)a.kpool;
+    const KT* vpool = (const KT*)a.vpool;
+    const int32_t* pt = a.page_table + (size_t)b * a.pages_per_seq;
+    auto row_offset = [&](int p) -> size_t {
+        const int slot = p % cap;
+        return (((size_t)pt[slot / a.page_tokens] * a.Nkv + kvh) * a.page_tokens +
+                (slot % a.page_tokens)) * (size_t)D + lane * EPT;
+    };
+    auto issue = [&](int p, Raw& kr, Raw& vr) {            // loads only; the current token comes from shared memory
+        if (p < end && p != pos) {
+            const size_t off = row_offset(p);
+            kraw_load<KT, EPT>(kpool + off, kr);
+            kraw_load<KT, EPT>(vpool + off, vr);
+        }
+    };
+    Raw kr[PD], vr[PD];
+    if (has_work) {
+#pragma unroll
+        for (int q = 0; q < PD; ++q) issue(begin + warp + q * NW, kr[q], vr[q]);
+    }
     if (has_work) {
         const int slot_cur = pos % cap;
         cur_off = (((size_t)a.page_table[(size_t)b * a.pages_per_seq + slot_cur / a.page_tokens] * a.Nkv + kvh) *
@@ -218,8 +247,6 @@ DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, c
     stamp(a.ts, 1);
 
     if (has_work) {
-        const int begin = lo + (int)(((long long)n * s) / n_eff);
-        const int end = lo + (int)(((long long)n * (s + 1)) / n_eff);
         const bool owner = (s == n_eff - 1);        // the range that contains `pos`
         bar();                                      // the rotation factors are in shared memory
         // tasks 0..G-1: query heads (norm + rope); task G: key (norm + rope + append);
@@ -283,11 +310,11 @@ DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, c
         bar();
         stamp(a.ts, 2);
 
-        float q[G][EPT];
+        float q_[G][EPT];
 #pragma unroll
         for (int g = 0; g < G; ++g)
 #pragma unroll
-            for (int e = 0; e < EPT; ++e) q[g][e] = qs[g * D + lane * EPT + e];
+            for (int e = 0; e < EPT; ++e) q_[g][e] = qs[g * D + lane * EPT + e];
         float m[G], l[G], acc[G][EPT];
 #pragma unroll
         for (int g = 0; g < G; ++g) {
@@ -296,67 +323,85 @@ DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, c
 #pragma unroll
             for (int e = 0; e < EPT; ++e) acc[g][e] = 0.0f;
         }
-        const KT* kpool = (const KT*)a.kpool;
-        const KT* vpool = (const KT*)a.vpool;
-        const int32_t* pt = a.page_table + (size_t)b * a.pages_per_seq;
-        auto row_offset = [&](int p) -> size_t {
-            const int slot = p % cap;
-            return (((size_t)pt[slot / a.page_tokens] * a.Nkv + kvh) * a.page_tokens +
-                    (slot % a.page_tokens)) * (size_t)D + lane * EPT;
-        };
-        auto consume = [&](const float (&kf)[EPT], const float (&vf)[EPT]) {
+        // The PD positions of a step: all PD * G dot products first, their butterfly reductions interleaved
+        // (PD * G independent shuffles per level instead of one dependent chain per score), then the
+        // updates in position order.
+        auto use_step = [&](int p0, const Raw* kr, const Raw* vr, auto pd_tag) {
+            constexpr int NP = decltype(pd_tag)::value;
+            float sc[NP][G];
+#pragma unroll
+            for (int q = 0; q < NP; ++q) {
+                const int pq = p0 + q * NW;
+                float kf[EPT];
+                if (pq == pos) {
+#pragma unroll
+                    for (int e = 0; e < EPT; ++e) kf[e] = kcur[lane * EPT + e];
+                } else {
+                    kraw_cvt<KT, EPT>(kr[q], kf);          // rows past `end` were never loaded: their scores are not used
+                }
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    float t = 0.0f;
+#pragma unroll
+                    for (int e = 0; e < EPT; ++e) t = fmaf(q_[g][e], kf[e], t);
+                    sc[q][g] = t;
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                for (int q = 0; q < NP; ++q)
+#pragma unroll
+                    for (int g = 0; g < G; ++g) sc[q][g] += __shfl_xor_sync(0xffffffffu, sc[q][g], o);
+            // one online-softmax step for the NP positions together: a single rescale of the running sums
+            float pe[NP][G];
 #pragma unroll
             for (int g = 0; g < G; ++g) {
-                float sc = 0.0f;
+                float mn = m[g];
 #pragma unroll
-                for (int e = 0; e < EPT; ++e) sc = fmaf(q[g][e], kf[e], sc);
-                sc = warp_sum(sc);
-                const float mn = fmaxf(m[g], sc);
-                const float corr = expf(m[g] - mn);       // exp(-inf) = 0 on the first position
-                const float pe = expf(sc - mn);
-                l[g] = l[g] * corr + pe;
+                for (int q = 0; q < NP; ++q)
+                    if (p0 + q * NW < end) mn = fmaxf(mn, sc[q][g]);
+                const float corr = expf(m[g] - mn);       // exp(-inf) = 0 on the first step
+                float ls = l[g] * corr;
 #pragma unroll
-                for (int e = 0; e < EPT; ++e) acc[g][e] = acc[g][e] * corr + pe * vf[e];
+                for (int q = 0; q < NP; ++q) {
+                    pe[q][g] = (p0 + q * NW < end) ? expf(sc[q][g] - mn) : 0.0f;
+                    ls += pe[q][g];
+                }
+                l[g] = ls;
                 m[g] = mn;
-            }
-        };
-        typedef KRaw<KT, EPT> Raw;
-        auto issue = [&](int p, Raw& kr, Raw& vr) {            // loads only; the current token comes from shared memory
-            if (p < end && p != pos) {
-                const size_t off = row_offset(p);
-                kraw_load<KT, EPT>(kpool + off, kr);
-                kraw_load<KT, EPT>(vpool + off, vr);
-            }
-        };
-        auto use = [&](int p, const Raw& kr, const Raw& vr) {
-            if (p >= end) return;
-            float kf[EPT], vf[EPT];
-            if (p == pos) {
 #pragma unroll
-                for (int e = 0; e < EPT; ++e) { kf[e] = kcur[lane * EPT + e]; vf[e] = vcur[lane * EPT + e]; }
-            } else {
-                kraw_cvt<KT, EPT>(kr, kf);
-                kraw_cvt<KT, EPT>(vr, vf);
+                for (int e = 0; e < EPT; ++e) acc[g][e] *= corr;
             }
-            consume(kf, vf);
+#pragma unroll
+            for (int q = 0; q < NP; ++q) {
+                const int pq = p0 + q * NW;
+                if (pq >= end) break;
+                float vf[EPT];
+                if (pq == pos) {
+#pragma unroll
+                    for (int e = 0; e < EPT; ++e) vf[e] = vcur[lane * EPT + e];
+                } else {
+                    kraw_cvt<KT, EPT>(vr[q], vf);
+                }
+#pragma unroll
+                for (int g = 0; g < G; ++g)
+#pragma unroll
+                    for (int e = 0; e < EPT; ++e) acc[g][e] = fmaf(pe[q][g], vf[e], acc[g][e]);
+            }
         };
         // PD positions per step, the next step's loads issued before this step's arithmetic: 2 * PD rows of
         // K and of V in flight per warp (PD = 4 when one sequence has the whole GPU and latency is all that counts)
-        constexpr int PD = DEEP ? 4 : 2;
-        Raw kr[PD], vr[PD];
-        int p = begin + warp;
-#pragma unroll
-        for (int q = 0; q < PD; ++q) issue(p + q * NW, kr[q], vr[q]);
-        for (; p < end; p += PD * NW) {
+        for (int p = begin + warp; p < end; p += PD * NW) {
             Raw nk[PD], nv[PD];
 #pragma unroll
             for (int q = 0; q < PD; ++q) issue(p + (PD + q) * NW, nk[q], nv[q]);
-#pragma unroll
-            for (int q = 0; q < PD; ++q) use(p + q * NW, kr[q], vr[q]);
+            use_step(p, kr, vr, std::integral_constant<int, PD>{});
 #pragma unroll
             for (int q = 0; q < PD; ++q) { kr[q] = nk[q]; vr[q] = nv[q]; }
         }
 
+        stamp(a.ts_mid, 1);
         // merge the warps of this CTA (fixed warp order)
 #pragma unroll
         for (int g = 0; g < G; ++g) {
@@ -365,21 +410,27 @@ DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, c
             for (int e = 0; e < EPT; ++e) wacc[((size_t)warp * G + g) * D + lane * EPT + e] = acc[g][e];
         }
         bar();
+        // one scale factor exp(m_w - M) per (warp, head), computed once instead of once per output element
+        if (tid < NW * G) {
+            const int g = tid % G;
+            float M = -INFINITY;
+            for (int w = 0; w < NW; ++w) M = fmaxf(M, wm[w * G + g]);
+            const float mw = wm[tid];
+            s_scale[tid] = (mw == -INFINITY) ? 0.0f : expf(mw - M);
+            if (tid < G) s_M[g] = M;
+        }
+        bar();
         float* my = CL ? cpart : part + (size_t)s * (G * (D + 2));
         for (int idx = tid; idx < G * D; idx += nthreads) {
             const int g = idx / D, d = idx % D;
-            float M = -INFINITY;
-            for (int w = 0; w < NW; ++w) M = fmaxf(M, wm[w * G + g]);
             float A = 0.0f, L = 0.0f;
             for (int w = 0; w < NW; ++w) {
-                const float mw = wm[w * G + g];
-                if (mw == -INFINITY) continue;
-                const float e = expf(mw - M);
+                const float e = s_scale[w * G + g];
                 A += e * wacc[((size_t)w * G + g) * D + d];
                 L += e * wl[w * G + g];
             }
             my[g * (D + 2) + d] = A;
-            if (d == 0) { my[g * (D + 2) + D] = M; my[g * (D + 2) + D + 1] = L; }
+            if (d == 0) { my[g * (D + 2) + D] = s_M[g]; my[g * (D + 2) + D + 1] = L; }
         }
     }
 
@@ -387,28 +438,44 @@ DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, c
         // ---- cluster merge: every CTA finishes a slice of the outputs from its peers' shared memory ----
         namespace cg = cooperative_groups;
         cg::cluster_group cluster = cg::this_cluster();
+        stamp(a.ts_mid, 2);
         cluster.sync();                                    // every CTA of the cluster arrives, with or without work
+        stamp(a.ts_mid, 3);
         if (active) {
+            // (m, l) of every split -> this CTA's shared memory in one round of remote loads, then one scale
+            // factor per (split, head); the weighted sums below are independent remote loads
+            if (tid < n_eff * G) {
+                const int sp = tid / G, g = tid % G;
+                const float* ps = cluster.map_shared_rank(cpart, sp) + g * (D + 2);
+                s_scale[tid] = ps[D];
+                s_l[tid] = ps[D + 1];
+            }
+            bar();
+            if (tid < G) {
+                const int g = tid;
+                float M = -INFINITY;
+                for (int sp = 0; sp < n_eff; ++sp) M = fmaxf(M, s_scale[sp * G + g]);
+                float L = 0.0f;
+                for (int sp = 0; sp < n_eff; ++sp) {
+                    const float ms = s_scale[sp * G + g];
+                    const float e = (ms == -INFINITY) ? 0.0f : expf(ms - M);
+                    s_scale[sp * G + g] = e;
+                    L += e * s_l[sp * G + g];
+                }
+                s_M[g] = L;
+            }
+            bar();
             const int cs = (int)gridDim.x;
             const int per = (G * D + cs - 1) / cs;
             const int hi = min(G * D, (s + 1) * per);
             for (int idx = s * per + tid; idx < hi; idx += nthreads) {
                 const int g = idx / D, d = idx % D;
-                float M = -INFINITY;
+                float A = 0.0f;
                 for (int sp = 0; sp < n_eff; ++sp)
-                    M = fmaxf(M, cluster.map_shared_rank(cpart, sp)[g * (D + 2) + D]);
-                float A = 0.0f, L = 0.0f;
-                for (int sp = 0; sp < n_eff; ++sp) {
-                    const float* ps = cluster.map_shared_rank(cpart, sp) + g * (D + 2);
-                    const float ms = ps[D];
-                    if (ms == -INFINITY) continue;
-                    const float e = expf(ms - M);
-                    A += e * ps[d];
-                    L += e * ps[D + 1];
-                }
+                    A += s_scale[sp * G + g] * cluster.map_shared_rank(cpart, sp)[g * (D + 2) + d];
                 {
                     const size_t oi = (size_t)b * a.Nq * D + (size_t)(kvh * G + g) * D + d;
-                    const float ov = A / L;
+                    const float ov = A / s_M[g];
                     a.out[oi] = ov;
                     if (a.out_bf16) a.out_bf16[oi] = (uint16_t)f32_to_bf16_bits(ov);
                 }

@@ -41,7 +41,7 @@ constexpr int kMegaConsumers = kMegaConsumerWarps * 32;      // 512: attention.c
 constexpr int kMegaThreads = kMegaConsumers + 32;            // + the producer warp
 constexpr int kMegaStages = kMegaConsumerWarps;             // one ring stage per consumer warp
 constexpr int kMegaMaxJ = 11;                                 // hidden size <= 11 * 512
-constexpr unsigned int kMegaSpinLimit = 1u << 22;             // grid-barrier polls before giving up
+constexpr unsigned int kMegaSpinLimit = 1u << 21;             // polls (each up to ~2 us asleep) before a wait gives up
 
 struct MegaLayer {            // per-layer model constants (device array)
     const void *wqkv, *wo, *wgate, *wup, *wdown;
@@ -112,19 +112,21 @@ DEVINL void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar)
                  : "memory");
 }
 // Bounded mbarrier wait that also gives up when the CTA (`dead`) or the grid (`abort`) has given up.
+// The wait carries a suspend-time hint: a warp whose piece has not landed sleeps inside try_wait instead
+// of re-issuing polls, which would take issue slots from the warps of its scheduler that are multiplying.
 DEVINL bool mega_wait(uint64_t* bar, uint32_t parity, const volatile int* dead, const unsigned int* abort) {
     const uint32_t addr = smem_u32(bar);
     for (uint32_t i = 1; i <= kMegaSpinLimit; ++i) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(done)
-            : "r"(addr), "r"(parity)
+            : "r"(addr), "r"(parity), "r"(2000u)
             : "memory");
         if (done) return true;
-        if ((i & 63u) == 0u && (*dead || ld_relaxed_gpu(abort))) return false;
+        if ((i & 7u) == 0u && (*dead || ld_relaxed_gpu(abort))) return false;
     }
     return false;
 }
@@ -287,6 +289,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
             atomicAdd(&a.sync->arrived, 1u);
             unsigned int polls = 0;
             while (ld_acquire_gpu(&a.sync->arrived) < target) {
+                __nanosleep(40);
                 if (++polls > kMegaSpinLimit || ((polls & 255u) == 0u && ld_relaxed_gpu(&a.sync->abort))) {
                     dead = 1;
                     if (polls > kMegaSpinLimit) mega_fail(a.sync, a.status, 1u, blockIdx.x, gen, 0u);
@@ -541,7 +544,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
             at.cap = ly.sliding ? a.cap_slide : a.cap_full;
             at.n_splits = ly.sliding ? a.splits_slide : a.splits_full;
             at.ts = a.ts ? a.ts + 15 * a.L + 2 + 4 * l : nullptr;
-            at.ts_mid = at.ts ? at.ts : nullptr;       // slot 0 (entry) doubles as 'partial complete'
+            at.ts_mid = nullptr;
             const int units = at.n_splits * a.Nkv;
             for (int u = blockIdx.x; u < units; u += gridDim.x) {
                 attn_cta<KT, D, G, false, false, false>(at, reinterpret_cast<float*>(xreg), u % at.n_splits, u / at.n_splits, 0,

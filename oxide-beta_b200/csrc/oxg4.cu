@@ -1270,6 +1270,7 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
             a.pf_bytes = (unsigned long long)m->I * H * m->es;
         }
         a.ts = ln.ts();
+        a.ts_mid = ln.ts_base ? ln.ts_base + 4 * (size_t)(kMaxTimeline - 1 - l) : nullptr;   // extra stamps, from the end of the buffer
         const bool cl = c->attn_cluster && a.n_splits <= 16;
         // few CTAs (one sequence): 16 warps each to cut latency; many CTAs: 4 warps each so that several
         // fit on an SM (the kernel needs ~90 registers per thread)
