@@ -1275,7 +1275,9 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
         // few CTAs (one sequence): 16 warps each to cut latency; many CTAs: 4 warps each so that several
         // fit on an SM (the kernel needs ~90 registers per thread)
         const int aw = (a.n_splits * m->Nkv * B <= m->num_sms) ? kAttnWarps : 4;
-        const bool deep = cl && aw == kAttnWarps;      // more K/V rows in flight per warp when latency is all that counts
+        // more K/V rows in flight per warp when latency is all that counts (with more than two query heads
+        // per kv head the extra rows would spill registers)
+        const bool deep = cl && aw == kAttnWarps && m->G <= 2;
         auto fn = c->kv_dtype == OXG4_BF16 ? pick_attn<uint16_t>(D, m->G, cl, deep) : pick_attn<float>(D, m->G, cl, deep);
         const size_t smem = sizeof(float) * (size_t)(m->G * D + 2 * D + 2 * aw * m->G + aw * m->G * D + m->G * (D + 2) + D);
         ln.cluster_x = cl ? a.n_splits : 0;
