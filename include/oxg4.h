@@ -167,6 +167,17 @@ int32_t oxg4_decode_topk(oxg4_model* model, oxg4_cache* cache, const uint32_t* t
 int32_t oxg4_decode_greedy(oxg4_model* model, oxg4_cache* cache, const uint32_t* first_tokens,
                            int32_t steps, uint32_t* out_ids, float* ms_per_step);
 
+/* Device-resident sampled generation (no counterpart in the reference, whose host draws every token
+ * in sample_topk_candidates, sampling.rs:88-158): runs `steps` decode steps; after each one a kernel
+ * draws the next token from the step's top_k (2..=64) candidates with the reference's arithmetic
+ * (temperature, softmax, top-p, xorshift64 13/7/17, 24-bit uniform) and feeds it back without leaving
+ * the GPU. Tokens fed in are marked seen, the repetition penalty applies as in oxg4_decode_topk.
+ * seeds: [batch] generator states, updated in place, so that oxg4_sample_topk_candidates continues the
+ * same stream on the host. out_ids: [steps, batch]. Not available with tensor parallelism. */
+int32_t oxg4_decode_sampled(oxg4_model* model, oxg4_cache* cache, const uint32_t* first_tokens, int32_t steps,
+                            int32_t top_k, float temperature, float top_p, float repetition_penalty,
+                            uint64_t* seeds, uint32_t* out_ids, float* ms_per_step);
+
 /* Number of kernels launched by this library since the model was created (graph replays count
  * the kernels inside the graph). */
 int64_t oxg4_kernel_launches(const oxg4_model* model);

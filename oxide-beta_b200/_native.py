@@ -71,6 +71,8 @@ SYMBOLS = {
     "oxg4_decode_logits": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "oxg4_decode_topk": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_float, C.c_int32,
                                      C.c_void_p, C.c_void_p]),
+    "oxg4_decode_sampled": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_float,
+                                        C.c_float, C.c_float, C.c_void_p, C.c_void_p, C.c_void_p]),
     "oxg4_decode_greedy": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
                                        C.POINTER(C.c_float)]),
     "oxg4_kernel_launches": (C.c_int64, [C.c_void_p]),

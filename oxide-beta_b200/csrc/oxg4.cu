@@ -638,6 +638,9 @@ struct oxg4_cache {
     // pinned staging
     uint32_t* h_tokens = nullptr;
     StepCtl* h_ctl = nullptr;
+    unsigned long long* rng = nullptr;        // [B] xorshift64 state of the device-side sampler
+    int want_sample = 0;                      // copied into the step's control words by stage_inputs
+    float sample_temperature = 1.0f, sample_top_p = 1.0f;
     uint32_t* h_ids = nullptr;
     float* h_scores = nullptr;
     std::map<std::string, GraphEntry> graphs;
@@ -755,6 +758,7 @@ static int32_t cache_build(oxg4_cache* c) {
     TRY(dalloc(c, &c->pos, B));
     TRY(dalloc(c, &c->seen, (size_t)B * m->V));
     TRY(dalloc(c, &c->ctl, 1));
+    TRY(dalloc(c, &c->rng, B));
     TRY(dalloc(c, &c->hA, (size_t)B * H));
     TRY(dalloc(c, &c->hB, (size_t)B * H));
     TRY(dalloc(c, &c->qkv_raw, (size_t)B * m->p_qkv.N));
@@ -1555,6 +1559,10 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
                   (const Cand*)c->topk_stage, chunks * top_k, top_k, c->topk_ids, c->topk_scores);
         }
     }
+    if (kind == STEP_TOPK && top_k > 1)      // a no-op unless the step's control words ask for a sampled token
+        ln.go("sample", sample_candidates_kernel, dim3(1), dim3(64), 0, B, top_k, (const uint32_t*)c->tokens,
+              (const uint32_t*)c->topk_ids, (const float*)c->topk_scores, (const StepCtl*)c->ctl, c->rng, c->best_ids,
+              c->best_scores);
     ln.go("step_end", step_end_kernel, dim3(1), dim3(128), 0, B, c->tokens, c->pos,
           (const uint32_t*)c->best_ids, c->history, c->ctl);
     if (n_kernels) *n_kernels = ln.kernels;
@@ -1620,6 +1628,9 @@ static int32_t stage_inputs(oxg4_cache* c, const uint32_t* tokens, int mark_seen
     c->h_ctl->feed_back = feed_back;
     c->h_ctl->step = 0;
     c->h_ctl->history_cap = c->history_cap;
+    c->h_ctl->sample = c->want_sample;
+    c->h_ctl->temperature = c->sample_temperature;
+    c->h_ctl->top_p = c->sample_top_p;
     CK(cudaMemcpyAsync(c->tokens, c->h_tokens, sizeof(uint32_t) * c->B, cudaMemcpyHostToDevice, st));
     CK(cudaMemcpyAsync(c->ctl, c->h_ctl, sizeof(StepCtl), cudaMemcpyHostToDevice, st));
     return OXG4_OK;
@@ -1754,6 +1765,62 @@ extern "C" int32_t oxg4_decode_greedy(oxg4_model* m, oxg4_cache* c, const uint32
     for (int s = 0; s < steps; ++s) TRY(launch_step(c, STEP_TOPK, 1, 1.0f));
     CK(cudaEventRecord(c->ev1, m->stream));
     CK(cudaMemcpyAsync(out_ids, c->history, sizeof(uint32_t) * (size_t)steps * c->B, cudaMemcpyDeviceToHost, m->stream));
+    CK(cudaStreamSynchronize(m->stream));
+    TRY(check_tc(c));
+    float ms = 0;
+    CK(cudaEventElapsedTime(&ms, c->ev0, c->ev1));
+    if (ms_per_step) *ms_per_step = ms / steps;
+    advance_host(c, first_tokens, steps);
+    return OXG4_OK;
+}
+
+// Device-resident sampled generation: `steps` tokens per sequence drawn from the top-k list of every step
+// by sample_candidates_kernel, fed back on the device; one synchronisation at the end. `seeds` holds one
+// xorshift64 state per sequence and receives the state after the last draw, so that a host loop calling
+// oxg4_sample_topk_candidates with the same state continues identically.
+extern "C" int32_t oxg4_decode_sampled(oxg4_model* m, oxg4_cache* c, const uint32_t* first_tokens, int32_t steps,
+                                       int32_t top_k, float temperature, float top_p, float penalty,
+                                       uint64_t* seeds, uint32_t* out_ids, float* ms_per_step) {
+    if (!m || !c || !first_tokens || !seeds || !out_ids || c->m != m)
+        return fail(OXG4_INVALID_ARGUMENT, "null or mismatched handle");
+    if (steps <= 0) return fail(OXG4_INVALID_ARGUMENT, "steps must be positive");
+    if (!std::isfinite(temperature) || temperature <= 0.0f)
+        return fail(OXG4_INVALID_ARGUMENT, "generation temperature must be finite and greater than zero");
+    if (!std::isfinite(top_p) || top_p < 0.0f || top_p > 1.0f)
+        return fail(OXG4_INVALID_ARGUMENT, "generation top_p must be finite and between zero and one");
+    if (!std::isfinite(penalty) || penalty < 1.0f)
+        return fail(OXG4_INVALID_ARGUMENT, "generation repetition_penalty must be finite and at least one");
+    top_k = std::min(std::min(std::max(top_k, 1), 64), m->V);
+    if (top_k < 2) return fail(OXG4_INVALID_ARGUMENT, "sampling needs at least two candidates; use oxg4_decode_greedy for top_k = 1");
+    if (m->tp > 1) return fail(OXG4_UNSUPPORTED, "device-side sampling is not available with tensor parallelism");
+    TRY(bind_device(m));
+    TRY(check_tokens(c, first_tokens, true));
+    for (int b = 0; b < c->B; ++b)
+        if (first_tokens[b] != kInactiveToken && c->pos_host[b] + steps > c->max_seq[b])
+            return fail(OXG4_INVALID_SHAPE, "sequence %d would outgrow the cache table's max_sequence", b);
+    if (c->history_cap < steps) {
+        uint32_t* h = nullptr;
+        TRY(dalloc(c, &h, (size_t)steps * c->B));
+        c->history = h;
+        c->history_cap = steps;
+        for (auto& g : c->graphs) {                       // the history pointer is a kernel argument
+            if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
+            if (g.second.graph) cudaGraphDestroy(g.second.graph);
+        }
+        c->graphs.clear();
+    }
+    CK(cudaMemcpyAsync(c->rng, seeds, sizeof(uint64_t) * c->B, cudaMemcpyHostToDevice, m->stream));
+    c->want_sample = 1;
+    c->sample_temperature = temperature;
+    c->sample_top_p = top_p;
+    int32_t s = stage_inputs(c, first_tokens, 1, 1);
+    c->want_sample = 0;
+    if (s != OXG4_OK) return s;
+    CK(cudaEventRecord(c->ev0, m->stream));
+    for (int i = 0; i < steps; ++i) TRY(launch_step(c, STEP_TOPK, top_k, penalty));
+    CK(cudaEventRecord(c->ev1, m->stream));
+    CK(cudaMemcpyAsync(out_ids, c->history, sizeof(uint32_t) * (size_t)steps * c->B, cudaMemcpyDeviceToHost, m->stream));
+    CK(cudaMemcpyAsync(seeds, c->rng, sizeof(uint64_t) * c->B, cudaMemcpyDeviceToHost, m->stream));
     CK(cudaStreamSynchronize(m->stream));
     TRY(check_tc(c));
     float ms = 0;

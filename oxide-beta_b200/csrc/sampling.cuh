@@ -16,6 +16,8 @@ struct StepCtl {              // device-resident control words, written by the h
     int32_t feed_back;        // 1: next token[b] = arg-max of this step (device-resident greedy loop)
     int32_t step;             // steps run since the loop started (index into `history`)
     int32_t history_cap;      // capacity of `history` in steps
+    int32_t sample;           // 1: the token fed back is drawn from the step's top-k list (sample_candidates_kernel)
+    float temperature, top_p;
 };
 
 __global__ void step_begin_kernel(int B, int V, const uint32_t* tokens, uint8_t* seen, const StepCtl* ctl) {
@@ -46,6 +48,81 @@ __global__ void step_end_kernel(int B, uint32_t* tokens, int32_t* pos, const uin
     }
     __syncthreads();
     if (threadIdx.x == 0 && fb) ctl->step = step + 1;
+}
+
+// f32::total_cmp key (the reference sorts candidates with it, sampling.rs:88-158)
+DEVINL int32_t total_order_key_dev(float f) {
+    int32_t b = __float_as_int(f);
+    b ^= (int32_t)(((uint32_t)(b >> 31)) >> 1);
+    return b;
+}
+
+// The reference's sample_topk_candidates (crates/oxide-torch-models/src/models/gemma4/sampling.rs:88-158) on
+// the device, one thread per sequence over the step's (<= 64) top-k candidates: temperature, stable
+// descending sort, softmax, top-p cut, xorshift64 (13, 7, 17), 24-bit uniform, cumulative pick. The same
+// f32 operations in the same order as the host version (oxg4_sample_topk_candidates); the generator state
+// lives on the device so that a sampled generation loop needs no per-token host round trip. The chosen
+// token replaces best_ids[b], which step_end feeds back.
+__global__ void sample_candidates_kernel(int B, int k, const uint32_t* tokens, const uint32_t* cand_ids,
+                                         const float* cand_scores, const StepCtl* ctl, unsigned long long* rng,
+                                         uint32_t* best_ids, float* best_scores) {
+    pdl_wait();
+    pdl_launch();
+    if (!ctl->sample) return;
+    const float temperature = ctl->temperature, top_p = ctl->top_p;
+    for (int b = threadIdx.x; b < B; b += blockDim.x) {       // launched as a single block
+        if (tokens[b] == kInactiveToken) continue;
+        uint32_t id[64];
+        float v[64];
+        int n = 0;
+        for (int i = 0; i < k; ++i) {
+            const float s = cand_scores[(size_t)b * k + i];
+            if (isfinite(s)) { id[n] = cand_ids[(size_t)b * k + i]; v[n] = s / temperature; ++n; }
+        }
+        if (n == 0) continue;                                  // keep the arg-max
+        for (int i = 1; i < n; ++i) {                          // stable insertion sort, descending total order
+            const float vi = v[i];
+            const uint32_t ii = id[i];
+            int j = i - 1;
+            while (j >= 0 && total_order_key_dev(v[j]) < total_order_key_dev(vi)) { v[j + 1] = v[j]; id[j + 1] = id[j]; --j; }
+            v[j + 1] = vi;
+            id[j + 1] = ii;
+        }
+        const float maximum = v[0];
+        float total = 0.0f;
+        for (int i = 0; i < n; ++i) { v[i] = expf(v[i] - maximum); total += v[i]; }
+        if (total == 0.0f || !isfinite(total)) continue;
+        for (int i = 0; i < n; ++i) v[i] /= total;
+        if (top_p < 1.0f) {
+            float cumulative = 0.0f;
+            int keep = 0;
+            for (int i = 0; i < n; ++i) {
+                cumulative += v[i];
+                ++keep;
+                if (cumulative >= top_p) break;
+            }
+            n = max(keep, 1);
+            total = 0.0f;
+            for (int i = 0; i < n; ++i) total += v[i];
+        } else {
+            total = 1.0f;
+        }
+        unsigned long long r = rng[b];
+        if (r == 0) r = 0x4d595df4d0f33173ull;
+        r ^= r << 13;
+        r ^= r >> 7;
+        r ^= r << 17;
+        rng[b] = r;
+        const float unit = __fdiv_rn((float)((uint32_t)(r >> 40)), 16777216.0f);
+        float threshold = __fmul_rn(unit, total);
+        int pick = n - 1;
+        for (int i = 0; i < n; ++i) {
+            if (threshold <= v[i]) { pick = i; break; }
+            threshold = __fsub_rn(threshold, v[i]);
+        }
+        best_ids[b] = id[pick];
+        best_scores[b] = v[pick];
+    }
 }
 
 // Tensor parallelism: every rank holds the arg-max of its vocabulary slice; after an all-gather this

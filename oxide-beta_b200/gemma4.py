@@ -330,6 +330,20 @@ class Gemma4CudaState:
         N.check(N.lib().oxg4_decode_greedy(self._h, table._h, _ptr(t), steps, _ptr(out), C.byref(ms)))
         return out, ms.value
 
+    def decode_sampled(self, first_tokens, table: Gemma4CudaCacheTable, steps: int, top_k: int, temperature: float,
+                       top_p: float, repetition_penalty: float, seeds):
+        """Device-resident sampled loop: returns (ids [steps, batch], generator states after the last
+        draw [batch], mean device ms per step). `seeds`: one xorshift64 state per sequence."""
+        t = _as_u32(np.atleast_1d(first_tokens))
+        s = np.ascontiguousarray(np.atleast_1d(seeds), dtype=np.uint64).copy()
+        if s.size != table.batch:
+            raise ValueError("one generator state per sequence is required")
+        out = np.zeros((steps, table.batch), dtype=np.uint32)
+        ms = C.c_float(0)
+        N.check(N.lib().oxg4_decode_sampled(self._h, table._h, _ptr(t), steps, top_k, temperature, top_p,
+                                            repetition_penalty, _ptr(s), _ptr(out), C.byref(ms)))
+        return out, s, ms.value
+
     def profile_step(self, tokens, table: Gemma4CudaCacheTable) -> dict:
         """One eager step with CUDA events around every kernel; mean ms per kernel kind."""
         t = _as_u32(np.atleast_1d(tokens))

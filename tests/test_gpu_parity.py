@@ -396,3 +396,45 @@ def test_persistent_kernel_matches_oracle_and_default_path(head_dim, heads, kv_h
             assert margin(lg) <= 4 * TOL_BF16, (a_, b_, margin(lg))
             break
         lg = ref.decode_logits(int(a_))
+
+
+# ---- device-side sampling ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("seed,top_k,top_p,penalty", [(1234, 8, 0.9, 1.3), (7, 64, 1.0, 1.0), (99, 4, 0.5, 1.1)])
+def test_device_sampled_loop_equals_host_sampling(c1, seed, top_k, top_p, penalty):
+    """oxg4_decode_sampled (draw on the device, no per-token round trip) against the host loop that calls
+    decode_topk + sample_topk_candidates per token: same tokens, same generator state afterwards."""
+    cfg, gpu, oracle = c1
+    prompt = syn.prompt_ids(cfg["vocab_size"], 12, seed=4)
+    steps, temperature = 20, 0.9
+    gcfg = pkg.GenerationConfig(max_new_tokens=steps, temperature=temperature, top_k=top_k, top_p=top_p,
+                                repetition_penalty=penalty, eos_token_ids=[], seed=seed)
+    first = int(np.argmax(gpu.prefill_prompt(prompt, gpu.new_cache_table(64, kv_dtype=pkg.F32))))
+    # host loop
+    t_host = gpu.new_cache_table(64, kv_dtype=pkg.F32)
+    gpu.prefill_prompt(prompt, t_host)
+    rnd = np.array([seed], dtype=np.uint64)
+    tok, host_ids = first, []
+    for _ in range(steps):
+        cand = gpu.decode_topk(tok, t_host, top_k, penalty, True)
+        tok = pkg.sample_topk_candidates(cand, gcfg, rnd)
+        host_ids.append(tok)
+    # device loop
+    t_dev = gpu.new_cache_table(64, kv_dtype=pkg.F32)
+    gpu.prefill_prompt(prompt, t_dev)
+    dev_ids, state, _ = gpu.decode_sampled(first, t_dev, steps, top_k, temperature, top_p, penalty, [seed])
+    assert dev_ids.ravel().tolist() == host_ids
+    assert int(state[0]) == int(rnd[0])
+    assert t_dev.position(0) == t_host.position(0)
+
+
+def test_device_sampled_loop_argument_checks(c1):
+    cfg, gpu, _ = c1
+    t = gpu.new_cache_table(32, kv_dtype=pkg.F32)
+    gpu.prefill_prompt(syn.prompt_ids(cfg["vocab_size"], 4, seed=1), t)
+    with pytest.raises(pkg.Oxg4Error):
+        gpu.decode_sampled(1, t, 4, 1, 1.0, 1.0, 1.0, [1])          # one candidate: greedy, not sampling
+    with pytest.raises(pkg.Oxg4Error):
+        gpu.decode_sampled(1, t, 4, 8, 0.0, 1.0, 1.0, [1])          # temperature must be positive
+    with pytest.raises(pkg.Oxg4Error):
+        gpu.decode_sampled(1, t, 400, 8, 1.0, 1.0, 1.0, [1])        # would outgrow the table
