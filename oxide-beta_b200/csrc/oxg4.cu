@@ -105,7 +105,8 @@ struct oxg4_model {
     int mega_R[4] = {1, 1, 1, 1}, mega_F[4] = {1, 1, 1, 1}, mega_stage_bytes = 0, mega_x_bytes = 0, mega_slot_floats = 0;
     size_t mega_smem = 0;
     int mega_pf_kb = 192;
-    int pf_cap_kb = 256;
+    int pf_cap_kb = 128;          // KiB of its own weight block a CTA pulls into L2 before the dependency wait
+    int pf_cap_gu_kb = -1, pf_cap_down_kb = -1;   // overrides for the gate/up and down projections (-1: pf_cap_kb)
     bool timeline = false;        // OXG4_TIMELINE: kernels stamp the global timer into the cache's buffer     // pull later kernels' weights into L2 during latency-bound kernels
     bool finalized = false;
     std::map<std::string, Tensor> tensors;
@@ -224,6 +225,8 @@ extern "C" int32_t oxg4_model_create(const oxg4_config* c, int32_t device, oxg4_
     m->use_pdl = getenv("OXG4_DISABLE_PDL") == nullptr;
     m->timeline = getenv("OXG4_TIMELINE") != nullptr;
     if (const char* e = getenv("OXG4_PREFETCH_KB")) m->pf_cap_kb = std::max(0, atoi(e));
+    if (const char* e = getenv("OXG4_PREFETCH_KB_GATEUP")) m->pf_cap_gu_kb = std::max(0, atoi(e));
+    if (const char* e = getenv("OXG4_PREFETCH_KB_DOWN")) m->pf_cap_down_kb = std::max(0, atoi(e));
     m->far_prefetch = getenv("OXG4_FAR_PREFETCH") != nullptr;   // measured slower on B200: off by default
     if (cudaSetDevice(device) != cudaSuccess) { delete m; return fail(OXG4_CUDA, "Gemma 4 CUDA error: cudaSetDevice"); }
     cudaDeviceProp prop;
@@ -1175,6 +1178,8 @@ static void launch_gemv(Launcher& ln, const char* kind, oxg4_cache* c, GemvArgs 
     a.eps = m->cfg.rms_norm_eps;
     a.ts = ln.ts();
     a.pf_cap_kb = m->pf_cap_kb;
+    if (epi == EPI_GATEUP && m->pf_cap_gu_kb >= 0) a.pf_cap_kb = m->pf_cap_gu_kb;
+    if (!strcmp(kind, "down") && m->pf_cap_down_kb >= 0) a.pf_cap_kb = m->pf_cap_down_kb;
     if (pro == PRO_NORM && p.K > std::min(kGemvMaxJ * kGemvThreads, kSimtMaxJ * kSimtThreads)) {
         ln.status = fail(OXG4_UNSUPPORTED, "hidden size above %d is not supported",
                          std::min(kGemvMaxJ * kGemvThreads, kSimtMaxJ * kSimtThreads));
