@@ -14,6 +14,10 @@ the tied LM head and the fused arg-max. Prints ONE JSON line (rank 0).
              right after the timed region; `step_*` keys give the whole-step figure.
   cpu_baseline / --impl reference: the CPU oracle (a port of the reference's arithmetic; the
              reference has no CPU forward pass of its own) on this box's host cores.
+  tp         (default workload only) the ~12B workload tensor-parallel over all N ranks, N = 1 included:
+             tokens/s, step time, per-kind kernel times and the time spent in the per-layer all-reduces,
+             so that a 1/2/4/8-GPU series of this command also measures the path's real exchange step
+             (the default ~4B workload itself runs one replica per GPU: no data-path collective).
 
 Weights are seeded random N(0, 0.02) (generated with torch on the GPU when one is present, then
 handed to the library through its host-pointer upload call); prompts are seeded uniform ids.
@@ -38,6 +42,7 @@ METRIC = "decode_tokens_per_s"
 UNIT = "tok/s"
 DEFAULT_WORKLOAD = "c3"          # ~4B-class, batch 1: the configuration the 70%-of-HBM target is quoted on
 NCU_TRAFFIC_BYTES = {"c3": 108442368}   # gate/up launch: dram read + write bytes from the ncu capture in profiles/
+TP_RECORD_PROMPT = 512           # prompt length of the tensor-parallel (~12B) record that accompanies the default run
 
 
 def peaks():
@@ -144,6 +149,112 @@ def cpu_oracle_run(cfg, weights_iter, prompt, steps, warmup):
     return steps / dt, dt, orc.num_threads()
 
 
+def run_workload(pkg, dist, rank, local_rank, world, name, tp, prompt_len, steps, warmup, layers=None, vocab=None,
+                 keep_host=False, e2e=True, sampler=None):
+    """Loads workload `name` (tensor-parallel over `tp` ranks, or one replica per rank), ingests the
+    prompts, then times `steps` decode steps after `warmup`. Returns the measurements of this rank
+    (times already reduced to the maximum over ranks)."""
+    import torch
+    syn = pkg.synthetic
+    w = syn.workload(name)
+    cfg, B = w["cfg"], w["batch"]
+    if layers or vocab:
+        cfg = syn.scaled_down(cfg, layers=layers, vocab=vocab)
+    if prompt_len is None:
+        prompt_len = w["prompt"] if isinstance(w["prompt"], int) else None
+    t_load = time.perf_counter()
+    state = pkg.Gemma4CudaState(pkg.Gemma4TextConfig(cfg), local_rank, pkg.BF16, tp_rank=rank if tp > 1 else 0,
+                                tp_size=tp)
+    host_weights = []
+    for wname, a in torch_weights(cfg, f"cuda:{local_rank}"):
+        state.upload(wname, a)
+        if keep_host:
+            host_weights.append((wname, a))
+    state.finalize()
+    if tp > 1:
+        ids = [pkg.Gemma4CudaState.tp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        state.tp_init(ids[0])
+    torch.cuda.empty_cache()
+    load_s = time.perf_counter() - t_load
+
+    if prompt_len is None:           # ragged workload: per-sequence prompt lengths from seed 2
+        lens = syn.ragged_lengths(B, w["prompt"][0], w["prompt"][1], seed=2).tolist()
+    else:
+        lens = [prompt_len] * B
+    total_steps = warmup + steps
+    max_seq = [n + 2 * total_steps + 16 for n in lens]
+    table = state.new_cache_table(max_seq, batch=B, kv_dtype=pkg.BF16)
+    tp_exchange = "nccl"
+    if tp > 1 and 8 <= B <= 64 and os.environ.get("OXG4_TP_PEER"):
+        handles = [None] * world           # opt-in: the O/down sums travel through peer memory instead of NCCL
+        dist.all_gather_object(handles, table.tp_export())
+        table.tp_connect(handles)
+        tp_exchange = "peer-memory"
+    prompts = [syn.prompt_ids(cfg["vocab_size"], n, seed=1 + b) for b, n in enumerate(lens)]
+    t_pre = time.perf_counter()
+    logits = state.prefill_prompt(np.concatenate(prompts), table, lens=lens)
+    prefill_s = time.perf_counter() - t_pre
+    first = np.atleast_2d(logits).argmax(-1).astype(np.uint32)
+
+    # device-resident loop: warm-up, then the timed K steps bracketed by barrier + synchronize
+    ids, _ = state.decode_greedy(first, table, warmup)
+    if dist:
+        dist.barrier()
+    torch.cuda.synchronize()
+    if sampler:
+        sampler.start()                    # SM clocks and throttle reasons DURING the timed region
+    launches1 = state.kernel_launches()
+    ids, ms_step = state.decode_greedy(ids[-1], table, steps)
+    torch.cuda.synchronize()
+    launches_timed = state.kernel_launches() - launches1
+    if dist:
+        dist.barrier()
+    tok = ids[-1].copy()
+    e2e_s, e2e_steps, inter_token_ms = float("nan"), 0, [float("nan")]
+    if e2e:
+        # end to end: the per-token public call with host buffers (H2D token ids, D2H (id, score), one sync)
+        for _ in range(3):
+            r = state.decode_topk(tok, table, 1, 1.0, True)
+            tok = np.array([r[0][0]], dtype=np.uint32) if B == 1 else r[0][:, 0].copy()
+        e2e_steps = min(steps, total_steps - 3)
+        t0 = time.perf_counter()
+        stamps = [t0]
+        for _ in range(e2e_steps):
+            r = state.decode_topk(tok, table, 1, 1.0, True)
+            tok = np.array([r[0][0]], dtype=np.uint32) if B == 1 else r[0][:, 0].copy()
+            stamps.append(time.perf_counter())
+        e2e_s = stamps[-1] - t0
+        inter_token_ms = sorted(1000.0 * (b_ - a_) for a_, b_ in zip(stamps[:-1], stamps[1:]))
+    clocks = sampler.stop() if sampler else None
+    if dist:
+        t = torch.tensor([ms_step, e2e_s if e2e else 0.0], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step, e2e_s = float(t[0]), float(t[1]) if e2e else e2e_s
+
+    # per-kernel timing: eager steps with CUDA events around every launch and collective
+    contexts = [table.position(b) for b in range(B)]
+    prof, prof_step = {}, {}
+    n_prof = 5
+    for _ in range(n_prof):
+        for k, v in state.profile_step(tok, table).items():
+            prof[k] = prof.get(k, 0.0) + v / n_prof
+        for k, v in state.profile_step(tok, table, totals=True).items():
+            prof_step[k] = prof_step.get(k, 0.0) + v / n_prof
+    step_bytes, parts = algorithmic_bytes(cfg, B, contexts)
+    parts["gateup_launch"] //= tp          # a rank streams its shard of the projection
+    if dist:
+        dist.barrier()                     # no rank frees its cache table while a peer may still read it
+    del table
+    state.close()
+    torch.cuda.empty_cache()
+    return dict(cfg=cfg, B=B, lens=lens, tp=tp, tp_exchange=tp_exchange, ms_step=ms_step, e2e_s=e2e_s,
+                e2e_steps=e2e_steps, inter_token_ms=inter_token_ms, contexts=contexts, prof=prof, prof_step=prof_step,
+                step_bytes=step_bytes, parts=parts, load_s=load_s, prefill_s=prefill_s,
+                launches_timed=int(launches_timed), host_weights=host_weights, steps=steps, warmup=warmup,
+                clocks=clocks)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -153,6 +264,9 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
     ap.add_argument("--prompt", type=int, default=None, help="override the prompt length")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-tp-record", action="store_true",
+                    help="skip the tensor-parallel ~12B measurement that accompanies the default workload")
+    ap.add_argument("--tp-prompt", type=int, default=TP_RECORD_PROMPT, help="prompt length of the tensor-parallel record")
     ap.add_argument("--layers", type=int, default=None, help="profiling aid: keep only the first LAYERS layers")
     ap.add_argument("--vocab", type=int, default=None, help="profiling aid: shrink the vocabulary")
     args = ap.parse_args()
@@ -163,11 +277,6 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     pkg = importlib.import_module("oxide-beta_b200")
     syn = pkg.synthetic
-    w = syn.workload(args.workload)
-    cfg, B = w["cfg"], w["batch"]
-    if args.layers or args.vocab:
-        cfg = syn.scaled_down(cfg, layers=args.layers, vocab=args.vocab)
-    prompt_len = args.prompt or (w["prompt"] if isinstance(w["prompt"], int) else w["prompt"][1])
 
     import torch
     has_gpu = torch.cuda.is_available()
@@ -178,17 +287,22 @@ def main():
             return
         # torchrun exports OMP_NUM_THREADS=1 to every rank; the CPU reference uses all host cores
         os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
+        w = syn.workload(args.workload)
+        cfg = w["cfg"]
+        if args.layers or args.vocab:
+            cfg = syn.scaled_down(cfg, layers=args.layers, vocab=args.vocab)
+        # a bounded sample of the workload: the step count asked for, after a short prompt (ingesting the
+        # full prompt token by token on the CPU would take minutes and is outside the timed region anyway)
         sample_prompt = 32
-        steps = min(args.steps, 16)
-        wu = min(warmup, 3)
+        steps = args.steps
         weights = torch_weights(cfg, "cuda:0" if has_gpu else "cpu")
         prompt = syn.prompt_ids(cfg["vocab_size"], sample_prompt, seed=1)
-        tps, dt, cores = cpu_oracle_run(cfg, weights, prompt, steps, wu)
+        tps, dt, cores = cpu_oracle_run(cfg, weights, prompt, steps, warmup)
         sample = (f"{steps} greedy decode steps at batch 1 after a {sample_prompt}-token prompt "
                   f"(full {args.workload} weights, BF16 recipe, OpenMP over {cores} threads)")
         print(json.dumps({
             "impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-            "warmup": wu, "ms_per_step": 1000.0 * dt / steps, "higher_is_better": True, "scaling": "weak",
+            "warmup": warmup, "ms_per_step": 1000.0 * dt / steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": args.workload, "batch": 1, "prompt": sample_prompt,
                        "note": "CPU port of the reference arithmetic; the reference has no CPU forward pass"},
@@ -207,107 +321,46 @@ def main():
 
     # the 12B / 27B workloads are tensor-parallel across the ranks; the smaller ones run one replica per GPU
     tp = world if (world > 1 and args.workload in ("c4", "c5")) else 1
-    t_load = time.perf_counter()
-    state = pkg.Gemma4CudaState(pkg.Gemma4TextConfig(cfg), local_rank, pkg.BF16, tp_rank=rank if tp > 1 else 0,
-                                tp_size=tp)
-    host_weights = []
     keep_host = (rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload in ("c1", "c2", "c3"))
-    for name, a in torch_weights(cfg, f"cuda:{local_rank}"):
-        state.upload(name, a)
-        if keep_host:
-            host_weights.append((name, a))
-    state.finalize()
-    if tp > 1:
-        ids = [pkg.Gemma4CudaState.tp_unique_id() if rank == 0 else None]
-        dist.broadcast_object_list(ids, src=0)
-        state.tp_init(ids[0])
-    torch.cuda.empty_cache()
-    load_s = time.perf_counter() - t_load
-
-    lens = [prompt_len] * B
-    if not isinstance(w["prompt"], int) and args.prompt is None:
-        lens = syn.ragged_lengths(B, w["prompt"][0], w["prompt"][1], seed=2).tolist()
-    total_steps = warmup + args.steps
-    max_seq = [n + 2 * total_steps + 8 for n in lens]
-    table = state.new_cache_table(max_seq, batch=B, kv_dtype=pkg.BF16)
-    tp_exchange = "nccl"
-    if tp > 1 and 8 <= B <= 64 and os.environ.get("OXG4_TP_PEER"):
-        handles = [None] * world           # opt-in: the O/down sums travel through peer memory instead of NCCL
-        dist.all_gather_object(handles, table.tp_export())
-        table.tp_connect(handles)
-        tp_exchange = "peer-memory"
-    prompts = [syn.prompt_ids(cfg["vocab_size"], n, seed=1 + b) for b, n in enumerate(lens)]
-    t_pre = time.perf_counter()
-    logits = state.prefill_prompt(np.concatenate(prompts), table, lens=lens)
-    prefill_s = time.perf_counter() - t_pre
-    first = np.atleast_2d(logits).argmax(-1).astype(np.uint32)
-
-    launches0 = state.kernel_launches()
-    # device-resident loop: warm-up then the timed K steps
-    ids, _ = state.decode_greedy(first, table, warmup)
-    if dist:
-        dist.barrier()
-    torch.cuda.synchronize()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-    launches1 = state.kernel_launches()
-    ids, ms_step = state.decode_greedy(ids[-1], table, args.steps)
-    torch.cuda.synchronize()
-    launches_timed = state.kernel_launches() - launches1
-    if dist:
-        dist.barrier()
-    # end-to-end: per-token public call with host buffers
-    tok = ids[-1].copy()
-    for _ in range(3):
-        r = state.decode_topk(tok, table, 1, 1.0, True)
-        tok = np.array([r[0][0]], dtype=np.uint32) if B == 1 else r[0][:, 0].copy()
-    e2e_steps = min(args.steps, total_steps - 3)
-    t0 = time.perf_counter()
-    stamps = [t0]
-    for _ in range(e2e_steps):
-        r = state.decode_topk(tok, table, 1, 1.0, True)
-        tok = np.array([r[0][0]], dtype=np.uint32) if B == 1 else r[0][:, 0].copy()
-        stamps.append(time.perf_counter())
-    e2e_s = stamps[-1] - t0
-    inter_token_ms = sorted(1000.0 * (b_ - a_) for a_, b_ in zip(stamps[:-1], stamps[1:]))
-    clocks = sampler.stop()
-
-    if dist:
-        t = torch.tensor([ms_step, e2e_s], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_step, e2e_s = float(t[0]), float(t[1])
+    r = run_workload(pkg, dist, rank, local_rank, world, args.workload, tp, args.prompt, args.steps, warmup,
+                     args.layers, args.vocab, keep_host=keep_host, sampler=ClockSampler(local_rank))
+    clocks = r["clocks"]
+    cfg, B, lens, ms_step = r["cfg"], r["B"], r["lens"], r["ms_step"]
     replicas = world // tp
     value = replicas * B * 1000.0 / ms_step
-    e2e_value = replicas * B * e2e_steps / e2e_s
-
-    # dominant-kernel timing: eager steps with CUDA events around every launch
-    contexts = [table.position(b) for b in range(B)]
-    prof = {}
-    n_prof = 5
-    for _ in range(n_prof):
-        p = state.profile_step(tok, table)
-        for k, v in p.items():
-            if v >= 0:
-                prof[k] = prof.get(k, 0.0) + v / n_prof
-        tok = tok.copy()
+    e2e_value = replicas * B * r["e2e_steps"] / r["e2e_s"]
     peak, peak_kind = peaks()
-    step_bytes, parts = algorithmic_bytes(cfg, B, contexts)
-    gu_ms = prof.get("gateup", float("nan"))
-    parts["gateup_launch"] //= tp          # a rank streams its shard of the projection
-    achieved = parts["gateup_launch"] / (gu_ms * 1e-3) / 1e9
+    gu_ms = r["prof"].get("gateup", float("nan"))
+    achieved = r["parts"]["gateup_launch"] / (gu_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": ("gemv_kernel<bf16, PRO_NORM, EPI_GATEUP>" if B == 1 else
                            "gemv_mma_kernel<PRO_NORM, EPI_GATEUP>" if B < 8 else
                            "tc_gemm_kernel (tcgen05, gate and up maps)" if B <= 64 else
                            "gemv_mma_kernel<PRO_NORM, EPI_GATEUP>") + " (gate/up projection)",
                 "achieved": achieved, "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
                 "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
-                "bytes_per_launch": parts["gateup_launch"], "ms_per_launch": gu_ms,
-                "step_bytes": step_bytes, "step_achieved": step_bytes / (ms_step * 1e-3) / 1e9,
-                "step_frac": step_bytes / (ms_step * 1e-3) / 1e9 / (peak * tp),
-                "kernel_ms": {k: round(v, 5) for k, v in prof.items()}}
+                "bytes_per_launch": r["parts"]["gateup_launch"], "ms_per_launch": gu_ms,
+                "step_bytes": r["step_bytes"], "step_achieved": r["step_bytes"] / (ms_step * 1e-3) / 1e9,
+                "step_frac": r["step_bytes"] / (ms_step * 1e-3) / 1e9 / (peak * tp),
+                "kernel_ms": {k: round(v, 5) for k, v in r["prof"].items()}}
 
-    if dist:
-        dist.barrier()                     # no rank frees its cache table while a peer may still read it
+    # the tensor-parallel record: the ~12B workload split over all N ranks (N = 1 included), so that the
+    # 1/2/4/8-GPU series of the default workload also carries a strong-scaling curve with a real exchange
+    tp_record = None
+    if args.workload == DEFAULT_WORKLOAD and not args.no_tp_record and not (args.layers or args.vocab):
+        t_steps, t_warm = min(args.steps, 64), min(warmup, 8)
+        t = run_workload(pkg, dist, rank, local_rank, world, "c4", world, args.tp_prompt, t_steps, t_warm, e2e=False)
+        ar = t["prof_step"].get("allreduce", 0.0) + t["prof_step"].get("allgather", 0.0)
+        tp_record = {
+            "workload": "c4", "tp": world, "batch": t["B"], "prompt": args.tp_prompt, "steps": t_steps, "warmup": t_warm,
+            "context_at_timing": t["contexts"][0], "value": t["B"] * 1000.0 / t["ms_step"], "unit": UNIT,
+            "ms_per_step": t["ms_step"], "scaling": "strong", "exchange": t["tp_exchange"] if world > 1 else "none",
+            "step_bytes": t["step_bytes"], "step_frac": t["step_bytes"] / (t["ms_step"] * 1e-3) / 1e9 / (peak * world),
+            "kernel_ms": {k: round(v, 5) for k, v in t["prof"].items()},
+            "kernel_ms_per_step": {k: round(v, 4) for k, v in t["prof_step"].items()},
+            "collectives_ms_per_step": round(ar, 4),
+            "note": "eager event timing per launch (no overlap between launches); ms_per_step is the graph replay",
+            "load_s": round(t["load_s"], 2), "prefill_s": round(t["prefill_s"], 2)}
+
     if rank != 0:
         dist.destroy_process_group()
         return
@@ -318,21 +371,23 @@ def main():
         "config": {"workload": args.workload + (f" (reduced: layers={args.layers} vocab={args.vocab})"
                                                  if (args.layers or args.vocab) else ""),
                    "batch": B, "prompt": lens[0] if len(set(lens)) == 1 else "ragged",
-                   "context_at_timing": contexts[0], "kv_dtype": "bf16", "page_tokens": 256,
-                   "parallelism": "single GPU" if world == 1 else (f"tp{tp} (sums after O and down: {tp_exchange})"
+                   "context_at_timing": r["contexts"][0], "kv_dtype": "bf16", "page_tokens": 256,
+                   "parallelism": "single GPU" if world == 1 else (f"tp{tp} (sums after O and down: {r['tp_exchange']})"
                                                                    if tp > 1 else f"{world} independent replicas"),
                    "l2": "per-step inputs (weights + KV) exceed the 126 MB L2; no flush",
-                   "load_s": round(load_s, 2), "prefill_s": round(prefill_s, 2)},
-        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * B + 16, "d2h_bytes_per_step": 8 * B,
-                "steps": e2e_steps, "p50_inter_token_ms": inter_token_ms[len(inter_token_ms) // 2],
-                "p95_inter_token_ms": inter_token_ms[int(len(inter_token_ms) * 0.95)]},
-        "gpu_launches": int(launches_timed),
+                   "load_s": round(r["load_s"], 2), "prefill_s": round(r["prefill_s"], 2)},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * B + 28, "d2h_bytes_per_step": 8 * B,
+                "steps": r["e2e_steps"], "p50_inter_token_ms": r["inter_token_ms"][len(r["inter_token_ms"]) // 2],
+                "p95_inter_token_ms": r["inter_token_ms"][int(len(r["inter_token_ms"]) * 0.95)]},
+        "gpu_launches": r["launches_timed"],
         "clocks": clocks,
         "roofline": roofline,
     }
+    if tp_record is not None:
+        out["tp"] = tp_record
     if keep_host:
         sample_prompt, cpu_steps = 32, 8
-        tps, dt, cores = cpu_oracle_run(cfg, host_weights, syn.prompt_ids(cfg["vocab_size"], sample_prompt, seed=1),
+        tps, dt, cores = cpu_oracle_run(cfg, r["host_weights"], syn.prompt_ids(cfg["vocab_size"], sample_prompt, seed=1),
                                         cpu_steps, 2)
         out["cpu_baseline"] = {"value": tps, "unit": UNIT, "cores": cores, "kind": "port",
                                "sample": f"{cpu_steps} greedy decode steps at batch 1 after a {sample_prompt}-token "

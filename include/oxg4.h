@@ -183,11 +183,14 @@ int32_t oxg4_decode_sampled(oxg4_model* model, oxg4_cache* cache, const uint32_t
 int64_t oxg4_kernel_launches(const oxg4_model* model);
 
 /* Mean device time in milliseconds, measured with CUDA events on the model's stream, of the
- * decode kernels of the kind `kind` ("qkv", "attn", "o", "gateup", "down", "lmhead") during the
- * most recent oxg4_profile_step call; that call runs one eager decode step with events around
- * every kernel. */
+ * launches of the kind `kind` ("qkv", "attn", "o", "gateup", "down", "lmhead", "norm", "geglu", "sum",
+ * "topk1", "topk2", "allreduce", "allgather", ...) during the most recent oxg4_profile_step call, and
+ * how many launches of that kind the step made; that call runs one eager decode step with events
+ * around every kernel and every tensor-parallel collective. Measurement aid in the role of the
+ * reference's GEMMA4_PROFILE hook (crates/oxide-torch-models/examples/gemma4_load.rs:277-284). */
 int32_t oxg4_profile_step(oxg4_model* model, oxg4_cache* cache, const uint32_t* tokens);
 float oxg4_profile_ms(const oxg4_model* model, const char* kind);
+int32_t oxg4_profile_count(const oxg4_model* model, const char* kind);
 
 /* Top-k selection that allocates nothing (no counterpart in the reference). It is meant for callers
  * that are not allowed to allocate device memory at the moment they need a top-k: code running

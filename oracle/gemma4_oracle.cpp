@@ -121,9 +121,44 @@ struct Cache {
     std::vector<uint8_t> seen;     // repetition-penalty bitmap (decode.rs:681-688)
 };
 
+// Summation order of every projection's dot products. The reference leaves it to cuBLAS (unpinned), so
+// tests may select another order to measure how far two correct implementations can drift apart:
+//   0  the compiler's vectorised reduction (default)
+//   1  eight interleaved partial sums (k mod 8), added pairwise at the end
+//   2  one serial f32 sum from the last element to the first
+int g_accum_order = 0;
+
+template <class Load>
+inline float dot_ordered(const float* x, int64_t K, Load w) {
+    if (g_accum_order == 1) {
+        float p[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        int64_t k = 0;
+        for (; k + 8 <= K; k += 8)
+            for (int j = 0; j < 8; ++j) p[j] += x[k + j] * w(k + j);
+        for (int j = 0; k < K; ++k, ++j) p[j] += x[k] * w(k);
+        return ((p[0] + p[4]) + (p[2] + p[6])) + ((p[1] + p[5]) + (p[3] + p[7]));
+    }
+    float acc = 0.0f;
+    for (int64_t k = K - 1; k >= 0; --k) acc += x[k] * w(k);
+    return acc;
+}
+
 // out[n] = sum_k x[k] * W[n,k]   (cublas.rs:101: output[m,n] = input[m,k] . weight[n,k]^T, m = 1)
 void gemv(const Matrix& W, const float* x, float* out) {
     const int64_t N = W.rows, K = W.cols;
+    if (g_accum_order != 0) {
+#pragma omp parallel for schedule(static)
+        for (int64_t n = 0; n < N; ++n) {
+            if (W.is_bf16) {
+                const uint16_t* row = W.h.data() + n * K;
+                out[n] = dot_ordered(x, K, [row](int64_t k) { return bf16_bits_to_f32(row[k]); });
+            } else {
+                const float* row = W.f.data() + n * K;
+                out[n] = dot_ordered(x, K, [row](int64_t k) { return row[k]; });
+            }
+        }
+        return;
+    }
     if (W.is_bf16) {
         const uint16_t* w = W.h.data();
 #pragma omp parallel for schedule(static)
@@ -749,6 +784,15 @@ int orc_decode_trace(void* model, void* cache, uint32_t token, const float* inje
     forward_token(*m, *(Cache*)cache, token, hidden, inject_or_null, trace_or_null);
     if (logits_or_null) lm_head(*m, hidden, logits_or_null);
     return 0;
+}
+
+// Test aid (no counterpart in the reference): summation order of the projections, see g_accum_order.
+void orc_set_accum_order(int order) { g_accum_order = order; }
+
+// gemma4_cuda/mod.rs:573-579 — apply_logit_softcap: tanh(x / cap) * cap in f32 on the host.
+void orc_softcap(float* values, int64_t n, float cap) {
+    if (cap > 0.0f)
+        for (int64_t i = 0; i < n; ++i) values[i] = tanhf(values[i] / cap) * cap;
 }
 
 void orc_set_num_threads(int n) {

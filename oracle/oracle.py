@@ -258,11 +258,18 @@ class OracleCache:
         if lib().orc_prefill_token(self.model._h, self._h, C.c_uint32(token)) != 0:
             raise ValueError("token id exceeds vocabulary")
 
+    def _softcap(self, values: np.ndarray):
+        """gemma4_cuda/mod.rs:573-579: the reference softcaps the scores it hands back to the host."""
+        cap = self.model.cfg.get("final_logit_softcapping")
+        if cap:
+            lib().orc_softcap(_fp(values), C.c_int64(values.size), C.c_float(cap))
+        return values
+
     def decode_logits(self, token: int) -> np.ndarray:
         logits = np.empty(self.model.cfg["vocab_size"], dtype=np.float32)
         if lib().orc_decode_logits(self.model._h, self._h, C.c_uint32(token), _fp(logits)) != 0:
             raise ValueError("token id exceeds vocabulary")
-        return logits
+        return self._softcap(logits)
 
     def decode_trace(self, token: int, inject=None, want_logits=True):
         """One token; returns (trace [layers + 1, hidden], logits). `inject` [layers, hidden] replaces
@@ -288,8 +295,13 @@ class OracleCache:
         if k < 0:
             raise ValueError("token id exceeds vocabulary")
         if want_logits:
-            return ids[:k].copy(), scores[:k].copy(), logits
-        return ids[:k].copy(), scores[:k].copy()
+            return ids[:k].copy(), self._softcap(scores[:k].copy()), self._softcap(logits)
+        return ids[:k].copy(), self._softcap(scores[:k].copy())
+
+
+def set_accum_order(order: int):
+    """0: default; 1: eight interleaved partial sums; 2: serial from the last element (test aid)."""
+    lib().orc_set_accum_order(C.c_int(order))
 
 
 def set_num_threads(n: int):

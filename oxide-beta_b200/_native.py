@@ -78,6 +78,7 @@ SYMBOLS = {
     "oxg4_kernel_launches": (C.c_int64, [C.c_void_p]),
     "oxg4_profile_step": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "oxg4_profile_ms": (C.c_float, [C.c_void_p, C.c_char_p]),
+    "oxg4_profile_count": (C.c_int32, [C.c_void_p, C.c_char_p]),
     "oxg4_topk_noalloc": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_float, C.c_int32, C.c_void_p,
                                       C.c_void_p, C.c_void_p]),
     "oxg4_decode_trace": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),

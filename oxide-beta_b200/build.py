@@ -12,11 +12,11 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "liboxg4.so")
 SOURCES = ["oxg4.cu"]
-HEADERS = ["common.cuh", "gemv.cuh", "gemv_mma.cuh", "attention.cuh", "sampling.cuh", "tc_gemm.cuh", "tp.h"]
 
 
 def _newest_source() -> float:
-    files = [os.path.join(CSRC, f) for f in SOURCES + HEADERS]
+    # every file under csrc/ is compiled into the one translation unit: any edit triggers a rebuild
+    files = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cu", ".cuh", ".h"))]
     files.append(os.path.join(os.path.dirname(HERE), "include", "oxg4.h"))
     return max(os.path.getmtime(f) for f in files if os.path.exists(f))
 

@@ -1125,19 +1125,39 @@ struct Launcher {
         ++kernels;
     }
 
+    // profiling steps bracket every launch (collectives included) with a pair of events on the model's stream
+    void prof_begin(cudaEvent_t& e0, cudaEvent_t& e1) {
+        e0 = e1 = nullptr;
+        if (!m->profiling) return;
+        cudaEventCreate(&e0);
+        cudaEventCreate(&e1);
+        cudaEventRecord(e0, m->stream);
+    }
+    void prof_end(const char* kind, cudaEvent_t e0, cudaEvent_t e1) {
+        if (!m->profiling) return;
+        cudaEventRecord(e1, m->stream);
+        m->prof_events.push_back({kind, {e0, e1}});
+    }
+
     // in-place sum over the tensor-parallel ranks (one NCCL all-reduce on the model's stream)
     void allreduce(float* buf, size_t count) {
         if (status != OXG4_OK || m->tp == 1) return;
         if (!m->comm) { status = fail(OXG4_NCCL, "tensor-parallel model used before oxg4_model_tp_init"); return; }
+        cudaEvent_t e0, e1;
+        prof_begin(e0, e1);
         const int rc = nccl().AllReduce(buf, buf, count, NcclApi::kFloat32, NcclApi::kSum, m->comm, m->stream);
         if (rc != 0) { status = fail(OXG4_NCCL, "NCCL: ncclAllReduce: %s", nccl().GetErrorString(rc)); return; }
+        prof_end("allreduce", e0, e1);
         ++kernels;
     }
     void allgather(const void* src, void* dst, size_t bytes_per_rank) {
         if (status != OXG4_OK || m->tp == 1) return;
         if (!m->comm) { status = fail(OXG4_NCCL, "tensor-parallel model used before oxg4_model_tp_init"); return; }
+        cudaEvent_t e0, e1;
+        prof_begin(e0, e1);
         const int rc = nccl().AllGather(src, dst, bytes_per_rank, NcclApi::kUint8, m->comm, m->stream);
         if (rc != 0) { status = fail(OXG4_NCCL, "NCCL: ncclAllGather: %s", nccl().GetErrorString(rc)); return; }
+        prof_end("allgather", e0, e1);
         ++kernels;
     }
 };
@@ -1243,6 +1263,10 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
     Launcher ln{m};
     ln.ts_base = c->ts_buf;
     const int B = c->B, L = m->cfg.num_hidden_layers, H = m->H, D = m->D;
+    // Sums over peer memory only in steps whose last exchange is consumed (the closing norm before the
+    // LM head): a prompt-ingestion step skips that norm, so it takes the NCCL all-reduce instead and the
+    // single exchange buffer per kind is never pushed into while a peer may still read it.
+    const bool peer = c->peer_ready && kind != STEP_PREFILL;
     ln.go("step_begin", step_begin_kernel, dim3(1), dim3(128), 0, B, m->V,
           (const uint32_t*)c->tokens, c->seen, (const StepCtl*)c->ctl);
     // q/k norm + RoPE + v norm + KV append + attention (decode.rs:99-157)
@@ -1352,9 +1376,9 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
                 n.tokens = c->tokens;
                 n.embed_scale = sqrtf((float)H);
             } else {
-                n.raw = m->tp > 1 ? (c->peer_ready ? c->px[1].gathered : c->down_raw) : c->down_part;
-                n.raw_splits = m->tp > 1 ? (c->peer_ready ? m->tp : 1) : c->s_down;
-                if (m->tp > 1 && c->peer_ready) n.px = c->px[1];
+                n.raw = m->tp > 1 ? (peer ? c->px[1].gathered : c->down_raw) : c->down_part;
+                n.raw_splits = m->tp > 1 ? (peer ? m->tp : 1) : c->s_down;
+                if (m->tp > 1 && peer) n.px = c->px[1];
                 n.w_post = m->layers[l - 1].post_ff_ln;
                 n.scalar = m->layers[l - 1].layer_scalar;
             }
@@ -1373,19 +1397,19 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
             const dim3 sum_grid((unsigned)((bh + kRowsThreads - 1) / kRowsThreads));
             PeerExchange none{};
             none.tp = 1;
-            const float* xo = c->peer_ready ? c->px[0].gathered : c->o_raw;        // what the next norm reads
-            const int xs = c->peer_ready ? m->tp : 1;                              // partials to add there
+            const float* xo = peer ? c->px[0].gathered : c->o_raw;        // what the next norm reads
+            const int xs = peer ? m->tp : 1;                              // partials to add there
             if (m->tp > 1) {      // row-split projection: add the K-splits locally, then the ranks
                 ln.go("sum", sum_splits_kernel, sum_grid, dim3(kRowsThreads), 0, (const float*)c->o_part, c->s_o, bh, c->o_raw,
-                      c->peer_ready ? c->px[0] : none);
-                if (!c->peer_ready) ln.allreduce(c->o_raw, bh);
+                      peer ? c->px[0] : none);
+                if (!peer) ln.allreduce(c->o_raw, bh);
             }
             RowsNormArgs n2{};
             n2.B = B; n2.H = H;
             n2.h_in = c->hB; n2.h_out = c->hA;
             n2.raw = m->tp > 1 ? xo : c->o_part;
             n2.raw_splits = m->tp > 1 ? xs : c->s_o;
-            n2.px = (m->tp > 1 && c->peer_ready) ? c->px[0] : none;
+            n2.px = (m->tp > 1 && peer) ? c->px[0] : none;
             n2.w_post = p.post_attn_ln;
             n2.scalar = 1.0f;
             n2.w_norm = p.pre_ff_ln;
@@ -1398,8 +1422,8 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
             ln.tc("down", c, p.wdown, nullptr, c->x_i, H, m->I, c->s_down, c->down_part, H, 0);
             if (m->tp > 1) {
                 ln.go("sum", sum_splits_kernel, sum_grid, dim3(kRowsThreads), 0, (const float*)c->down_part, c->s_down, bh,
-                      c->down_raw, c->peer_ready ? c->px[1] : none);
-                if (!c->peer_ready) ln.allreduce(c->down_raw, bh);
+                      c->down_raw, peer ? c->px[1] : none);
+                if (!peer) ln.allreduce(c->down_raw, bh);
             }
             continue;
         }
@@ -1492,9 +1516,9 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
         RowsNormArgs n{};
         n.B = B; n.H = H;
         n.h_in = c->hA; n.h_out = c->hB;
-        n.raw = m->tp > 1 ? (c->peer_ready ? c->px[1].gathered : c->down_raw) : c->down_part;
-        n.raw_splits = m->tp > 1 ? (c->peer_ready ? m->tp : 1) : c->s_down;
-        if (m->tp > 1 && c->peer_ready) n.px = c->px[1];
+        n.raw = m->tp > 1 ? (peer ? c->px[1].gathered : c->down_raw) : c->down_part;
+        n.raw_splits = m->tp > 1 ? (peer ? m->tp : 1) : c->s_down;
+        if (m->tp > 1 && peer) n.px = c->px[1];
         n.w_post = m->layers[L - 1].post_ff_ln;
         n.scalar = m->layers[L - 1].layer_scalar;
         n.w_norm = m->final_norm;
@@ -1565,7 +1589,8 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
         }
     }
     if (kind == STEP_TOPK && top_k > 1)      // a no-op unless the step's control words ask for a sampled token
-        ln.go("sample", sample_candidates_kernel, dim3(1), dim3(64), 0, B, top_k, (const uint32_t*)c->tokens,
+        ln.go("sample", sample_candidates_kernel, dim3(1), dim3(64), 0, B, top_k, m->cfg.final_logit_softcapping,
+              (const uint32_t*)c->tokens,
               (const uint32_t*)c->topk_ids, (const float*)c->topk_scores, (const StepCtl*)c->ctl, c->rng, c->best_ids,
               c->best_scores);
     ln.go("step_end", step_end_kernel, dim3(1), dim3(128), 0, B, c->tokens, c->pos,
@@ -1908,6 +1933,12 @@ extern "C" float oxg4_profile_ms(const oxg4_model* m, const char* kind) {
     auto it = m->profile.find(kind);
     if (it == m->profile.end() || it->second.count == 0) return -1.0f;
     return (float)(it->second.ms / it->second.count);
+}
+
+extern "C" int32_t oxg4_profile_count(const oxg4_model* m, const char* kind) {
+    if (!m || !kind) return 0;
+    auto it = m->profile.find(kind);
+    return it == m->profile.end() ? 0 : it->second.count;
 }
 
 extern "C" int32_t oxg4_prefill(oxg4_model* m, oxg4_cache* c, const uint32_t* tokens, const int32_t* lens,

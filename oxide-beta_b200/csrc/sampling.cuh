@@ -62,8 +62,8 @@ DEVINL int32_t total_order_key_dev(float f) {
 // descending sort, softmax, top-p cut, xorshift64 (13, 7, 17), 24-bit uniform, cumulative pick. The same
 // f32 operations in the same order as the host version (oxg4_sample_topk_candidates); the generator state
 // lives on the device so that a sampled generation loop needs no per-token host round trip. The chosen
-// token replaces best_ids[b], which step_end feeds back.
-__global__ void sample_candidates_kernel(int B, int k, const uint32_t* tokens, const uint32_t* cand_ids,
+// token replaces best_ids[b], which step_end feeds back. `softcap` > 0 applies tanh(x / cap) * cap first.
+__global__ void sample_candidates_kernel(int B, int k, float softcap, const uint32_t* tokens, const uint32_t* cand_ids,
                                          const float* cand_scores, const StepCtl* ctl, unsigned long long* rng,
                                          uint32_t* best_ids, float* best_scores) {
     pdl_wait();
@@ -76,7 +76,10 @@ __global__ void sample_candidates_kernel(int B, int k, const uint32_t* tokens, c
         float v[64];
         int n = 0;
         for (int i = 0; i < k; ++i) {
-            const float s = cand_scores[(size_t)b * k + i];
+            float s = cand_scores[(size_t)b * k + i];
+            // final_logit_softcapping is applied to the candidate scores before they are sampled
+            // (gemma4_cuda/mod.rs:573-579, decode.rs:644,746), as the host path does
+            if (softcap > 0.0f) s = tanhf(s / softcap) * softcap;
             if (isfinite(s)) { id[n] = cand_ids[(size_t)b * k + i]; v[n] = s / temperature; ++n; }
         }
         if (n == 0) continue;                                  // keep the arg-max

@@ -122,7 +122,7 @@ class Gemma4CudaCacheTable:
     """Owner of an oxg4_cache handle: KV pages, device decode state and the captured step graphs."""
 
     def __init__(self, state: "Gemma4CudaState", max_sequence, batch: int = 1, page_tokens: int = 256,
-                 kv_dtype: int = N.BF16):
+                 kv_dtype: int = N.F32):
         ms = np.ascontiguousarray(np.broadcast_to(np.asarray(max_sequence, dtype=np.int32), (batch,)))
         self._state = state
         self.batch = batch
@@ -264,7 +264,9 @@ class Gemma4CudaState:
         return N.lib().oxg4_kernel_launches(self._h)
 
     def new_cache_table(self, config=None, max_sequence=None, batch: int = 1, page_tokens: int = 256,
-                        kv_dtype: int = N.BF16) -> Gemma4CudaCacheTable:
+                        kv_dtype: int = N.F32) -> Gemma4CudaCacheTable:
+        """The default KV element type is f32, the reference's ring (cache_write_f32_state);
+        BF16 pages (half the bytes per step, rounded once at append) are an explicit opt-in."""
         if max_sequence is None:               # allow new_cache_table(max_sequence)
             config, max_sequence = None, config
         return Gemma4CudaCacheTable(self, max_sequence, batch, page_tokens, kv_dtype)
@@ -344,12 +346,21 @@ class Gemma4CudaState:
                                             repetition_penalty, _ptr(s), _ptr(out), C.byref(ms)))
         return out, s, ms.value
 
-    def profile_step(self, tokens, table: Gemma4CudaCacheTable) -> dict:
-        """One eager step with CUDA events around every kernel; mean ms per kernel kind."""
+    PROFILE_KINDS = ["qkv", "qkv_post", "attn", "attn_merge", "o", "gateup", "down", "lmhead", "norm", "geglu", "sum",
+                     "topk1", "topk2", "tp_pick", "allreduce", "allgather", "step_begin", "step_end"]
+
+    def profile_step(self, tokens, table: Gemma4CudaCacheTable, totals: bool = False) -> dict:
+        """One eager step with CUDA events around every kernel and collective. Returns the mean ms per
+        launch of every kind that ran, or with `totals` the ms per STEP of every kind (mean x launches)."""
         t = _as_u32(np.atleast_1d(tokens))
         N.check(N.lib().oxg4_profile_step(self._h, table._h, _ptr(t)))
-        kinds = ["qkv", "attn", "o", "gateup", "down", "lmhead", "step_begin", "step_end"]
-        return {k: N.lib().oxg4_profile_ms(self._h, k.encode()) for k in kinds}
+        out = {}
+        for k in self.PROFILE_KINDS:
+            n = N.lib().oxg4_profile_count(self._h, k.encode())
+            if n > 0:
+                ms = N.lib().oxg4_profile_ms(self._h, k.encode())
+                out[k] = ms * n if totals else ms
+        return out
 
 
 def tp_shard(name: str, rows: int, cols: int, tp_rank: int, tp_size: int, cfg: "Gemma4TextConfig"):
@@ -389,7 +400,7 @@ class Gemma4ForCausalLM:
         self._weights = weights
         self._device = device
         self._weight_dtype = weight_dtype
-        self._kv_dtype = kv_dtype if kv_dtype is not None else weight_dtype
+        self._kv_dtype = kv_dtype if kv_dtype is not None else N.F32     # the reference's cache is f32
         self._dir = checkpoint_directory
         self._cuda: Optional[Gemma4CudaState] = None
         self._validate_checkpoint()

@@ -245,9 +245,9 @@ def test_batch_rows_are_independent():
     gpu, _ = build_pair(cfg, "bf16", kv_bf16=True, want_oracle=False)
     a = syn.prompt_ids(cfg["vocab_size"], 9, seed=30)
     b = syn.prompt_ids(cfg["vocab_size"], 5, seed=31)
-    t1 = gpu.new_cache_table([16, 16], batch=2, page_tokens=4)
+    t1 = gpu.new_cache_table([16, 16], batch=2, page_tokens=4, kv_dtype=pkg.BF16)
     l1 = gpu.prefill_prompt(np.concatenate([a, b]), t1, lens=[9, 5])
-    t2 = gpu.new_cache_table([16, 16, 16], batch=3, page_tokens=4)
+    t2 = gpu.new_cache_table([16, 16, 16], batch=3, page_tokens=4, kv_dtype=pkg.BF16)
     l2 = gpu.prefill_prompt(np.concatenate([b, b, a]), t2, lens=[5, 5, 9])
     assert np.array_equal(l1[0], l2[2]) and np.array_equal(l1[1], l2[0]) and np.array_equal(l2[0], l2[1])
 
@@ -257,7 +257,8 @@ def test_batch_rows_are_independent():
 @pytest.mark.parametrize("name,layers", [("c2", 7), ("c3", 6)])
 def test_benchmark_architecture_reduced_depth_f32(name, layers):
     """Full widths and vocabulary of the ~1B / ~4B workloads at reduced depth, f32 recipe, so that the
-    end-to-end comparison is well conditioned (see test_bf16_end_to_end_is_ill_conditioned)."""
+    end-to-end comparison is well conditioned (tests/test_oracle.py::test_summation_order_spread_grows_with_depth
+    shows why the BF16 recipe is not, at depth)."""
     w = syn.workload(name)
     cfg = syn.scaled_down(w["cfg"], layers=layers)
     gpu, oracle = build_pair(cfg, "f32", kv_bf16=False)
@@ -284,7 +285,7 @@ def test_determinism_two_runs_identical():
     prompt = syn.prompt_ids(cfg["vocab_size"], 40, seed=5)
     runs = []
     for _ in range(2):
-        table = gpu.new_cache_table(64)
+        table = gpu.new_cache_table(64, kv_dtype=pkg.BF16)
         first = int(np.argmax(gpu.prefill_prompt(prompt, table)))
         ids, _ = gpu.decode_greedy(first, table, 16)
         runs.append((ids.copy(), gpu.decode_token(int(ids[-1, 0]), table)))
@@ -438,3 +439,56 @@ def test_device_sampled_loop_argument_checks(c1):
         gpu.decode_sampled(1, t, 4, 8, 0.0, 1.0, 1.0, [1])          # temperature must be positive
     with pytest.raises(pkg.Oxg4Error):
         gpu.decode_sampled(1, t, 400, 8, 1.0, 1.0, 1.0, [1])        # would outgrow the table
+
+
+# ---- final_logit_softcapping ----------------------------------------------------------------------------
+
+@pytest.fixture(scope="module")
+def capped():
+    cfg = small_cfg(hidden=128, layers=2, heads=2, kv_heads=1, head_dim=64, inter=256, vocab=1500, window=8,
+                    layer_types=["sliding_attention", "full_attention"])
+    cfg["final_logit_softcapping"] = 0.75          # small enough to bend the seeded model's logits (|x| up to ~1.5)
+    gpu, oracle = build_pair(cfg, "f32", kv_bf16=False, norm_jitter=0.1)
+    return cfg, gpu, oracle
+
+
+def test_softcap_logits_and_topk_match_oracle(capped):
+    """gemma4_cuda/mod.rs:573-579: tanh(x / cap) * cap on every score handed back to the host."""
+    cfg, gpu, oracle = capped
+    prompt = syn.prompt_ids(cfg["vocab_size"], 10, seed=3)
+    worst, g_ids, o_ids, _ = run_both(gpu, oracle, prompt, 6, pkg.F32, page_tokens=4)
+    assert worst <= TOL_F32 and g_ids == o_ids
+    table = gpu.new_cache_table(8, kv_dtype=pkg.F32)
+    cache = oracle.new_cache(8)
+    tok = 3
+    for k, pen in [(4, 1.0), (16, 1.4)]:
+        got = gpu.decode_topk(tok, table, k, pen, True)
+        ids, scores = cache.decode_topk(tok, k, pen, True)
+        assert [g[0] for g in got] == ids.tolist()
+        np.testing.assert_allclose([g[1] for g in got], scores, atol=TOL_F32)
+        assert max(abs(g[1]) for g in got) < 0.75
+        tok = int(ids[0])
+
+
+@pytest.mark.parametrize("seed,top_k,top_p,penalty", [(1234, 8, 0.9, 1.3), (5, 32, 1.0, 1.0)])
+def test_device_sampled_loop_equals_host_sampling_with_softcap(capped, seed, top_k, top_p, penalty):
+    """The device sampler softcaps the candidate scores before the draw, like the host loop
+    (decode_topk -> softcap -> sample_topk_candidates): same tokens, same generator state."""
+    cfg, gpu, _ = capped
+    prompt = syn.prompt_ids(cfg["vocab_size"], 9, seed=4)
+    steps, temperature = 16, 0.7
+    gcfg = pkg.GenerationConfig(max_new_tokens=steps, temperature=temperature, top_k=top_k, top_p=top_p,
+                                repetition_penalty=penalty, eos_token_ids=[], seed=seed)
+    t_host = gpu.new_cache_table(40, kv_dtype=pkg.F32)
+    first = int(np.argmax(gpu.prefill_prompt(prompt, t_host)))
+    rnd = np.array([seed], dtype=np.uint64)
+    tok, host_ids = first, []
+    for _ in range(steps):
+        cand = gpu.decode_topk(tok, t_host, top_k, penalty, True)
+        tok = pkg.sample_topk_candidates(cand, gcfg, rnd)
+        host_ids.append(tok)
+    t_dev = gpu.new_cache_table(40, kv_dtype=pkg.F32)
+    gpu.prefill_prompt(prompt, t_dev)
+    dev_ids, state, _ = gpu.decode_sampled(first, t_dev, steps, top_k, temperature, top_p, penalty, [seed])
+    assert dev_ids.ravel().tolist() == host_ids
+    assert int(state[0]) == int(rnd[0])

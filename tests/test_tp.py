@@ -63,21 +63,18 @@ WORKER_CPU = textwrap.dedent("""
 """)
 
 
-def _torchrun(script, nproc, extra_env=None, timeout=600):
+def _torchrun(script, nproc, workdir, extra_env=None, timeout=600):
     env = dict(os.environ, OXG4_ROOT=ROOT, **(extra_env or {}))
-    path = os.path.join(ROOT, "tests", "_tp_worker_tmp.py")
+    path = os.path.join(str(workdir), "tp_worker.py")
     with open(path, "w") as f:
         f.write(script)
-    try:
-        return subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
-                               "--master-addr", "127.0.0.1", "--master-port", "29611", path],
-                              env=env, capture_output=True, text=True, timeout=timeout)
-    finally:
-        os.unlink(path)
+    return subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+                           "--master-addr", "127.0.0.1", "--master-port", "29611", path],
+                          env=env, capture_output=True, text=True, timeout=timeout)
 
 
-def test_shard_table_world_size_2_gloo():
-    r = _torchrun(WORKER_CPU, 2)
+def test_shard_table_world_size_2_gloo(tmp_path):
+    r = _torchrun(WORKER_CPU, 2, tmp_path)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     assert r.stdout.count("ok") == 2
 
