@@ -45,6 +45,8 @@ struct AttnArgs {
     const int32_t* page_table;   // [B, pages_per_seq]
     int pages_per_seq, page_tokens;
     const int32_t* cap;      // [B] ring capacity of this layer kind for each sequence
+    int window;              // a token sees the last `window` positions up to its own (sliding layers), INT_MAX otherwise
+    const int32_t* row_seq;  // [B] sequence (page table, ring) of every row, or null: row b is sequence b
     int n_splits, min_split;
     float* part;             // [B, Nkv, n_splits, G, D + 2]
     unsigned int* ticket;    // [B, Nkv]
@@ -136,13 +138,8 @@ template <typename KT> DEVINL float kv_widen(KT v);
 template <> DEVINL float kv_widen<float>(float v) { return v; }
 template <> DEVINL float kv_widen<uint16_t>(uint16_t v) { return __uint_as_float((uint32_t)v << 16); }
 
-// Block-wide barrier policies: the whole CTA, or the first 512 threads of a CTA whose remaining warp does
-// other work (the persistent decode kernel keeps one warp for TMA).
 struct BarCta {
     DEVINL void operator()() const { __syncthreads(); }
-};
-struct BarFirst512 {
-    DEVINL void operator()() const { asm volatile("bar.sync 1, 512;" ::: "memory"); }
 };
 
 // One CTA's share of a launch: split `s` of kv head `kvh` of sequence `b`, computed by the `nthreads`
@@ -192,8 +189,13 @@ DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, c
     // of the dependency wait.
     const bool active = a.tokens[b] != kInactiveToken;
     const int pos = a.pos[b];
-    const int cap = a.cap[b];
-    const int lo = max(0, pos + 1 - cap);
+    const int sb = a.row_seq ? a.row_seq[b] : b;
+    const int cap = a.cap[sb];
+    const int lo = max(0, pos + 1 - min(cap, a.window));
+    // The variant that merges through global memory (CL = false) serves the rows of a prompt chunk: K and V of
+    // every row, the current position included, are already in the cache (qkv_post_kernel appended the whole
+    // chunk first), so the CTA only norms its queries.
+    constexpr bool ext = !CL;
     const int n = pos - lo + 1;
     const int n_eff = min(a.n_splits, (n + a.min_split - 1) / a.min_split);
     const bool has_work = active && s < n_eff;
@@ -208,14 +210,14 @@ DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, c
     typedef KRaw<KT, EPT> Raw;
     const KT* kpool = (const KT*)a.kpool;
     const KT* vpool = (const KT*)a.vpool;
-    const int32_t* pt = a.page_table + (size_t)b * a.pages_per_seq;
+    const int32_t* pt = a.page_table + (size_t)sb * a.pages_per_seq;
     auto row_offset = [&](int p) -> size_t {
         const int slot = p % cap;
         return (((size_t)pt[slot / a.page_tokens] * a.Nkv + kvh) * a.page_tokens +
                 (slot % a.page_tokens)) * (size_t)D + lane * EPT;
     };
     auto issue = [&](int p, Raw& kr, Raw& vr) {            // loads only; the current token comes from shared memory
-        if (p < end && p != pos) {
+        if (p < end && (p != pos || ext)) {
             const size_t off = row_offset(p);
             kraw_load<KT, EPT>(kpool + off, kr);
             kraw_load<KT, EPT>(vpool + off, vr);
@@ -228,7 +230,7 @@ DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, c
     }
     if (has_work) {
         const int slot_cur = pos % cap;
-        cur_off = (((size_t)a.page_table[(size_t)b * a.pages_per_seq + slot_cur / a.page_tokens] * a.Nkv + kvh) *
+        cur_off = (((size_t)pt[slot_cur / a.page_tokens] * a.Nkv + kvh) *
                        a.page_tokens + (slot_cur % a.page_tokens)) * (size_t)D;
         // rotation factors of this position, one cosf or sinf per thread instead of 2 * D / 32 per lane
         for (int i = tid; i < D; i += nthreads) {
@@ -251,7 +253,7 @@ DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, c
         bar();                                      // the rotation factors are in shared memory
         // tasks 0..G-1: query heads (norm + rope); task G: key (norm + rope + append);
         // task G+1: value (unit norm + append). One warp per task.
-        const int n_tasks = owner ? G + 2 : G;
+        const int n_tasks = (owner && !ext) ? G + 2 : G;
         for (int task = warp; task < n_tasks; task += NW) {
             int col;
             if (task < G) col = (kvh * G + task) * D;
@@ -333,7 +335,7 @@ DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, c
             for (int q = 0; q < NP; ++q) {
                 const int pq = p0 + q * NW;
                 float kf[EPT];
-                if (pq == pos) {
+                if (pq == pos && !ext) {
 #pragma unroll
                     for (int e = 0; e < EPT; ++e) kf[e] = kcur[lane * EPT + e];
                 } else {
@@ -378,7 +380,7 @@ DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, c
                 const int pq = p0 + q * NW;
                 if (pq >= end) break;
                 float vf[EPT];
-                if (pq == pos) {
+                if (pq == pos && !ext) {
 #pragma unroll
                     for (int e = 0; e < EPT; ++e) vf[e] = vcur[lane * EPT + e];
                 } else {
@@ -549,10 +551,11 @@ DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, c
     stamp(a.ts, 3);
 }
 
-// CL = true: the splits of one (sequence, kv head) form a thread-block cluster (gridDim.x <= 16 CTAs);
-// partials stay in shared memory and are merged through distributed shared memory after one cluster
-// barrier. CL = false: partials go through global memory and the last CTA to arrive (atomic ticket)
-// merges them.
+// CL = true (decode steps): the splits of one (sequence, kv head) form a thread-block cluster (gridDim.x <= 16
+// CTAs); partials stay in shared memory and are merged through distributed shared memory after one cluster
+// barrier; the CTA that owns the current position also norms, rotates and appends its K and V.
+// CL = false (rows of a prompt chunk): K/V are in the cache already, partials go through global memory and the
+// last CTA to arrive (atomic ticket) merges them.
 template <typename KT, int D, int G, bool CL, bool DEEP = false>
 __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const AttnArgs a) {
     extern __shared__ __align__(16) float attn_sm[];

@@ -60,18 +60,30 @@ struct RowsNormArgs {
     PeerExchange px;         // px.tp > 1: `raw` is the local gather buffer; wait for every rank's push first
 };
 
+constexpr int kRowsMaxJ = 24;                 // values of a row held per thread: hidden <= 24 * 256 = 6144
+
 __global__ void __launch_bounds__(kRowsThreads) rows_norm_kernel(const RowsNormArgs a) {
     __shared__ float red[32];
     pdl_wait();
     pdl_launch();
     const int b = blockIdx.x, tid = threadIdx.x, H = a.H;
     const size_t ro = (size_t)b * H;
-    float r = 0.0f;
-    uint32_t tok = 0;
+    float hv[kRowsMaxJ];
     if (a.embed != nullptr) {
-        tok = a.tokens[b];
+        uint32_t tok = a.tokens[b];
         if (tok == kInactiveToken) tok = 0;
-    } else if (a.raw != nullptr) {
+#pragma unroll
+        for (int j = 0; j < kRowsMaxJ; ++j) {
+            const int i = tid + j * kRowsThreads;
+            hv[j] = i < H ? __uint_as_float((uint32_t)a.embed[(size_t)tok * H + i] << 16) * a.embed_scale : 0.0f;
+        }
+    } else if (a.raw == nullptr) {
+#pragma unroll
+        for (int j = 0; j < kRowsMaxJ; ++j) {
+            const int i = tid + j * kRowsThreads;
+            hv[j] = i < H ? a.h_in[ro + i] : 0.0f;
+        }
+    } else {
         if (a.px.tp > 1) {
             // wait (bounded) until every rank has published this exchange
             if (tid < a.px.tp) {
@@ -83,35 +95,47 @@ __global__ void __launch_bounds__(kRowsThreads) rows_norm_kernel(const RowsNormA
             }
             __syncthreads();
         }
+        // the row is read once: the pending projection output (its K-split partials added in split order) and the
+        // residual stream stay in registers between the two reductions
+        float t[kRowsMaxJ];
         float ss[1] = {0.0f};
-        for (int i = tid; i < H; i += kRowsThreads) {
-            float t = 0.0f;
-            for (int s = 0; s < a.raw_splits; ++s) t += __ldcg(a.raw + ((size_t)s * a.B + b) * H + i);
-            ss[0] += t * t;
+#pragma unroll
+        for (int j = 0; j < kRowsMaxJ; ++j) {
+            const int i = tid + j * kRowsThreads;
+            float v = 0.0f;
+            if (i < H) {
+                for (int s = 0; s < a.raw_splits; ++s) v += __ldcg(a.raw + ((size_t)s * a.B + b) * H + i);
+                hv[j] = a.h_in[ro + i];
+            } else {
+                hv[j] = 0.0f;
+            }
+            t[j] = v;
+            ss[0] += v * v;
         }
         block_sum<1>(ss, red);
-        r = 1.0f / sqrtf(ss[0] / (float)H + a.eps);
-    }
-    auto hidden = [&](int i) -> float {
-        if (a.embed != nullptr) return __uint_as_float((uint32_t)a.embed[(size_t)tok * H + i] << 16) * a.embed_scale;
-        float h = a.h_in[ro + i];
-        if (a.raw != nullptr) {
-            float t = 0.0f;
-            for (int s = 0; s < a.raw_splits; ++s) t += __ldcg(a.raw + ((size_t)s * a.B + b) * H + i);
-            h = (h + t * r * a.w_post[i]) * a.scalar;
+        const float r = 1.0f / sqrtf(ss[0] / (float)H + a.eps);
+#pragma unroll
+        for (int j = 0; j < kRowsMaxJ; ++j) {
+            const int i = tid + j * kRowsThreads;
+            if (i < H) hv[j] = (hv[j] + t[j] * r * a.w_post[i]) * a.scalar;
         }
-        return h;
-    };
+    }
     float ss2[1] = {0.0f};
-    for (int i = tid; i < H; i += kRowsThreads) {
-        const float h = hidden(i);
-        a.h_out[ro + i] = h;
-        ss2[0] += h * h;
+#pragma unroll
+    for (int j = 0; j < kRowsMaxJ; ++j) {
+        const int i = tid + j * kRowsThreads;
+        if (i < H) {
+            a.h_out[ro + i] = hv[j];
+            ss2[0] += hv[j] * hv[j];
+        }
     }
     block_sum<1>(ss2, red);
     const float r2 = 1.0f / sqrtf(ss2[0] / (float)H + a.eps);
-    for (int i = tid; i < H; i += kRowsThreads)
-        a.x[ro + i] = (uint16_t)f32_to_bf16_bits(a.h_out[ro + i] * r2 * a.w_norm[i]);
+#pragma unroll
+    for (int j = 0; j < kRowsMaxJ; ++j) {
+        const int i = tid + j * kRowsThreads;
+        if (i < H) a.x[ro + i] = (uint16_t)f32_to_bf16_bits(hv[j] * r2 * a.w_norm[i]);
+    }
 }
 
 // out[i] = sum_s part[s][i] in split order (tensor parallelism: one compact buffer goes through the

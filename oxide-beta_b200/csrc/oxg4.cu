@@ -20,12 +20,12 @@
 
 #include "../../include/oxg4.h"
 #include "attention.cuh"
+#include "attention_mma.cuh"
 #include "gemv.cuh"
 #include "gemv_mma.cuh"
 #include "sampling.cuh"
 #include "batch_ops.cuh"
 #include "tc_gemm.cuh"
-#include "decode_mega.cuh"
 #include "tp.h"
 
 using namespace oxg4;
@@ -99,12 +99,6 @@ struct oxg4_model {
     int num_sms = 148;
     bool use_pdl = true;
     bool far_prefetch = false;
-    // persistent decode kernel (one sequence, BF16 weights): geometry fixed by the model's shapes
-    bool mega_ok = false;
-    MegaLayer* mega_layers = nullptr;
-    int mega_R[4] = {1, 1, 1, 1}, mega_F[4] = {1, 1, 1, 1}, mega_stage_bytes = 0, mega_x_bytes = 0, mega_slot_floats = 0;
-    size_t mega_smem = 0;
-    int mega_pf_kb = 192;
     int pf_cap_kb = 128;          // KiB of its own weight block a CTA pulls into L2 before the dependency wait
     int pf_cap_gu_kb = -1, pf_cap_down_kb = -1;   // overrides for the gate/up and down projections (-1: pf_cap_kb)
     bool timeline = false;        // OXG4_TIMELINE: kernels stamp the global timer into the cache's buffer     // pull later kernels' weights into L2 during latency-bound kernels
@@ -380,96 +374,6 @@ static int32_t set_attn_attrs() {
     return OXG4_OK;
 }
 
-template <typename KT>
-static void (*pick_mega(int D, int G))(const MegaArgs) {
-#define PM(DD)                                                \
-    if (D == DD) {                                            \
-        if (G == 1) return decode_mega_kernel<KT, DD, 1>;     \
-        if (G == 2) return decode_mega_kernel<KT, DD, 2>;     \
-        if (G == 4) return decode_mega_kernel<KT, DD, 4>;     \
-        if (G == 8) return decode_mega_kernel<KT, DD, 8>;     \
-    }
-    PM(64) PM(128) PM(256)
-#undef PM
-    return nullptr;
-}
-
-// Geometry of the persistent decode kernel for this model, or mega_ok = false when a shape does not fit.
-static int32_t mega_setup(oxg4_model* m) {
-    m->mega_ok = false;
-    // opt-in while it is slower than the per-projection kernels on the workloads measured so far
-    if (m->es != 2 || m->tp != 1 || !getenv("OXG4_MEGA") || getenv("OXG4_DISABLE_MEGA")) return OXG4_OK;
-    const int H = m->H, D = m->D, L = m->cfg.num_hidden_layers;
-    auto fn16 = pick_mega<uint16_t>(D, m->G);
-    auto fn32 = pick_mega<float>(D, m->G);
-    if (!fn16 || !fn32) return OXG4_OK;
-    int coop = 0;
-    CK(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, m->device));
-    if (!coop) return OXG4_OK;
-    const int K[4] = {H, m->Nq * D, H, m->I};
-    if (H > kMegaMaxJ * kMegaConsumers) return OXG4_OK;
-    // shared memory: activations / attention scratch, the residual stream, one result slot per row (fraction),
-    // and what is left is cut into sixteen ring stages
-    int kmax = 0;
-    for (int k = 0; k < 4; ++k) kmax = std::max(kmax, K[k]);
-    const int attn_floats = m->G * D + 2 * D + 2 * kMegaConsumerWarps * m->G + kMegaConsumerWarps * m->G * D + m->G * (D + 2) + D;
-    int xb = std::max(kmax * 2, attn_floats * 4);
-    xb = (xb + 127) & ~127;
-    const int rows[4] = {m->p_qkv.N, H, m->I, H};
-    int slot_floats = 16;
-    for (int k = 0; k < 4; ++k)
-        slot_floats = std::max(slot_floats, ((rows[k] + m->num_sms - 1) / m->num_sms) * (k == 2 ? 2 : 1) * 8);   // F <= 8
-    cudaFuncAttributes fa;
-    CK(cudaFuncGetAttributes(&fa, (const void*)fn16));
-    const int budget = 227 * 1024 - (int)fa.sharedSizeBytes - 256;
-    const int fixed = xb + H * 4 + slot_floats * 4;
-    int stage_max = ((budget - fixed) / kMegaStages) & ~127;
-    if (const char* e = getenv("OXG4_MEGA_STAGE_KB")) stage_max = std::min(stage_max, std::max(1, atoi(e)) * 1024);
-    int stage = 0;
-    for (int k = 0; k < 4; ++k) {
-        // R whole rows per piece, each cut into nseg interleaved segments that become the 16 rows of the mma
-        // A operand; a row that does not fit a stage goes in F contiguous fractions (R = 1)
-        if (K[k] % 16 != 0) return OXG4_OK;
-        int R = 16, F = 1;
-        auto fits = [&](int r, int f) {
-            const int kf = K[k] / f;
-            return K[k] % f == 0 && kf % 16 == 0 && (kf / 16) % mega_nseg(r) == 0 && r * (kf * 2 + 16) <= stage_max;
-        };
-        while (R > 1 && !fits(R, 1)) R /= 2;
-        while (F < 8 && !fits(R, F)) F *= 2;
-        if (!fits(R, F)) return OXG4_OK;
-        m->mega_R[k] = R;
-        m->mega_F[k] = F;
-        stage = std::max(stage, R * (K[k] / F * 2 + 16));
-    }
-    stage = (stage + 127) & ~127;
-    if (const char* e = getenv("OXG4_MEGA_PF_KB")) m->mega_pf_kb = std::max(0, std::min(4096, atoi(e)));
-    m->mega_stage_bytes = stage;
-    m->mega_x_bytes = xb;
-    m->mega_slot_floats = slot_floats;
-    m->mega_smem = (size_t)kMegaStages * stage + fixed;
-    TRY(allow_big_smem(fn16));
-    TRY(allow_big_smem(fn32));
-    int occ = 0;
-    CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn16, kMegaThreads, m->mega_smem));
-    if (occ < 1) return OXG4_OK;
-    std::vector<MegaLayer> hl(L);
-    for (int l = 0; l < L; ++l) {
-        const LayerPlan& p = m->layers[l];
-        MegaLayer& g = hl[l];
-        g.wqkv = p.wqkv; g.wo = p.wo; g.wgate = p.wgate; g.wup = p.wup; g.wdown = p.wdown;
-        g.input_ln = p.input_ln; g.post_attn_ln = p.post_attn_ln; g.pre_ff_ln = p.pre_ff_ln;
-        g.post_ff_ln = p.post_ff_ln; g.q_norm = p.q_norm; g.k_norm = p.k_norm; g.inv_freq = p.inv_freq;
-        g.layer_scalar = p.layer_scalar;
-        g.sliding = p.sliding ? 1 : 0;
-        g.rotary_half = p.rotary_dim / 2;
-    }
-    CK(cudaMalloc(&m->mega_layers, sizeof(MegaLayer) * L));
-    CK(cudaMemcpy(m->mega_layers, hl.data(), sizeof(MegaLayer) * L, cudaMemcpyHostToDevice));
-    m->mega_ok = true;
-    return OXG4_OK;
-}
-
 extern "C" int32_t oxg4_model_finalize(oxg4_model* m) {
     if (!m) return fail(OXG4_INVALID_ARGUMENT, "null model");
     if (m->finalized) return OXG4_OK;
@@ -548,7 +452,6 @@ extern "C" int32_t oxg4_model_finalize(oxg4_model* m) {
     TRY((set_attn_attrs<uint16_t, 64>())); TRY((set_attn_attrs<uint16_t, 128>())); TRY((set_attn_attrs<uint16_t, 256>()));
     TRY((set_attn_attrs<float, 64>())); TRY((set_attn_attrs<float, 128>())); TRY((set_attn_attrs<float, 256>()));
     TRY(allow_big_smem(topk_stage2_kernel));
-    TRY(mega_setup(m));
     CK(cudaDeviceSynchronize());
     m->finalized = true;
     return OXG4_OK;
@@ -650,14 +553,24 @@ struct oxg4_cache {
     std::vector<void*> owned;                 // every device allocation, for destroy
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     unsigned long long* ts_buf = nullptr;     // [kMaxTimeline][4] optional device timeline
-    // tcgen05 path (eight or more sequences): BF16 activations, K-split partial outputs, error flag
-    bool use_mega = false;                    // one sequence, BF16 weights: the whole layer stack is one persistent kernel
-    MegaKv* mega_kv = nullptr;
-    MegaSync* mega_sync = nullptr;
-    int* mega_status = nullptr;               // pinned, mapped: the kernel writes it only when it gives up
-    int mega_splits_full = 1, mega_splits_slide = 1;
-    bool use_tc = false;
-    int s_qkv = 1, s_o = 1, s_gu = 1, s_down = 1;
+    // rows a pass over the layers may carry: the batch for a decode step, up to kPrefillRows prompt tokens for a chunk
+    int rows_cap = 0;
+    // prompt chunks: per-row metadata (token, position, sequence) and the attention groups, device + pinned host
+    uint32_t *pf_tok = nullptr, *h_pf_tok = nullptr;
+    int32_t *pf_pos = nullptr, *pf_seq = nullptr, *pf_grp_row0 = nullptr, *pf_grp_n = nullptr, *h_pf_meta = nullptr;
+    int32_t *dec_grp_row0 = nullptr, *dec_grp_n = nullptr;      // decode: one group per sequence
+    float *last_h = nullptr, *last_raw = nullptr;               // [B, H] residual stream / pending update of every sequence's last prompt token
+    uint16_t* last_x = nullptr;                                 // [B, H] tcgen05 path: its normed BF16 activations
+    // tensor-core attention (BF16 KV pages): query hi/lo tiles, per-warp partials, one tensor map per layer and pool
+    bool mma_attn = false;
+    uint16_t* q_hl = nullptr;
+    float* am_part = nullptr;
+    std::vector<CUtensorMap> kmap, vmap;
+    // tcgen05 path (decode with eight or more sequences, and every prompt chunk of a BF16 model): BF16
+    // activations, K-split partial outputs, error flag
+    bool use_tc = false, tc_ok = false;
+    int s_qkv = 1, s_o = 1, s_gu = 1, s_down = 1;              // K-splits for a decode step (B rows)
+    int ps_qkv = 1, ps_o = 1, ps_gu = 1, ps_down = 1;          // K-splits for a full prompt chunk
     uint16_t *x_h = nullptr, *x_a = nullptr, *x_i = nullptr;
     float *qkv_part = nullptr, *o_part = nullptr, *gu_part = nullptr, *down_part = nullptr;
     int* tc_err = nullptr;
@@ -681,21 +594,32 @@ static int32_t dalloc(oxg4_cache* c, T** p, size_t count, bool zero = true) {
     return OXG4_OK;
 }
 
+constexpr int kPrefillRows = 256;             // most prompt tokens one pass over the layers carries
+
 static int32_t tc_gemm_setup();
+static int32_t attn_mma_setup();
 static int tc_pick_splits(int tiles, int kblocks, int grid, int B, int n_total, int K);
+static int32_t encode_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 
 static int32_t cache_build(oxg4_cache* c) {
     oxg4_model* m = c->m;
     const int B = c->B, L = m->cfg.num_hidden_layers, H = m->H, D = m->D, PT = c->PT;
     const size_t kes = c->kv_dtype == OXG4_BF16 ? 2 : 4;
-    // cache.rs:58-62: sliding capacity = min(window, max_seq); global capacity = max_seq
+    // Ring capacities. The reference keeps min(window, max_seq) rows on sliding layers and max_seq on global
+    // ones (cache.rs:58-62) and lets the ring itself implement the window. Here a sliding ring keeps
+    // kPrefillRows - 1 more rows, because a prompt chunk appends all its K/V rows before any of its tokens
+    // attends (the earliest token of the chunk still needs the rows that the latest one would overwrite), and
+    // every capacity is rounded up to the 16-position tile of the tensor-core attention; the window is
+    // applied by the kernels (a token sees positions (pos - window, pos]), so the visible set is the reference's.
+    auto round_up = [](int v, int q) { return (v + q - 1) / q * q; };
     std::vector<int32_t> capf(B), caps(B);
-    int maxf = 0, maxs = 0;
+    int maxf = 0, maxs = 0, vis_s = 0;
     for (int b = 0; b < B; ++b) {
-        capf[b] = c->max_seq[b];
-        caps[b] = std::min(m->cfg.sliding_window, c->max_seq[b]);
+        capf[b] = round_up(c->max_seq[b], kAmTile);
+        caps[b] = round_up(std::min(m->cfg.sliding_window + kPrefillRows - 1, c->max_seq[b]), kAmTile);
         maxf = std::max(maxf, capf[b]);
         maxs = std::max(maxs, caps[b]);
+        vis_s = std::max(vis_s, std::min(m->cfg.sliding_window, c->max_seq[b]));
     }
     c->pps_full = (maxf + PT - 1) / PT;
     c->pps_slide = (maxs + PT - 1) / PT;
@@ -705,6 +629,7 @@ static int32_t cache_build(oxg4_cache* c) {
         for (int i = 0; i < (capf[b] + PT - 1) / PT; ++i) ptf[(size_t)b * c->pps_full + i] = pages_full++;
         for (int i = 0; i < (caps[b] + PT - 1) / PT; ++i) pts[(size_t)b * c->pps_slide + i] = pages_slide++;
     }
+    // a ring never spans a partial last page: slot -> page look-ups stay inside the sequence's own pages
     TRY(dalloc(c, &c->pt_full, ptf.size()));
     TRY(dalloc(c, &c->pt_slide, pts.size()));
     TRY(dalloc(c, &c->cap_full, B));
@@ -713,8 +638,11 @@ static int32_t cache_build(oxg4_cache* c) {
     CK(cudaMemcpy(c->pt_slide, pts.data(), pts.size() * 4, cudaMemcpyHostToDevice));
     CK(cudaMemcpy(c->cap_full, capf.data(), B * 4, cudaMemcpyHostToDevice));
     CK(cudaMemcpy(c->cap_slide, caps.data(), B * 4, cudaMemcpyHostToDevice));
+    c->mma_attn = c->kv_dtype == OXG4_BF16 && PT % kAmTile == 0 && getenv("OXG4_DISABLE_MMA_ATTN") == nullptr;
     c->kpool.resize(L);
     c->vpool.resize(L);
+    c->kmap.resize(L);
+    c->vmap.resize(L);
     for (int l = 0; l < L; ++l) {
         const int pages = m->layers[l].sliding ? pages_slide : pages_full;
         const size_t bytes = (size_t)pages * m->Nkv * PT * D * kes;
@@ -724,54 +652,46 @@ static int32_t cache_build(oxg4_cache* c) {
         c->kpool[l] = k;
         c->vpool[l] = v;
         c->kv_bytes += 2 * (int64_t)bytes;
+        if (c->mma_attn) {
+            // the pool as a [pages * kv_heads * page_tokens, head_dim] BF16 matrix; boxes of 64 elements x 16 rows
+            TRY(encode_bf16_2d(&c->kmap[l], k, (uint64_t)pages * m->Nkv * PT, (uint64_t)D, kAmTile));
+            TRY(encode_bf16_2d(&c->vmap[l], v, (uint64_t)pages * m->Nkv * PT, (uint64_t)D, kAmTile));
+        }
     }
-    // split-KV geometry: enough CTAs to fill the GPU a few times over at the longest context
+    // split-KV geometry of the one-row attention kernel: enough CTAs to fill the GPU a few times over at the longest context
     const int pairs = std::max(1, m->Nkv * B);
     const int want = std::max(1, (8 * m->num_sms + pairs - 1) / pairs);
     c->min_split = 16;
-    c->attn_cluster = getenv("OXG4_ATTN_TICKET") == nullptr;
+    c->attn_cluster = true;
     // clusters of 16 CTAs (non-portable size) only while one CTA per SM is enough for the whole step
     int cluster_max = 16;
     if (const char* e = getenv("OXG4_ATTN_CLUSTER_MAX")) cluster_max = std::max(1, std::min(16, atoi(e)));
-    const int cap_splits = c->attn_cluster ? (pairs * 16 <= m->num_sms ? cluster_max : std::min(cluster_max, 8)) : 64;
+    const int cap_splits = pairs * 16 <= m->num_sms ? cluster_max : std::min(cluster_max, 8);
     auto pow2_floor = [](int v) { int p = 1; while (p * 2 <= v) p *= 2; return p; };
     c->splits_full = std::max(1, std::min({want, cap_splits, (maxf + c->min_split - 1) / c->min_split}));
-    c->splits_slide = std::max(1, std::min({want, cap_splits, (maxs + c->min_split - 1) / c->min_split}));
+    c->splits_slide = std::max(1, std::min({want, cap_splits, (vis_s + c->min_split - 1) / c->min_split}));
     if (c->attn_cluster) {
         c->splits_full = pow2_floor(c->splits_full);
         c->splits_slide = pow2_floor(c->splits_slide);
     }
-    int smax = std::max(c->splits_full, c->splits_slide);
-    c->use_mega = m->mega_ok && B == 1;
-    if (c->use_mega) {
-        // attention inside the persistent kernel: (split, kv head) units over all CTAs, merged by ticket
-        const int per = std::max(1, m->num_sms / m->Nkv);
-        c->mega_splits_full = std::max(1, std::min(per, (maxf + c->min_split - 1) / c->min_split));
-        c->mega_splits_slide = std::max(1, std::min(per, (maxs + c->min_split - 1) / c->min_split));
-        smax = std::max({smax, c->mega_splits_full, c->mega_splits_slide});
-        std::vector<MegaKv> hk(L);
-        for (int l = 0; l < L; ++l) { hk[l].k = c->kpool[l]; hk[l].v = c->vpool[l]; }
-        TRY(dalloc(c, &c->mega_kv, (size_t)L));
-        CK(cudaMemcpy(c->mega_kv, hk.data(), sizeof(MegaKv) * L, cudaMemcpyHostToDevice));
-        TRY(dalloc(c, &c->mega_sync, 1));
-        CK(cudaHostAlloc(&c->mega_status, sizeof(int), cudaHostAllocMapped));
-        *c->mega_status = 0;
-    }
+    const int smax = std::max(c->splits_full, c->splits_slide);
+    const int R = c->rows_cap = std::max(B, kPrefillRows);
+    const int qw = m->Nq * D;
     TRY(dalloc(c, &c->tokens, B));
     TRY(dalloc(c, &c->pos, B));
     TRY(dalloc(c, &c->seen, (size_t)B * m->V));
     TRY(dalloc(c, &c->ctl, 1));
     TRY(dalloc(c, &c->rng, B));
-    TRY(dalloc(c, &c->hA, (size_t)B * H));
-    TRY(dalloc(c, &c->hB, (size_t)B * H));
-    TRY(dalloc(c, &c->qkv_raw, (size_t)B * m->p_qkv.N));
-    TRY(dalloc(c, &c->attn_out, (size_t)B * m->Nq * D));
-    TRY(dalloc(c, &c->o_raw, (size_t)B * H));
-    TRY(dalloc(c, &c->gu_raw, (size_t)B * m->I));
-    TRY(dalloc(c, &c->down_raw, (size_t)B * H));
+    TRY(dalloc(c, &c->hA, (size_t)R * H));
+    TRY(dalloc(c, &c->hB, (size_t)R * H));
+    TRY(dalloc(c, &c->qkv_raw, (size_t)R * m->p_qkv.N));
+    TRY(dalloc(c, &c->attn_out, (size_t)R * qw));
+    TRY(dalloc(c, &c->o_raw, (size_t)R * H));
+    TRY(dalloc(c, &c->gu_raw, (size_t)R * m->I));
+    TRY(dalloc(c, &c->down_raw, (size_t)R * H));
     TRY(dalloc(c, &c->logits, (size_t)B * m->V));
-    TRY(dalloc(c, &c->attn_part, (size_t)B * m->Nkv * smax * m->G * (D + 2)));
-    TRY(dalloc(c, &c->attn_ticket, (size_t)B * m->Nkv));
+    TRY(dalloc(c, &c->attn_part, (size_t)R * m->Nkv * smax * m->G * (D + 2)));
+    TRY(dalloc(c, &c->attn_ticket, (size_t)R * m->Nkv));
     TRY(dalloc(c, &c->lm_ticket, (size_t)B + 1));
     TRY(dalloc(c, &c->blk_best, (size_t)B * m->num_sms));
     const int chunks = (m->V + kTopkChunk - 1) / kTopkChunk;
@@ -783,26 +703,61 @@ static int32_t cache_build(oxg4_cache* c) {
     TRY(dalloc(c, &c->topk_ids, (size_t)B * 64));
     TRY(dalloc(c, &c->topk_scores, (size_t)B * 64));
     if (m->timeline) TRY(dalloc(c, &c->ts_buf, (size_t)kMaxTimeline * 4));
-    c->use_tc = m->es == 2 && B >= 8 && B <= 64 && getenv("OXG4_DISABLE_TCGEN05") == nullptr;
-    if (c->use_tc) {
+    // prompt chunks
+    TRY(dalloc(c, &c->pf_tok, kPrefillRows));
+    TRY(dalloc(c, &c->pf_pos, kPrefillRows));
+    TRY(dalloc(c, &c->pf_seq, kPrefillRows));
+    TRY(dalloc(c, &c->pf_grp_row0, kAmMaxGroups));
+    TRY(dalloc(c, &c->pf_grp_n, kAmMaxGroups));
+    TRY(dalloc(c, &c->last_h, (size_t)B * H));
+    TRY(dalloc(c, &c->last_raw, (size_t)B * H));
+    TRY(dalloc(c, &c->last_x, (size_t)B * H));
+    CK(cudaMallocHost(&c->h_pf_tok, sizeof(uint32_t) * kPrefillRows));
+    CK(cudaMallocHost(&c->h_pf_meta, sizeof(int32_t) * (2 * kPrefillRows + 2 * kAmMaxGroups)));
+    {
+        std::vector<int32_t> r0(B), ones(B, 1);
+        for (int b = 0; b < B; ++b) r0[b] = b;
+        TRY(dalloc(c, &c->dec_grp_row0, B));
+        TRY(dalloc(c, &c->dec_grp_n, B));
+        CK(cudaMemcpy(c->dec_grp_row0, r0.data(), B * 4, cudaMemcpyHostToDevice));
+        CK(cudaMemcpy(c->dec_grp_n, ones.data(), B * 4, cudaMemcpyHostToDevice));
+    }
+    TRY(dalloc(c, &c->tc_err, 1));
+    if (c->mma_attn) {
+        TRY(attn_mma_setup());
+        TRY(dalloc(c, &c->q_hl, (size_t)R * m->Nq * 2 * D));
+        const int warps = m->num_sms * 4;                       // upper bound of the consumer warps of a launch
+        TRY(dalloc(c, &c->am_part, ((size_t)std::min(R, kAmMaxGroups) * m->Nkv + warps) * kAmRows * (D + 2)));
+    }
+    c->tc_ok = m->es == 2 && getenv("OXG4_DISABLE_TCGEN05") == nullptr;
+    c->use_tc = c->tc_ok && B >= 8 && B <= 64;
+    if (c->tc_ok) {
         TRY(tc_gemm_setup());
         const int sms = m->num_sms;
         auto tiles = [](int n) { return (n + kTcTileM - 1) / kTcTileM; };
         auto kbs = [](int k) { return (k + kTcTileK - 1) / kTcTileK; };
-        const int nqkv = m->p_qkv.N, qw = m->Nq * D;
-        c->s_qkv = tc_pick_splits(tiles(nqkv), kbs(H), sms, B, nqkv, H);
-        c->s_o = tc_pick_splits(tiles(H), kbs(qw), sms, B, H, qw);
-        c->s_gu = tc_pick_splits(2 * tiles(m->I), kbs(H), sms, B, 2 * m->I, H);
-        c->s_down = tc_pick_splits(tiles(H), kbs(m->I), sms, B, H, m->I);
-        TRY(dalloc(c, &c->x_h, (size_t)B * H));
-        TRY(dalloc(c, &c->x_a, (size_t)B * qw));
-        TRY(dalloc(c, &c->x_i, (size_t)B * m->I));
-        TRY(dalloc(c, &c->qkv_part, (size_t)c->s_qkv * B * nqkv));
-        TRY(dalloc(c, &c->o_part, (size_t)c->s_o * B * H));
-        TRY(dalloc(c, &c->gu_part, (size_t)c->s_gu * B * 2 * m->I));
-        TRY(dalloc(c, &c->down_part, (size_t)c->s_down * B * H));
-        TRY(dalloc(c, &c->tc_err, 1));
-        if (m->tp > 1) {
+        const int nqkv = m->p_qkv.N;
+        const int Bd = std::min(B, 64);
+        c->s_qkv = tc_pick_splits(tiles(nqkv), kbs(H), sms, Bd, nqkv, H);
+        c->s_o = tc_pick_splits(tiles(H), kbs(qw), sms, Bd, H, qw);
+        c->s_gu = tc_pick_splits(2 * tiles(m->I), kbs(H), sms, Bd, 2 * m->I, H);
+        c->s_down = tc_pick_splits(tiles(H), kbs(m->I), sms, Bd, H, m->I);
+        // a full chunk has kPrefillRows / 64 row blocks per weight tile: far more units than SMs, so K-splits
+        // only where a projection has very few tiles
+        const int tb = kPrefillRows / 64;
+        c->ps_qkv = tc_pick_splits(tiles(nqkv) * tb, kbs(H), sms, kPrefillRows, nqkv, H);
+        c->ps_o = tc_pick_splits(tiles(H) * tb, kbs(qw), sms, kPrefillRows, H, qw);
+        c->ps_gu = tc_pick_splits(2 * tiles(m->I) * tb, kbs(H), sms, kPrefillRows, 2 * m->I, H);
+        c->ps_down = tc_pick_splits(tiles(H) * tb, kbs(m->I), sms, kPrefillRows, H, m->I);
+        auto rows_splits = [&](int sd, int sp) { return (size_t)std::max(sd * B, sp * kPrefillRows); };
+        TRY(dalloc(c, &c->x_h, (size_t)R * H));
+        TRY(dalloc(c, &c->x_a, (size_t)R * qw));
+        TRY(dalloc(c, &c->x_i, (size_t)R * m->I));
+        TRY(dalloc(c, &c->qkv_part, rows_splits(c->s_qkv, c->ps_qkv) * nqkv));
+        TRY(dalloc(c, &c->o_part, rows_splits(c->s_o, c->ps_o) * H));
+        TRY(dalloc(c, &c->gu_part, rows_splits(c->s_gu, c->ps_gu) * 2 * m->I));
+        TRY(dalloc(c, &c->down_part, rows_splits(c->s_down, c->ps_down) * H));
+        if (m->tp > 1 && c->use_tc) {
             const size_t bytes = sizeof(float) * 2 * (size_t)m->tp * B * H + sizeof(unsigned int) * 2 * kMaxTp;
             CK(cudaMalloc(&c->px_block, bytes));          // own allocation: its IPC handle is exported
             CK(cudaMemset(c->px_block, 0, bytes));
@@ -830,9 +785,10 @@ extern "C" void oxg4_cache_destroy(oxg4_cache* c) {
     for (int r = 0; r < kMaxTp; ++r)
         if (c->px_peer_base[r] && c->px_peer_base[r] != c->px_block) cudaIpcCloseMemHandle(c->px_peer_base[r]);
     if (c->px_block) cudaFree(c->px_block);
-    if (c->mega_status) cudaFreeHost(c->mega_status);
     for (void* p : c->owned) cudaFree(p);
     if (c->h_tokens) cudaFreeHost(c->h_tokens);
+    if (c->h_pf_tok) cudaFreeHost(c->h_pf_tok);
+    if (c->h_pf_meta) cudaFreeHost(c->h_pf_meta);
     if (c->h_ctl) cudaFreeHost(c->h_ctl);
     if (c->h_ids) cudaFreeHost(c->h_ids);
     if (c->h_scores) cudaFreeHost(c->h_scores);
@@ -998,7 +954,8 @@ static int tc_pick_splits(int tiles, int kblocks, int grid, int B, int n_total, 
 // out[S, B, n_mats * N] = per-split partials of x[B, K] . W_m[N, K]^T on device pointers (BF16 in, f32 out).
 static int32_t tc_gemm_launch(const void* w_dev, const void* w1_dev, const void* x_dev, int N, int K, int B, int S,
                               float* out_dev, int ld, int col0, int* err_dev, int num_sms, cudaStream_t st, bool pdl) {
-    if (B < 1 || B > 64 || K % 8 != 0) return fail(OXG4_INVALID_SHAPE, "tcgen05 projection: 1..64 rows and K %% 8 == 0 required");
+    if (B < 1 || B > kPrefillRows || K % 8 != 0)
+        return fail(OXG4_INVALID_SHAPE, "tcgen05 projection: 1..%d rows and K %% 8 == 0 required", kPrefillRows);
     const int bn = B <= 16 ? 16 : (B <= 32 ? 32 : 64);
     CUtensorMap mw, mw1, mx;
     TRY(encode_bf16_2d(&mw, w_dev, (uint64_t)N, (uint64_t)K, kTcTileM));
@@ -1009,12 +966,13 @@ static int32_t tc_gemm_launch(const void* w_dev, const void* w1_dev, const void*
     a.N = N; a.K = K; a.B = B;
     a.n_mats = w1_dev ? 2 : 1;
     a.S = S;
+    a.TB = (B + bn - 1) / bn;
     a.kb_per_split = (kblocks + S - 1) / S;
     a.out = out_dev;
     a.ld = ld;
     a.col0 = col0;
     a.err = err_dev;
-    const int units = ((N + kTcTileM - 1) / kTcTileM) * a.n_mats * S;
+    const int units = ((N + kTcTileM - 1) / kTcTileM) * a.n_mats * S * a.TB;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(std::min(units, num_sms));
     cfg.blockDim = dim3(kTcThreads);
@@ -1106,22 +1064,15 @@ struct Launcher {
     }
 
     // tcgen05 batched projection (csrc/tc_gemm.cuh): partials [S, B, ld] of x . W^T
-    void tc(const char* kind, oxg4_cache* c, const void* w0, const void* w1, const uint16_t* x, int N, int K, int S,
-            float* out, int ld, int col0) {
+    void tc(const char* kind, oxg4_cache* c, int rows, const void* w0, const void* w1, const uint16_t* x, int N, int K,
+            int S, float* out, int ld, int col0) {
         if (status != OXG4_OK) return;
-        cudaEvent_t e0 = nullptr, e1 = nullptr;
-        if (m->profiling) {
-            cudaEventCreate(&e0);
-            cudaEventCreate(&e1);
-            cudaEventRecord(e0, m->stream);
-        }
-        status = tc_gemm_launch(w0, w1, x, N, K, c->B, S, out, ld, col0, c->tc_err, m->num_sms, m->stream,
+        cudaEvent_t e0, e1;
+        prof_begin(e0, e1);
+        status = tc_gemm_launch(w0, w1, x, N, K, rows, S, out, ld, col0, c->tc_err, m->num_sms, m->stream,
                                 m->use_pdl && !m->profiling);
         if (status != OXG4_OK) return;
-        if (m->profiling) {
-            cudaEventRecord(e1, m->stream);
-            m->prof_events.push_back({kind, {e0, e1}});
-        }
+        prof_end(kind, e0, e1);
         ++kernels;
     }
 
@@ -1187,9 +1138,10 @@ static void (*pick_mma(int pro, int epi))(const GemvArgs) {
     return nullptr;
 }
 
-static void launch_gemv(Launcher& ln, const char* kind, oxg4_cache* c, GemvArgs a, const GemvPlan& p, int pro, int epi) {
+static void launch_gemv(Launcher& ln, const char* kind, oxg4_cache* c, int rows, GemvArgs a, const GemvPlan& p, int pro,
+                        int epi) {
     oxg4_model* m = c->m;
-    const int B = c->B;
+    const int B = rows;
     a.N = p.N;
     a.K = p.K;
     a.cpr = p.cpr;
@@ -1251,121 +1203,171 @@ static void (*pick_attn(int D, int G, bool cl, bool deep))(const AttnArgs) {
     return nullptr;
 }
 
+typedef void (*AttnMmaFn)(const CUtensorMap, const CUtensorMap, const AttnMmaArgs);
+typedef void (*AttnMergeFn)(const AttnMmaArgs);
+static void pick_attn_mma(int D, int G, AttnMmaFn* fn, AttnMergeFn* merge, size_t* smem, int* ncw) {
+    *fn = nullptr;
+#define PM1(DD, GG)                                            \
+    if (D == DD && G == GG) {                                  \
+        *fn = attn_mma_kernel<DD, GG>;                         \
+        *merge = attn_merge_kernel<DD, GG>;                    \
+        *smem = attn_mma_smem_bytes<DD>();                     \
+        *ncw = AmGeom<DD>::NCW;                                \
+    }
+#define PM(DD) PM1(DD, 1) PM1(DD, 2) PM1(DD, 4) PM1(DD, 8)
+    PM(64) PM(128) PM(256)
+#undef PM
+#undef PM1
+}
+
+static int32_t attn_mma_setup() {
+#define SM1(DD, GG) TRY(allow_big_smem(attn_mma_kernel<DD, GG>));
+#define SM(DD) SM1(DD, 1) SM1(DD, 2) SM1(DD, 4) SM1(DD, 8)
+    SM(64) SM(128) SM(256)
+#undef SM
+#undef SM1
+    return OXG4_OK;
+}
+
+// The rows one pass over the layers carries: the sequences of a decode step, or up to kPrefillRows prompt
+// tokens (a chunk), each with its token id, absolute position and, for a chunk, the sequence it belongs to.
+struct RowSet {
+    int R = 0;
+    const uint32_t* tok = nullptr;       // device [R]; kInactiveToken rows sit a decode step out
+    const int32_t* pos = nullptr;        // device [R]
+    const int32_t* seq = nullptr;        // device [R], or null: row r is sequence r
+    bool chunk = false;                  // prompt chunk: all K/V rows are appended before any token attends
+    const int32_t* grp_row0 = nullptr;   // attention groups (consecutive tokens of one sequence)
+    const int32_t* grp_n = nullptr;
+    int NG = 0, part_rows = 0;
+};
+
 // Launches every kernel of one step on the model's stream (eagerly or under stream capture).
 struct TraceCtx {
     const float* inject_dev;   // [L][B][H] layer inputs to force, or null
     float* trace_dev;          // [L+1][B][H] receives every layer's input and the final hidden state
 };
 
-static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* n_kernels,
-                        const TraceCtx* tr = nullptr) {
+// q/k norm + RoPE + v norm + KV append + attention of layer l for the rows of `rs` (decode.rs:99-157,
+// 176-325). qkv: [qkv_splits, R, qkv_n] projection output; the result goes to c->attn_out (+ BF16 copy).
+static void launch_attention(Launcher& ln, oxg4_cache* c, const RowSet& rs, int l, const float* qkv, int qkv_splits,
+                             uint16_t* out_bf16, bool many_rows) {
     oxg4_model* m = c->m;
-    Launcher ln{m};
-    ln.ts_base = c->ts_buf;
-    const int B = c->B, L = m->cfg.num_hidden_layers, H = m->H, D = m->D;
-    // Sums over peer memory only in steps whose last exchange is consumed (the closing norm before the
-    // LM head): a prompt-ingestion step skips that norm, so it takes the NCCL all-reduce instead and the
-    // single exchange buffer per kind is never pushed into while a peer may still read it.
-    const bool peer = c->peer_ready && kind != STEP_PREFILL;
-    ln.go("step_begin", step_begin_kernel, dim3(1), dim3(128), 0, B, m->V,
-          (const uint32_t*)c->tokens, c->seen, (const StepCtl*)c->ctl);
-    // q/k norm + RoPE + v norm + KV append + attention (decode.rs:99-157)
-    auto launch_attn = [&](int l, const float* qkv, int qkv_splits, uint16_t* out_bf16) {
-        const LayerPlan& p = m->layers[l];
-        AttnArgs a{};
-        a.qkv = qkv;
-        a.qkv_splits = qkv_splits;
-        a.out_bf16 = out_bf16;
-        a.qkv_n = m->p_qkv.N;
-        a.B = B;
-        a.Nq = m->Nq;
-        a.Nkv = m->Nkv;
-        a.q_norm = p.q_norm;
-        a.k_norm = p.k_norm;
-        a.inv_freq = p.inv_freq;
-        a.rotary_half = p.rotary_dim / 2;
-        a.eps = m->cfg.rms_norm_eps;
-        a.pos = c->pos;
-        a.tokens = c->tokens;
-        a.kpool = c->kpool[l];
-        a.vpool = c->vpool[l];
-        a.page_table = p.sliding ? c->pt_slide : c->pt_full;
-        a.pages_per_seq = p.sliding ? c->pps_slide : c->pps_full;
-        a.page_tokens = c->PT;
-        a.cap = p.sliding ? c->cap_slide : c->cap_full;
-        a.n_splits = p.sliding ? c->splits_slide : c->splits_full;
-        a.min_split = c->min_split;
-        a.part = c->attn_part;
-        a.ticket = c->attn_ticket;
-        a.out = c->attn_out;
-        if (m->far_prefetch) {
-            a.pf_ptr = p.wup;
-            a.pf_bytes = (unsigned long long)m->I * H * m->es;
-        }
-        a.ts = ln.ts();
-        a.ts_mid = ln.ts_base ? ln.ts_base + 4 * (size_t)(kMaxTimeline - 1 - l) : nullptr;   // extra stamps, from the end of the buffer
-        const bool cl = c->attn_cluster && a.n_splits <= 16;
-        // few CTAs (one sequence): 16 warps each to cut latency; many CTAs: 4 warps each so that several
-        // fit on an SM (the kernel needs ~90 registers per thread)
-        const int aw = (a.n_splits * m->Nkv * B <= m->num_sms) ? kAttnWarps : 4;
-        // more K/V rows in flight per warp when latency is all that counts (with more than two query heads
-        // per kv head the extra rows would spill registers)
-        const bool deep = cl && aw == kAttnWarps && m->G <= 2;
-        auto fn = c->kv_dtype == OXG4_BF16 ? pick_attn<uint16_t>(D, m->G, cl, deep) : pick_attn<float>(D, m->G, cl, deep);
-        const size_t smem = sizeof(float) * (size_t)(m->G * D + 2 * D + 2 * aw * m->G + aw * m->G * D + m->G * (D + 2) + D);
-        ln.cluster_x = cl ? a.n_splits : 0;
-        ln.go("attn", fn, dim3(a.n_splits, m->Nkv, B), dim3(aw * 32), smem, a);
-        ln.cluster_x = 0;
-    };
-    const bool mega = c->use_mega && tr == nullptr;
-    if (mega) {
-        // ---- one sequence, BF16 weights: every layer in one persistent cooperative kernel ----
-        MegaArgs g{};
-        g.layers = m->mega_layers;
-        g.kv = c->mega_kv;
-        g.L = L; g.H = H; g.I = m->I; g.Nq = m->Nq; g.Nkv = m->Nkv; g.qkv_n = m->p_qkv.N;
-        for (int k = 0; k < 4; ++k) { g.R[k] = m->mega_R[k]; g.F[k] = m->mega_F[k]; }
-        g.stage_bytes = m->mega_stage_bytes;
-        g.pf_kb = m->mega_pf_kb;
-        g.x_bytes = m->mega_x_bytes;
-        g.slot_floats = m->mega_slot_floats;
-        g.embed = (const uint16_t*)m->embed;
-        g.tokens = c->tokens;
-        g.embed_scale = sqrtf((float)H);
-        g.eps = m->cfg.rms_norm_eps;
-        g.qkv_raw = c->qkv_raw; g.attn_out = c->attn_out; g.o_raw = c->o_raw; g.gu_raw = c->gu_raw;
-        g.down_raw = c->down_raw; g.h_out = c->hA;
-        g.pos = c->pos;
-        g.pt_full = c->pt_full; g.pt_slide = c->pt_slide; g.cap_full = c->cap_full; g.cap_slide = c->cap_slide;
-        g.pps_full = c->pps_full; g.pps_slide = c->pps_slide;
-        g.page_tokens = c->PT;
-        g.splits_full = c->mega_splits_full; g.splits_slide = c->mega_splits_slide;
-        g.min_split = c->min_split;
-        g.part = c->attn_part;
-        g.ticket = c->attn_ticket;
-        g.sync = c->mega_sync;
-        g.status = c->mega_status;
-        g.ts = (ln.ts() && 19 * L + 2 + 4 * (ln.kernels + 4) <= kMaxTimeline * 4) ? ln.ts() : nullptr;
-        if (ln.status == OXG4_OK && cudaMemsetAsync(c->mega_sync, 0, sizeof(MegaSync), m->stream) != cudaSuccess)
-            ln.status = fail(OXG4_CUDA, "Gemma 4 CUDA error: cudaMemsetAsync failed");
-        auto fn = c->kv_dtype == OXG4_BF16 ? pick_mega<uint16_t>(D, m->G) : pick_mega<float>(D, m->G);
-        ln.coop = true;
-        ln.go("mega", fn, dim3(m->num_sms), dim3(kMegaThreads), m->mega_smem, g);
-        ln.coop = false;
+    const LayerPlan& p = m->layers[l];
+    const int D = m->D, R = rs.R;
+    const int32_t* page_table = p.sliding ? c->pt_slide : c->pt_full;
+    const int pps = p.sliding ? c->pps_slide : c->pps_full;
+    const int32_t* cap = p.sliding ? c->cap_slide : c->cap_full;
+    const int window = p.sliding ? m->cfg.sliding_window : 0x7fffffff;
+    const bool use_mma = c->mma_attn && (many_rows || rs.chunk);
+    if (use_mma || rs.chunk) {
+        // norms, RoPE and the K/V append of every row first (a chunk's later tokens are visible to none of its earlier ones
+        // only through the causal mask, so all rows may be in the cache before attention starts)
+        QkvPostArgs q{};
+        q.qkv = qkv; q.qkv_n = m->p_qkv.N; q.splits = qkv_splits; q.R = R; q.Nq = m->Nq; q.Nkv = m->Nkv;
+        q.q_norm = p.q_norm; q.k_norm = p.k_norm; q.inv_freq = p.inv_freq; q.rotary_half = p.rotary_dim / 2;
+        q.eps = m->cfg.rms_norm_eps;
+        q.row_pos = rs.pos; q.row_seq = rs.seq; q.row_tok = rs.tok;
+        q.kpool = c->kpool[l]; q.vpool = c->vpool[l];
+        q.page_table = page_table; q.pages_per_seq = pps; q.page_tokens = c->PT; q.cap = cap;
+        q.q_hl = use_mma ? c->q_hl : nullptr;
+        const int per_row = use_mma ? m->Nq + 2 * m->Nkv : 2 * m->Nkv;
+        void (*fn)(const QkvPostArgs) = nullptr;
+        if (c->kv_dtype == OXG4_BF16) fn = D == 64 ? qkv_post_kernel<uint16_t, 64> : D == 128 ? qkv_post_kernel<uint16_t, 128> : qkv_post_kernel<uint16_t, 256>;
+        else fn = D == 64 ? qkv_post_kernel<float, 64> : D == 128 ? qkv_post_kernel<float, 128> : qkv_post_kernel<float, 256>;
+        ln.go("qkv_post", fn, dim3((R * per_row + 3) / 4), dim3(128), 0, q);
     }
-    for (int l = 0; l < L && !mega; ++l) {
+    if (use_mma) {
+        AttnMmaArgs a{};
+        a.q_hl = c->q_hl; a.Nq = m->Nq; a.Nkv = m->Nkv; a.NG = rs.NG;
+        a.grp_row0 = rs.grp_row0; a.grp_n = rs.grp_n;
+        a.row_pos = rs.pos; a.row_seq = rs.seq; a.row_tok = rs.tok;
+        a.page_table = page_table; a.pages_per_seq = pps; a.page_tokens = c->PT; a.cap = cap;
+        a.window = window;
+        a.part_rows = rs.part_rows;
+        a.part = c->am_part;
+        a.err = c->tc_err;
+        a.out = c->attn_out;
+        a.out_bf16 = out_bf16;
+        AttnMmaFn fn;
+        AttnMergeFn merge;
+        size_t smem;
+        int ncw;
+        pick_attn_mma(D, m->G, &fn, &merge, &smem, &ncw);
+        a.total_warps = m->num_sms * ncw;
+        ln.go("attn", fn, dim3(m->num_sms), dim3((ncw + 1) * 32), smem, c->kmap[l], c->vmap[l], a);
+        ln.go("attn_merge", merge, dim3(rs.NG * m->Nkv), dim3(128), 0, a);
+        return;
+    }
+    AttnArgs a{};
+    a.qkv = qkv;
+    a.qkv_splits = qkv_splits;
+    a.out_bf16 = out_bf16;
+    a.qkv_n = m->p_qkv.N;
+    a.B = R;
+    a.Nq = m->Nq;
+    a.Nkv = m->Nkv;
+    a.q_norm = p.q_norm;
+    a.k_norm = p.k_norm;
+    a.inv_freq = p.inv_freq;
+    a.rotary_half = p.rotary_dim / 2;
+    a.eps = m->cfg.rms_norm_eps;
+    a.pos = rs.pos;
+    a.tokens = rs.tok;
+    a.row_seq = rs.seq;
+    a.window = window;
+    a.kpool = c->kpool[l];
+    a.vpool = c->vpool[l];
+    a.page_table = page_table;
+    a.pages_per_seq = pps;
+    a.page_tokens = c->PT;
+    a.cap = cap;
+    a.n_splits = p.sliding ? c->splits_slide : c->splits_full;
+    a.min_split = c->min_split;
+    a.part = c->attn_part;
+    a.ticket = c->attn_ticket;
+    a.out = c->attn_out;
+    if (m->far_prefetch && !rs.chunk) {
+        a.pf_ptr = p.wup;
+        a.pf_bytes = (unsigned long long)m->I * m->H * m->es;
+    }
+    a.ts = ln.ts();
+    a.ts_mid = ln.ts_base ? ln.ts_base + 4 * (size_t)(kMaxTimeline - 1 - l) : nullptr;   // extra stamps, from the end of the buffer
+    const bool cl = !rs.chunk;                   // decode: cluster merge; chunk rows: K/V already appended, ticket merge
+    // few CTAs (one sequence): 16 warps each to cut latency; many CTAs: 4 warps each so that several
+    // fit on an SM (the kernel needs ~90 registers per thread)
+    const int aw = (a.n_splits * m->Nkv * R <= m->num_sms) ? kAttnWarps : 4;
+    // more K/V rows in flight per warp when latency is all that counts (with more than two query heads
+    // per kv head the extra rows would spill registers)
+    const bool deep = cl && aw == kAttnWarps && m->G <= 2;
+    auto fn = c->kv_dtype == OXG4_BF16 ? pick_attn<uint16_t>(D, m->G, cl, deep) : pick_attn<float>(D, m->G, cl, deep);
+    const size_t smem = sizeof(float) * (size_t)(m->G * D + 2 * D + 2 * aw * m->G + aw * m->G * D + m->G * (D + 2) + D);
+    ln.cluster_x = cl ? a.n_splits : 0;
+    ln.go("attn", fn, dim3(a.n_splits, m->Nkv, R), dim3(aw * 32), smem, a);
+    ln.cluster_x = 0;
+}
+
+// All layers for the rows of `rs`. On return the last layer's residual update is still pending:
+// tcgen05 path: c->hA (+ the partials of the down projection), small-batch path: c->hA + c->down_raw.
+static void run_layers(oxg4_cache* c, Launcher& ln, const RowSet& rs, bool use_tc, bool peer, bool last_layer_prefetch,
+                       const TraceCtx* tr) {
+    oxg4_model* m = c->m;
+    const int R = rs.R, L = m->cfg.num_hidden_layers, H = m->H, D = m->D;
+    const int s_qkv = rs.chunk ? c->ps_qkv : c->s_qkv, s_o = rs.chunk ? c->ps_o : c->s_o;
+    const int s_gu = rs.chunk ? c->ps_gu : c->s_gu, s_down = rs.chunk ? c->ps_down : c->s_down;
+    for (int l = 0; l < L; ++l) {
         const LayerPlan& p = m->layers[l];
-        if (c->use_tc) {
-            // ---- eight or more sequences: tcgen05 projections fed by TMA, per-row kernels around them ----
+        if (use_tc) {
+            // ---- many rows: tcgen05 projections fed by TMA, per-row kernels around them ----
             const int nqkv = m->p_qkv.N, qw = m->Nq * D;
             auto copy_trace_tc = [&]() {
                 if (tr && ln.status == OXG4_OK &&
-                    cudaMemcpyAsync(tr->trace_dev + (size_t)l * B * H, c->hB, sizeof(float) * B * H,
+                    cudaMemcpyAsync(tr->trace_dev + (size_t)l * R * H, c->hB, sizeof(float) * R * H,
                                     cudaMemcpyDeviceToDevice, m->stream) != cudaSuccess)
                     ln.status = fail(OXG4_CUDA, "Gemma 4 CUDA error: trace copy failed");
             };
             RowsNormArgs n{};
-            n.B = B; n.H = H;
+            n.B = R; n.H = H;
             n.h_in = c->hA; n.h_out = c->hB;
             n.w_norm = p.input_ln;
             n.scalar = 1.0f;
@@ -1373,55 +1375,55 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
             n.x = c->x_h;
             if (l == 0) {
                 n.embed = (const uint16_t*)m->embed;
-                n.tokens = c->tokens;
+                n.tokens = rs.tok;
                 n.embed_scale = sqrtf((float)H);
             } else {
                 n.raw = m->tp > 1 ? (peer ? c->px[1].gathered : c->down_raw) : c->down_part;
-                n.raw_splits = m->tp > 1 ? (peer ? m->tp : 1) : c->s_down;
+                n.raw_splits = m->tp > 1 ? (peer ? m->tp : 1) : s_down;
                 if (m->tp > 1 && peer) n.px = c->px[1];
                 n.w_post = m->layers[l - 1].post_ff_ln;
                 n.scalar = m->layers[l - 1].layer_scalar;
             }
-            ln.go("norm", rows_norm_kernel, dim3(B), dim3(kRowsThreads), 0, n);
+            ln.go("norm", rows_norm_kernel, dim3(R), dim3(kRowsThreads), 0, n);
             copy_trace_tc();
             if (tr && tr->inject_dev) {
                 RowsNormArgs f = n;                      // layer-wise teacher forcing: forced input, nothing pending
                 f.embed = nullptr; f.raw = nullptr; f.w_post = nullptr; f.scalar = 1.0f;
-                f.h_in = tr->inject_dev + (size_t)l * B * H;
-                ln.go("norm", rows_norm_kernel, dim3(B), dim3(kRowsThreads), 0, f);
+                f.h_in = tr->inject_dev + (size_t)l * R * H;
+                ln.go("norm", rows_norm_kernel, dim3(R), dim3(kRowsThreads), 0, f);
             }
-            ln.tc("qkv", c, p.wqkv, nullptr, c->x_h, nqkv, H, c->s_qkv, c->qkv_part, nqkv, 0);
-            launch_attn(l, c->qkv_part, c->s_qkv, c->x_a);
-            ln.tc("o", c, p.wo, nullptr, c->x_a, H, qw, c->s_o, c->o_part, H, 0);
-            const size_t bh = (size_t)B * H;
+            ln.tc("qkv", c, R, p.wqkv, nullptr, c->x_h, nqkv, H, s_qkv, c->qkv_part, nqkv, 0);
+            launch_attention(ln, c, rs, l, c->qkv_part, s_qkv, c->x_a, true);
+            ln.tc("o", c, R, p.wo, nullptr, c->x_a, H, qw, s_o, c->o_part, H, 0);
+            const size_t bh = (size_t)R * H;
             const dim3 sum_grid((unsigned)((bh + kRowsThreads - 1) / kRowsThreads));
             PeerExchange none{};
             none.tp = 1;
             const float* xo = peer ? c->px[0].gathered : c->o_raw;        // what the next norm reads
             const int xs = peer ? m->tp : 1;                              // partials to add there
             if (m->tp > 1) {      // row-split projection: add the K-splits locally, then the ranks
-                ln.go("sum", sum_splits_kernel, sum_grid, dim3(kRowsThreads), 0, (const float*)c->o_part, c->s_o, bh, c->o_raw,
+                ln.go("sum", sum_splits_kernel, sum_grid, dim3(kRowsThreads), 0, (const float*)c->o_part, s_o, bh, c->o_raw,
                       peer ? c->px[0] : none);
                 if (!peer) ln.allreduce(c->o_raw, bh);
             }
             RowsNormArgs n2{};
-            n2.B = B; n2.H = H;
+            n2.B = R; n2.H = H;
             n2.h_in = c->hB; n2.h_out = c->hA;
             n2.raw = m->tp > 1 ? xo : c->o_part;
-            n2.raw_splits = m->tp > 1 ? xs : c->s_o;
+            n2.raw_splits = m->tp > 1 ? xs : s_o;
             n2.px = (m->tp > 1 && peer) ? c->px[0] : none;
             n2.w_post = p.post_attn_ln;
             n2.scalar = 1.0f;
             n2.w_norm = p.pre_ff_ln;
             n2.eps = m->cfg.rms_norm_eps;
             n2.x = c->x_h;
-            ln.go("norm", rows_norm_kernel, dim3(B), dim3(kRowsThreads), 0, n2);
-            ln.tc("gateup", c, p.wgate, p.wup, c->x_h, m->I, H, c->s_gu, c->gu_part, 2 * m->I, 0);
-            ln.go("geglu", geglu_rows_kernel, dim3((m->I + kRowsThreads - 1) / kRowsThreads, B), dim3(kRowsThreads), 0, B,
-                  m->I, (const float*)c->gu_part, c->s_gu, c->x_i);
-            ln.tc("down", c, p.wdown, nullptr, c->x_i, H, m->I, c->s_down, c->down_part, H, 0);
+            ln.go("norm", rows_norm_kernel, dim3(R), dim3(kRowsThreads), 0, n2);
+            ln.tc("gateup", c, R, p.wgate, p.wup, c->x_h, m->I, H, s_gu, c->gu_part, 2 * m->I, 0);
+            ln.go("geglu", geglu_rows_kernel, dim3((m->I + kRowsThreads - 1) / kRowsThreads, R), dim3(kRowsThreads), 0, R,
+                  m->I, (const float*)c->gu_part, s_gu, c->x_i);
+            ln.tc("down", c, R, p.wdown, nullptr, c->x_i, H, m->I, s_down, c->down_part, H, 0);
             if (m->tp > 1) {
-                ln.go("sum", sum_splits_kernel, sum_grid, dim3(kRowsThreads), 0, (const float*)c->down_part, c->s_down, bh,
+                ln.go("sum", sum_splits_kernel, sum_grid, dim3(kRowsThreads), 0, (const float*)c->down_part, s_down, bh,
                       c->down_raw, peer ? c->px[1] : none);
                 if (!peer) ln.allreduce(c->down_raw, bh);
             }
@@ -1436,7 +1438,7 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
             a.scalar = 1.0f;
             if (l == 0) {
                 a.embed = m->embed;
-                a.tokens = c->tokens;
+                a.tokens = rs.tok;
                 a.embed_scale = sqrtf((float)H);
             } else {
                 a.raw = c->down_raw;
@@ -1452,11 +1454,11 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
             }
             auto copy_trace = [&]() {
                 if (tr && ln.status == OXG4_OK &&
-                    cudaMemcpyAsync(tr->trace_dev + (size_t)l * B * H, c->hB, sizeof(float) * B * H,
+                    cudaMemcpyAsync(tr->trace_dev + (size_t)l * R * H, c->hB, sizeof(float) * R * H,
                                     cudaMemcpyDeviceToDevice, m->stream) != cudaSuccess)
                     ln.status = fail(OXG4_CUDA, "Gemma 4 CUDA error: trace copy failed");
             };
-            launch_gemv(ln, "qkv", c, a, m->p_qkv, PRO_NORM, EPI_STORE);
+            launch_gemv(ln, "qkv", c, R, a, m->p_qkv, PRO_NORM, EPI_STORE);
             copy_trace();          // the layer's input as this library computed it
             if (tr && tr->inject_dev) {
                 // layer-wise teacher forcing: redo the projection from the forced input, nothing pending
@@ -1464,18 +1466,18 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
                 a.raw = nullptr;
                 a.w_post = nullptr;
                 a.scalar = 1.0f;
-                a.h_in = tr->inject_dev + (size_t)l * B * H;
-                launch_gemv(ln, "qkv", c, a, m->p_qkv, PRO_NORM, EPI_STORE);
+                a.h_in = tr->inject_dev + (size_t)l * R * H;
+                launch_gemv(ln, "qkv", c, R, a, m->p_qkv, PRO_NORM, EPI_STORE);
             }
         }
-        launch_attn(l, c->qkv_raw, 1, nullptr);
+        launch_attention(ln, c, rs, l, c->qkv_raw, 1, nullptr, false);
         {   // O projection (decode.rs:159)
             GemvArgs a{};
             a.W0 = p.wo;
             a.in = c->attn_out;
             a.out = c->o_raw;
-            launch_gemv(ln, "o", c, a, m->p_o, PRO_PLAIN, EPI_STORE);
-            ln.allreduce(c->o_raw, (size_t)B * H);        // row-split projection: sum the ranks' partial outputs
+            launch_gemv(ln, "o", c, R, a, m->p_o, PRO_PLAIN, EPI_STORE);
+            ln.allreduce(c->o_raw, (size_t)R * H);        // row-split projection: sum the ranks' partial outputs
         }
         {   // post-attention norm + residual, pre-FF norm, gate and up projections (decode.rs:161-171, 14-16)
             GemvArgs a{};
@@ -1492,7 +1494,7 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
                 a.pf_ptr[0] = p.wdown;
                 a.pf_bytes[0] = (unsigned long long)m->p_down.N * m->p_down.K * m->es;
             }
-            launch_gemv(ln, "gateup", c, a, m->p_gateup, PRO_NORM, EPI_GATEUP);
+            launch_gemv(ln, "gateup", c, R, a, m->p_gateup, PRO_NORM, EPI_GATEUP);
         }
         {   // GeGLU + down projection (decode.rs:17-18)
             GemvArgs a{};
@@ -1503,35 +1505,53 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
                 if (l + 1 < L) {
                     a.pf_ptr[0] = m->layers[l + 1].wqkv;
                     a.pf_bytes[0] = (unsigned long long)m->p_qkv.N * m->p_qkv.K * m->es;
-                } else if (kind != STEP_PREFILL) {
+                } else if (last_layer_prefetch) {
                     a.pf_ptr[0] = (const char*)m->embed + (size_t)m->v0 * H * m->es;
                     a.pf_bytes[0] = std::min<unsigned long long>((unsigned long long)m->Vloc * H * m->es, 64ull << 20);
                 }
             }
-            launch_gemv(ln, "down", c, a, m->p_down, PRO_PLAIN, EPI_STORE);
-            ln.allreduce(c->down_raw, (size_t)B * H);
+            launch_gemv(ln, "down", c, R, a, m->p_down, PRO_PLAIN, EPI_STORE);
+            ln.allreduce(c->down_raw, (size_t)R * H);
         }
     }
-    if (kind != STEP_PREFILL && c->use_tc) {
-        RowsNormArgs n{};
-        n.B = B; n.H = H;
-        n.h_in = c->hA; n.h_out = c->hB;
-        n.raw = m->tp > 1 ? (peer ? c->px[1].gathered : c->down_raw) : c->down_part;
-        n.raw_splits = m->tp > 1 ? (peer ? m->tp : 1) : c->s_down;
-        if (m->tp > 1 && peer) n.px = c->px[1];
-        n.w_post = m->layers[L - 1].post_ff_ln;
-        n.scalar = m->layers[L - 1].layer_scalar;
-        n.w_norm = m->final_norm;
-        n.eps = m->cfg.rms_norm_eps;
-        n.x = c->x_h;
-        ln.go("norm", rows_norm_kernel, dim3(B), dim3(kRowsThreads), 0, n);
+}
+
+// tcgen05 path: the last layer's pending update + final norm for `rows` rows: h -> c->hB, x -> c->x_h
+static void closing_norm_tc(oxg4_cache* c, Launcher& ln, int rows, bool chunk, bool peer) {
+    oxg4_model* m = c->m;
+    const int L = m->cfg.num_hidden_layers;
+    RowsNormArgs n{};
+    n.B = rows; n.H = m->H;
+    n.h_in = c->hA; n.h_out = c->hB;
+    n.raw = m->tp > 1 ? (peer ? c->px[1].gathered : c->down_raw) : c->down_part;
+    n.raw_splits = m->tp > 1 ? (peer ? m->tp : 1) : (chunk ? c->ps_down : c->s_down);
+    if (m->tp > 1 && peer) n.px = c->px[1];
+    n.w_post = m->layers[L - 1].post_ff_ln;
+    n.scalar = m->layers[L - 1].layer_scalar;
+    n.w_norm = m->final_norm;
+    n.eps = m->cfg.rms_norm_eps;
+    n.x = c->x_h;
+    ln.go("norm", rows_norm_kernel, dim3(rows), dim3(kRowsThreads), 0, n);
+}
+
+// Tied LM head over B rows + arg-max / top-k (decode.rs:495-508, kernel_module.rs:1988-2075).
+// tcgen05 path: x [B, H] BF16 normed activations. Small-batch path: the pending update (h_in + raw) is closed by
+// the kernel's prologue.
+static void lm_head(oxg4_cache* c, Launcher& ln, int kind, int top_k, float penalty, bool use_tc, const uint16_t* x,
+                    const float* h_in, const float* raw, const TraceCtx* tr) {
+    oxg4_model* m = c->m;
+    const int B = c->B, L = m->cfg.num_hidden_layers, H = m->H;
+    auto trace_final = [&]() {
         if (tr && ln.status == OXG4_OK &&
             cudaMemcpyAsync(tr->trace_dev + (size_t)L * B * H, c->hB, sizeof(float) * B * H, cudaMemcpyDeviceToDevice,
                             m->stream) != cudaSuccess)
             ln.status = fail(OXG4_CUDA, "Gemma 4 CUDA error: trace copy failed");
+    };
+    if (use_tc) {
+        trace_final();
         if (m->tp > 1 && cudaMemsetAsync(c->logits, 0, sizeof(float) * (size_t)B * m->V, m->stream) != cudaSuccess)
             ln.status = fail(OXG4_CUDA, "Gemma 4 CUDA error: cudaMemsetAsync failed");
-        ln.tc("lmhead", c, (const char*)m->embed + (size_t)m->v0 * H * m->es, nullptr, c->x_h, m->Vloc, H, 1, c->logits,
+        ln.tc("lmhead", c, B, (const char*)m->embed + (size_t)m->v0 * H * m->es, nullptr, x, m->Vloc, H, 1, c->logits,
               m->V, m->v0);
         ln.allreduce(c->logits, (size_t)B * m->V);
         // top-k over the full logits (k = 1 is the arg-max the greedy loop feeds back)
@@ -1542,51 +1562,74 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
         ln.go("topk2", topk_stage2_kernel, dim3(1, B), dim3(kTopkThreads), (size_t)chunks * k * 8,
               (const Cand*)c->topk_stage, chunks * k, k, k == 1 ? c->best_ids : c->topk_ids,
               k == 1 ? c->best_scores : c->topk_scores);
-    } else if (kind != STEP_PREFILL) {
-        // post-FF norm + residual + layer_scalar of the last layer, final norm, tied LM head with
-        // fused arg-max (decode.rs:495-508, kernel_module.rs:1988-2075)
-        GemvArgs a{};
-        a.W0 = (const char*)m->embed + (size_t)m->v0 * H * m->es;
-        a.h_in = c->hA;
-        a.h_out = c->hB;
-        a.raw = c->down_raw;
-        a.w_post = m->layers[L - 1].post_ff_ln;
-        a.scalar = m->layers[L - 1].layer_scalar;
-        a.w_norm = m->final_norm;
-        const bool want_logits = (kind == STEP_LOGITS) || top_k > 1;
-        a.out = want_logits ? c->logits : nullptr;
-        a.seen = c->seen;
-        a.penalty = penalty;
-        a.row_offset = m->v0;
-        a.n_total = m->V;
-        a.blk_best = c->blk_best;
-        a.ticket = c->lm_ticket;
-        a.best_ids = c->best_ids;
-        a.best_scores = c->best_scores;
-        if (m->tp > 1 && want_logits) {
-            // every rank fills its vocabulary columns; the others stay zero and the sum assembles the row
-            if (cudaMemsetAsync(c->logits, 0, sizeof(float) * (size_t)B * m->V, m->stream) != cudaSuccess)
-                ln.status = fail(OXG4_CUDA, "Gemma 4 CUDA error: cudaMemsetAsync failed");
-        }
-        launch_gemv(ln, "lmhead", c, a, m->p_lm, PRO_NORM, EPI_LOGITS);
-        if (m->tp > 1) {
-            if (want_logits) ln.allreduce(c->logits, (size_t)B * m->V);
-            ln.allgather(c->best_scores, c->tp_scores, sizeof(float) * B);
-            ln.allgather(c->best_ids, c->tp_ids, sizeof(uint32_t) * B);
-            ln.go("tp_pick", tp_pick_kernel, dim3(1), dim3(128), 0, B, m->tp, (const float*)c->tp_scores,
-                  (const uint32_t*)c->tp_ids, c->best_ids, c->best_scores);
-        }
-        if (tr && ln.status == OXG4_OK &&
-            cudaMemcpyAsync(tr->trace_dev + (size_t)L * B * H, c->hB, sizeof(float) * B * H, cudaMemcpyDeviceToDevice,
-                            m->stream) != cudaSuccess)
-            ln.status = fail(OXG4_CUDA, "Gemma 4 CUDA error: trace copy failed");
-        if (kind == STEP_TOPK && top_k > 1) {
-            const int chunks = (m->V + kTopkChunk - 1) / kTopkChunk;
-            ln.go("topk1", topk_stage1_kernel, dim3(chunks, B), dim3(kTopkThreads), 0, (const float*)c->logits,
-                  m->V, (const uint8_t*)c->seen, penalty, top_k, c->topk_stage);
-            ln.go("topk2", topk_stage2_kernel, dim3(1, B), dim3(kTopkThreads), (size_t)chunks * top_k * 8,
-                  (const Cand*)c->topk_stage, chunks * top_k, top_k, c->topk_ids, c->topk_scores);
-        }
+        return;
+    }
+    // post-FF norm + residual + layer_scalar of the last layer, final norm, tied LM head with fused arg-max
+    GemvArgs a{};
+    a.W0 = (const char*)m->embed + (size_t)m->v0 * H * m->es;
+    a.h_in = h_in;
+    a.h_out = c->hB;
+    a.raw = raw;
+    a.w_post = m->layers[L - 1].post_ff_ln;
+    a.scalar = m->layers[L - 1].layer_scalar;
+    a.w_norm = m->final_norm;
+    const bool want_logits = (kind == STEP_LOGITS) || top_k > 1;
+    a.out = want_logits ? c->logits : nullptr;
+    a.seen = c->seen;
+    a.penalty = penalty;
+    a.row_offset = m->v0;
+    a.n_total = m->V;
+    a.blk_best = c->blk_best;
+    a.ticket = c->lm_ticket;
+    a.best_ids = c->best_ids;
+    a.best_scores = c->best_scores;
+    if (m->tp > 1 && want_logits) {
+        // every rank fills its vocabulary columns; the others stay zero and the sum assembles the row
+        if (cudaMemsetAsync(c->logits, 0, sizeof(float) * (size_t)B * m->V, m->stream) != cudaSuccess)
+            ln.status = fail(OXG4_CUDA, "Gemma 4 CUDA error: cudaMemsetAsync failed");
+    }
+    launch_gemv(ln, "lmhead", c, B, a, m->p_lm, PRO_NORM, EPI_LOGITS);
+    if (m->tp > 1) {
+        if (want_logits) ln.allreduce(c->logits, (size_t)B * m->V);
+        ln.allgather(c->best_scores, c->tp_scores, sizeof(float) * B);
+        ln.allgather(c->best_ids, c->tp_ids, sizeof(uint32_t) * B);
+        ln.go("tp_pick", tp_pick_kernel, dim3(1), dim3(128), 0, B, m->tp, (const float*)c->tp_scores,
+              (const uint32_t*)c->tp_ids, c->best_ids, c->best_scores);
+    }
+    trace_final();
+    if (kind == STEP_TOPK && top_k > 1) {
+        const int chunks = (m->V + kTopkChunk - 1) / kTopkChunk;
+        ln.go("topk1", topk_stage1_kernel, dim3(chunks, B), dim3(kTopkThreads), 0, (const float*)c->logits,
+              m->V, (const uint8_t*)c->seen, penalty, top_k, c->topk_stage);
+        ln.go("topk2", topk_stage2_kernel, dim3(1, B), dim3(kTopkThreads), (size_t)chunks * top_k * 8,
+              (const Cand*)c->topk_stage, chunks * top_k, top_k, c->topk_ids, c->topk_scores);
+    }
+}
+
+static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* n_kernels,
+                        const TraceCtx* tr = nullptr) {
+    oxg4_model* m = c->m;
+    Launcher ln{m};
+    ln.ts_base = c->ts_buf;
+    const int B = c->B;
+    // Sums over peer memory only in steps whose last exchange is consumed (the closing norm before the
+    // LM head): a prompt-ingestion step skips that norm, so it takes the NCCL all-reduce instead and the
+    // single exchange buffer per kind is never pushed into while a peer may still read it.
+    const bool peer = c->peer_ready && kind != STEP_PREFILL;
+    ln.go("step_begin", step_begin_kernel, dim3(1), dim3(128), 0, B, m->V,
+          (const uint32_t*)c->tokens, c->seen, (const StepCtl*)c->ctl);
+    RowSet rs;
+    rs.R = B;
+    rs.tok = c->tokens;
+    rs.pos = c->pos;
+    rs.grp_row0 = c->dec_grp_row0;
+    rs.grp_n = c->dec_grp_n;
+    rs.NG = B;
+    rs.part_rows = m->G;
+    run_layers(c, ln, rs, c->use_tc, peer, kind != STEP_PREFILL, tr);
+    if (kind != STEP_PREFILL) {
+        if (c->use_tc) closing_norm_tc(c, ln, B, false, peer);
+        lm_head(c, ln, kind, top_k, penalty, c->use_tc, c->x_h, c->hA, c->down_raw, tr);
     }
     if (kind == STEP_TOPK && top_k > 1)      // a no-op unless the step's control words ask for a sampled token
         ln.go("sample", sample_candidates_kernel, dim3(1), dim3(64), 0, B, top_k, m->cfg.final_logit_softcapping,
@@ -1673,17 +1716,13 @@ static void advance_host(oxg4_cache* c, const uint32_t* tokens, int steps = 1) {
 
 // the tcgen05 kernels raise a device flag instead of hanging when one of their bounded waits runs out
 static int32_t check_tc(oxg4_cache* c) {
-    if (c->use_mega && *(volatile int*)c->mega_status != 0) {      // mapped host word, read after a stream sync
-        const int code = *c->mega_status;
-        *c->mega_status = 0;
-        return fail(OXG4_TIMEOUT, "persistent decode kernel: a bounded wait ran out (kind %d: 1 grid barrier, 2 stage not released, 3 piece not delivered, 4 shared stage not released; CTA %d, piece/barrier %d, warp %d)", code & 15, (code >> 4) & 255, (code >> 12) & 16383, (code >> 26) & 31);
-    }
-    if (!c->use_tc) return OXG4_OK;
+    if (!c->tc_ok && !c->mma_attn) return OXG4_OK;
     int err = 0;
     CK(cudaMemcpy(&err, c->tc_err, sizeof err, cudaMemcpyDeviceToHost));
     if (err) {
         cudaMemset(c->tc_err, 0, sizeof err);
-        return fail(OXG4_TIMEOUT, "tcgen05 projection: a bounded barrier wait ran out (code %d)", err);
+        return fail(OXG4_TIMEOUT, "%s: a bounded barrier wait ran out (code %d)",
+                    err >= 10 ? "tensor-core attention" : "tcgen05 projection", err);
     }
     if (c->peer_ready) {
         CK(cudaMemcpy(&err, c->px_local + 4, sizeof err, cudaMemcpyDeviceToHost));
@@ -1941,29 +1980,112 @@ extern "C" int32_t oxg4_profile_count(const oxg4_model* m, const char* kind) {
     return it == m->profile.end() ? 0 : it->second.count;
 }
 
+// prefill_prompt (decode.rs:386-459): the prompts of all sequences go through the layers in chunks of up to
+// kPrefillRows tokens, each chunk one pass with matrix-shaped projections (tcgen05 for BF16 weights) and causal /
+// sliding paged attention over the chunk; a chunk may hold the tail of one sequence and the head of the next.
+// Unlike the reference there is no 4096-token limit and no requirement that the prompt fits the sliding ring.
 extern "C" int32_t oxg4_prefill(oxg4_model* m, oxg4_cache* c, const uint32_t* tokens, const int32_t* lens,
                                 float* last_logits) {
     if (!m || !c || !tokens || !lens || c->m != m) return fail(OXG4_INVALID_ARGUMENT, "null or mismatched handle");
-    const int B = c->B;
-    int maxlen = 0;
+    const int B = c->B, H = m->H;
     std::vector<int64_t> off(B + 1, 0);
     for (int b = 0; b < B; ++b) {
         if (lens[b] <= 0) return fail(OXG4_INVALID_ARGUMENT, "batched prefill requires at least one token per sequence");
         if (c->pos_host[b] != 0) return fail(OXG4_INVALID_ARGUMENT, "batched prefill requires an empty cache table");   // decode.rs:392-396
         if (lens[b] > c->max_seq[b]) return fail(OXG4_INVALID_SHAPE, "prompt does not fit the cache table");
         off[b + 1] = off[b] + lens[b];
-        maxlen = std::max(maxlen, lens[b]);
     }
-    // The prompt is ingested with the decode step, one token per sequence and step, as the
-    // reference's prefill_token does (decode.rs:464-472); shorter prompts sit out once exhausted.
-    std::vector<uint32_t> step_tokens(B);
-    for (int t = 0; t + 1 < maxlen; ++t) {
-        for (int b = 0; b < B; ++b) step_tokens[b] = (t + 1 < lens[b]) ? tokens[off[b] + t] : kInactiveToken;
-        TRY(oxg4_prefill_token(m, c, step_tokens.data()));
+    for (int64_t i = 0; i < off[B]; ++i)
+        if (tokens[i] >= (uint32_t)m->V) return fail(OXG4_INVALID_ARGUMENT, "token id exceeds CUDA decode vocabulary");
+    TRY(bind_device(m));
+    if (getenv("OXG4_PREFILL_BY_TOKEN")) {
+        // the reference's sequential alternative (prefill_token, decode.rs:464-472): one token per sequence and step
+        int maxlen = 0;
+        for (int b = 0; b < B; ++b) maxlen = std::max(maxlen, lens[b]);
+        std::vector<uint32_t> step_tokens(B);
+        for (int t = 0; t + 1 < maxlen; ++t) {
+            for (int b = 0; b < B; ++b) step_tokens[b] = (t + 1 < lens[b]) ? tokens[off[b] + t] : kInactiveToken;
+            TRY(oxg4_prefill_token(m, c, step_tokens.data()));
+        }
+        for (int b = 0; b < B; ++b) step_tokens[b] = tokens[off[b] + lens[b] - 1];
+        if (last_logits) return oxg4_decode_logits(m, c, step_tokens.data(), last_logits);
+        return oxg4_prefill_token(m, c, step_tokens.data());
     }
-    for (int b = 0; b < B; ++b) step_tokens[b] = tokens[off[b] + lens[b] - 1];
-    if (last_logits) return oxg4_decode_logits(m, c, step_tokens.data(), last_logits);
-    return oxg4_prefill_token(m, c, step_tokens.data());
+    const bool use_tc = c->tc_ok;
+    const int tg = std::max(1, kAmRows / m->G);               // tokens per attention group
+    int32_t* h_pos = c->h_pf_meta;
+    int32_t* h_seq = h_pos + kPrefillRows;
+    int32_t* h_g0 = h_seq + kPrefillRows;
+    int32_t* h_gn = h_g0 + kAmMaxGroups;
+    int b = 0, p = 0;                                          // next token to place: sequence b, position p
+    while (b < B) {
+        int R = 0, NG = 0;
+        std::vector<std::pair<int, int>> finishing;            // (sequence, row) of every last prompt token in this chunk
+        while (b < B && R < kPrefillRows) {
+            const int take = std::min(kPrefillRows - R, lens[b] - p);
+            for (int i = 0; i < take; ++i) {
+                c->h_pf_tok[R + i] = tokens[off[b] + p + i];
+                h_pos[R + i] = p + i;
+                h_seq[R + i] = b;
+            }
+            for (int i = 0; i < take; i += tg) { h_g0[NG] = R + i; h_gn[NG] = std::min(tg, take - i); ++NG; }
+            R += take;
+            p += take;
+            if (p == lens[b]) { finishing.push_back({b, R - 1}); ++b; p = 0; }
+        }
+        cudaStream_t st = m->stream;
+        CK(cudaMemcpyAsync(c->pf_tok, c->h_pf_tok, sizeof(uint32_t) * R, cudaMemcpyHostToDevice, st));
+        CK(cudaMemcpyAsync(c->pf_pos, h_pos, sizeof(int32_t) * R, cudaMemcpyHostToDevice, st));
+        CK(cudaMemcpyAsync(c->pf_seq, h_seq, sizeof(int32_t) * R, cudaMemcpyHostToDevice, st));
+        CK(cudaMemcpyAsync(c->pf_grp_row0, h_g0, sizeof(int32_t) * NG, cudaMemcpyHostToDevice, st));
+        CK(cudaMemcpyAsync(c->pf_grp_n, h_gn, sizeof(int32_t) * NG, cudaMemcpyHostToDevice, st));
+        Launcher ln{m};
+        RowSet rs;
+        rs.R = R;
+        rs.tok = c->pf_tok;
+        rs.pos = c->pf_pos;
+        rs.seq = c->pf_seq;
+        rs.chunk = true;
+        rs.grp_row0 = c->pf_grp_row0;
+        rs.grp_n = c->pf_grp_n;
+        rs.NG = NG;
+        rs.part_rows = kAmRows;
+        run_layers(c, ln, rs, use_tc, false, false, nullptr);
+        if (last_logits && !finishing.empty() && ln.status == OXG4_OK) {
+            // keep what the LM head will need of every sequence that ends in this chunk
+            if (use_tc) closing_norm_tc(c, ln, R, true, false);
+            for (auto& f : finishing) {
+                if (use_tc) {
+                    CK(cudaMemcpyAsync(c->last_x + (size_t)f.first * H, c->x_h + (size_t)f.second * H, sizeof(uint16_t) * H,
+                                       cudaMemcpyDeviceToDevice, st));
+                } else {
+                    CK(cudaMemcpyAsync(c->last_h + (size_t)f.first * H, c->hA + (size_t)f.second * H, sizeof(float) * H,
+                                       cudaMemcpyDeviceToDevice, st));
+                    CK(cudaMemcpyAsync(c->last_raw + (size_t)f.first * H, c->down_raw + (size_t)f.second * H,
+                                       sizeof(float) * H, cudaMemcpyDeviceToDevice, st));
+                }
+            }
+        }
+        TRY(ln.status);
+        m->launches += ln.kernels;
+        CK(cudaStreamSynchronize(st));                         // the pinned staging is reused by the next chunk
+        TRY(check_tc(c));
+    }
+    // device step state: every sequence continues at position lens[b]
+    std::vector<int32_t> np(lens, lens + B);
+    CK(cudaMemcpy(c->pos, np.data(), sizeof(int32_t) * B, cudaMemcpyHostToDevice));
+    for (int i = 0; i < B; ++i) c->pos_host[i] = lens[i];
+    if (last_logits) {
+        Launcher ln{m};
+        lm_head(c, ln, STEP_LOGITS, 1, 1.0f, use_tc, c->last_x, c->last_h, c->last_raw, nullptr);
+        TRY(ln.status);
+        m->launches += ln.kernels;
+        CK(cudaMemcpyAsync(last_logits, c->logits, sizeof(float) * (size_t)B * m->V, cudaMemcpyDeviceToHost, m->stream));
+        CK(cudaStreamSynchronize(m->stream));
+        TRY(check_tc(c));
+        softcap(last_logits, (size_t)B * m->V, m->cfg.final_logit_softcapping);
+    }
+    return OXG4_OK;
 }
 
 // ------------------------------------------------------------------------------------------------

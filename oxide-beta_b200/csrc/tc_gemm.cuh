@@ -1,8 +1,8 @@
 // Batched projection on the 5th-generation tensor cores (tcgen05 + TMEM), fed by TMA.
 //
 // out[b, n] = sum_k x[b, k] * W[n, k]   (the reference's cuBLAS contract, crates/oxide-torch-cuda/src/
-// cublas.rs:101-153: BF16 operands, f32 accumulate, f32 output) for 16..64 activation rows, where the
-// weight matrix is streamed from HBM exactly once.
+// cublas.rs:101-153: BF16 operands, f32 accumulate, f32 output) for 1..64 activation rows per block (up to
+// 256 rows in four blocks for prompt chunks), where the weight matrix is streamed from HBM exactly once.
 //
 // Roles are swapped with respect to a textbook GEMM because the batch is the small dimension: the
 // 128-row weight tile is the MMA's M operand (A, K-major in shared memory), the activations are
@@ -33,9 +33,11 @@ constexpr int kTcStages = 6;
 constexpr uint32_t kTcSpinLimit = 2u * 1000u * 1000u;   // bounded mbarrier polling
 
 struct TcGemmArgs {
-    int N, K, B;             // rows of ONE weight matrix, columns, activation rows (B <= BN)
+    int N, K, B;             // rows of ONE weight matrix, columns, activation rows (cut into blocks of BN rows)
     int n_mats;              // 1, or 2 when gate and up are streamed by one launch (second tensor map)
-    int S;                   // K-splits: a work unit is (128-row tile, split); S partial outputs are added later
+    int S;                   // K-splits: a work unit is (128-row tile, split, row block); S partial outputs are added later
+    int TB;                  // row blocks: ceil(B / BN). Units of one weight tile are adjacent, so that tile
+                             // crosses HBM once and the other row blocks find it in L2 (prompt chunks: B up to 256)
     int kb_per_split;        // 64-column blocks per split
     float* out;              // [S, B, ld]; matrix m occupies columns col0 + m * N ..
     int ld, col0;            // row stride of `out` (>= n_mats * N) and first column written
@@ -113,11 +115,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tiles_per_mat = (a.N + kTcTileM - 1) / kTcTileM;
-    const int n_tiles = tiles_per_mat * a.n_mats * a.S;          // work units: (matrix, tile, split)
+    const int n_tiles = tiles_per_mat * a.n_mats * a.S * a.TB;   // work units: (matrix, tile, split, row block)
     const int kblocks_all = (a.K + kTcTileK - 1) / kTcTileK;
-    // unit u -> split s = u % S, tile index (over both matrices) u / S
-    auto kb_begin = [&](int u) { return (u % a.S) * a.kb_per_split; };
-    auto kb_end = [&](int u) { return min(kblocks_all, (u % a.S + 1) * a.kb_per_split); };
+    // unit u -> row block u % TB, split (u / TB) % S, tile index (over both matrices) u / (TB * S)
+    auto kb_begin = [&](int u) { return ((u / a.TB) % a.S) * a.kb_per_split; };
+    auto kb_end = [&](int u) { return min(kblocks_all, ((u / a.TB) % a.S + 1) * a.kb_per_split); };
 
     if (tid == 0) {
         for (int s = 0; s < kTcStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -142,9 +144,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // ---- TMA producer ----
         uint32_t it = 0;
         for (int t = blockIdx.x; t < n_tiles && !failed; t += gridDim.x) {
-            const int tg = t / a.S;                               // tile over both matrices
+            const int tg = t / (a.S * a.TB);                      // tile over both matrices
             const bool second = tg >= tiles_per_mat;
             const int trow = (second ? tg - tiles_per_mat : tg) * kTcTileM;
+            const int xrow = (t % a.TB) * BN;                     // first activation row of this unit's block
             for (int kb = kb_begin(t); kb < kb_end(t); ++kb, ++it) {
                 const int s = it % kTcStages;
                 const uint32_t ph = (it / kTcStages) & 1;
@@ -152,7 +155,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 unsigned char* sa = tiles + (size_t)s * STAGE;
                 mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
                 tma_load_2d(sa, second ? &map_w1 : &map_w, kb * kTcTileK, trow, &full[s]);
-                tma_load_2d(sa + A_BYTES, &map_x, kb * kTcTileK, 0, &full[s]);
+                tma_load_2d(sa + A_BYTES, &map_x, kb * kTcTileK, xrow, &full[s]);
             }
         }
     } else if (warp == 1 && lane == 0) {
@@ -196,10 +199,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++tile_i) {
             if (!mbar_wait(&acc_full, tile_i & 1)) { if (lane == 0) atomicExch(a.err, 4); break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int tg = t / a.S, sp = t % a.S;
+            const int tg = t / (a.S * a.TB), sp = (t / a.TB) % a.S, b0 = (t % a.TB) * BN;
             const bool second = tg >= tiles_per_mat;
             const int row = (second ? tg - tiles_per_mat : tg) * kTcTileM + quad * 32 + lane;
-            float* dst = a.out + (size_t)sp * a.B * a.ld + a.col0 + (second ? a.N : 0);
+            float* dst = a.out + ((size_t)sp * a.B + b0) * a.ld + a.col0 + (second ? a.N : 0);
 #pragma unroll
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 uint32_t v[16];
@@ -213,7 +216,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 if (row < a.N) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
-                        if (c0 + j < a.B) dst[(size_t)(c0 + j) * a.ld + row] = __uint_as_float(v[j]);
+                        if (b0 + c0 + j < a.B) dst[(size_t)(c0 + j) * a.ld + row] = __uint_as_float(v[j]);
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
