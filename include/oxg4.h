@@ -114,6 +114,33 @@ int32_t oxg4_tp_shard(const char* name, int64_t rows, int64_t cols, int32_t tp_r
                       int32_t heads, int32_t kv_heads, int32_t head_dim, int32_t intermediate, int64_t* out4);
 int32_t oxg4_model_tp_init(oxg4_model* model, const void* unique_id_128_bytes);
 
+/* Tensor parallelism driven by one host thread (no counterpart in the reference). The reference's surface is
+ * single-threaded (Gemma4ForCausalLM::generate owns an Rc<RefCell<Gemma4CudaState>>, models/gemma4/
+ * generation.rs:70-140), so a multi-GPU state behind it cannot need one process or thread per rank from its
+ * caller: the group handle below owns one model per device in `device_ordinals` and one internal worker
+ * thread + stream per rank, and every call fans out to the ranks and waits. Semantics, arguments and
+ * results are those of the single-GPU entry points of the same name; uploads take the FULL tensor (every
+ * rank keeps its shard); NCCL is set up inside oxg4_tp_model_finalize. Handles are not thread-safe. */
+typedef struct oxg4_tp_model oxg4_tp_model;
+typedef struct oxg4_tp_cache oxg4_tp_cache;
+int32_t oxg4_tp_model_create(const oxg4_config* config, const int32_t* device_ordinals, int32_t tp, oxg4_tp_model** out);
+int32_t oxg4_tp_model_upload(oxg4_tp_model* model, const char* name, int32_t dtype, const int64_t* shape,
+                             int32_t rank, const void* data, size_t bytes);
+int32_t oxg4_tp_model_finalize(oxg4_tp_model* model);
+void oxg4_tp_model_destroy(oxg4_tp_model* model);
+int64_t oxg4_tp_weight_bytes(const oxg4_tp_model* model);
+int32_t oxg4_tp_cache_create(oxg4_tp_model* model, int32_t batch, const int32_t* max_seq, int32_t page_tokens,
+                             int32_t kv_dtype, oxg4_tp_cache** out);
+void oxg4_tp_cache_destroy(oxg4_tp_cache* cache);
+int32_t oxg4_tp_cache_position(const oxg4_tp_cache* cache, int32_t b);
+int32_t oxg4_tp_prefill(oxg4_tp_model* model, oxg4_tp_cache* cache, const uint32_t* tokens, const int32_t* lens,
+                        float* last_logits);
+int32_t oxg4_tp_decode_logits(oxg4_tp_model* model, oxg4_tp_cache* cache, const uint32_t* tokens, float* logits);
+int32_t oxg4_tp_decode_topk(oxg4_tp_model* model, oxg4_tp_cache* cache, const uint32_t* tokens, int32_t top_k,
+                            float repetition_penalty, int32_t mark_seen, uint32_t* ids, float* scores);
+int32_t oxg4_tp_decode_greedy(oxg4_tp_model* model, oxg4_tp_cache* cache, const uint32_t* first_tokens, int32_t steps,
+                              uint32_t* out_ids, float* ms_per_step);
+
 /* Peer-memory exchange for tensor parallelism (no counterpart in the reference). With tp_size > 1 and
  * 8..64 sequences the sums after the O and down projections can travel through buffers that the
  * ranks map into each other with CUDA IPC instead of NCCL calls: every rank exports the handle of its
@@ -191,6 +218,16 @@ int64_t oxg4_kernel_launches(const oxg4_model* model);
 int32_t oxg4_profile_step(oxg4_model* model, oxg4_cache* cache, const uint32_t* tokens);
 float oxg4_profile_ms(const oxg4_model* model, const char* kind);
 int32_t oxg4_profile_count(const oxg4_model* model, const char* kind);
+
+/* Failure-path test hooks (no counterpart in the reference, whose errors are Result values and whose
+ * capture always ends, crates/oxide-torch-cuda/src/cuda_graph.rs:84-97). Neither faults or hangs a GPU.
+ * oxg4_debug_wait_timeout runs one of the library's bounded device-side waits (kind 1: mbarrier phase,
+ * kind 2: tensor-parallel peer flag) on something nobody signals, with a polling budget of `spin_limit`:
+ * the kernel returns, the status word is raised and the call returns OXG4_TIMEOUT; later calls work.
+ * oxg4_debug_fail_alloc_after makes the n-th device allocation of the next oxg4_cache_create report
+ * OXG4_OOM (0 switches it off); the failed create must release everything it had allocated. */
+int32_t oxg4_debug_wait_timeout(oxg4_model* model, oxg4_cache* cache, int32_t kind, uint32_t spin_limit);
+void oxg4_debug_fail_alloc_after(int32_t n);
 
 /* Top-k selection that allocates nothing (no counterpart in the reference). It is meant for callers
  * that are not allowed to allocate device memory at the moment they need a top-k: code running

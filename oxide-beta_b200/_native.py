@@ -58,6 +58,22 @@ SYMBOLS = {
     "oxg4_tp_shard": (C.c_int32, [C.c_char_p, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                   C.c_int32, C.POINTER(C.c_int64)]),
     "oxg4_model_tp_init": (C.c_int32, [C.c_void_p, C.c_void_p]),
+    "oxg4_tp_model_create": (C.c_int32, [C.POINTER(Config), C.POINTER(C.c_int32), C.c_int32, C.POINTER(C.c_void_p)]),
+    "oxg4_tp_model_upload": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_int32, C.POINTER(C.c_int64), C.c_int32,
+                                         C.c_void_p, C.c_size_t]),
+    "oxg4_tp_model_finalize": (C.c_int32, [C.c_void_p]),
+    "oxg4_tp_model_destroy": (None, [C.c_void_p]),
+    "oxg4_tp_weight_bytes": (C.c_int64, [C.c_void_p]),
+    "oxg4_tp_cache_create": (C.c_int32, [C.c_void_p, C.c_int32, C.POINTER(C.c_int32), C.c_int32, C.c_int32,
+                                         C.POINTER(C.c_void_p)]),
+    "oxg4_tp_cache_destroy": (None, [C.c_void_p]),
+    "oxg4_tp_cache_position": (C.c_int32, [C.c_void_p, C.c_int32]),
+    "oxg4_tp_prefill": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "oxg4_tp_decode_logits": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "oxg4_tp_decode_topk": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_float, C.c_int32,
+                                        C.c_void_p, C.c_void_p]),
+    "oxg4_tp_decode_greedy": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
+                                          C.POINTER(C.c_float)]),
     "oxg4_cache_tp_export": (C.c_int32, [C.c_void_p, C.c_void_p]),
     "oxg4_cache_tp_connect": (C.c_int32, [C.c_void_p, C.c_void_p]),
     "oxg4_cache_create": (C.c_int32, [C.c_void_p, C.c_int32, C.POINTER(C.c_int32), C.c_int32, C.c_int32,
@@ -79,6 +95,8 @@ SYMBOLS = {
     "oxg4_profile_step": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "oxg4_profile_ms": (C.c_float, [C.c_void_p, C.c_char_p]),
     "oxg4_profile_count": (C.c_int32, [C.c_void_p, C.c_char_p]),
+    "oxg4_debug_wait_timeout": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_uint32]),
+    "oxg4_debug_fail_alloc_after": (None, [C.c_int32]),
     "oxg4_topk_noalloc": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_float, C.c_int32, C.c_void_p,
                                       C.c_void_p, C.c_void_p]),
     "oxg4_decode_trace": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),

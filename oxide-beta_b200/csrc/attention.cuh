@@ -224,7 +224,7 @@ DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, c
         }
     };
     Raw kr[PD], vr[PD];
-    if (has_work) {
+    if (has_work && !ext) {
 #pragma unroll
         for (int q = 0; q < PD; ++q) issue(begin + warp + q * NW, kr[q], vr[q]);
     }
@@ -247,6 +247,12 @@ DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, c
         pdl_launch();
     }
     stamp(a.ts, 1);
+    if (has_work && ext) {
+        // rows of a prompt chunk: the K/V rows of this very chunk were appended by the preceding kernel, so
+        // nothing may be read from the cache before the dependency wait
+#pragma unroll
+        for (int q = 0; q < PD; ++q) issue(begin + warp + q * NW, kr[q], vr[q]);
+    }
 
     if (has_work) {
         const bool owner = (s == n_eff - 1);        // the range that contains `pos`

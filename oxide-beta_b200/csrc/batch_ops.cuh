@@ -11,6 +11,7 @@
 //   geglu_rows_kernel gelu_mul_f32 + f32_to_bf16 (decode.rs:17, kernel_module.rs:1441-1458, 1338-1348)
 #pragma once
 #include "common.cuh"
+#include "tc_gemm.cuh"
 
 namespace oxg4 {
 
@@ -43,6 +44,13 @@ DEVINL void st_release_sys(unsigned int* p, unsigned int v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+// Bounded wait until *flag >= want; false when the polling budget ran out.
+DEVINL bool peer_flag_wait(const unsigned int* flag, unsigned int want, unsigned int limit = kPeerSpinLimit) {
+    unsigned int it = 0;
+    while (ld_acquire_sys(flag) < want && ++it < limit) {}
+    return it < limit;
+}
+
 struct RowsNormArgs {
     int B, H;
     const float* h_in;       // [B, H] (unused with embed)
@@ -60,81 +68,117 @@ struct RowsNormArgs {
     PeerExchange px;         // px.tp > 1: `raw` is the local gather buffer; wait for every rank's push first
 };
 
-constexpr int kRowsMaxJ = 24;                 // values of a row held per thread: hidden <= 24 * 256 = 6144
+constexpr int kRowsMaxJ = 6;                  // float4 groups of a row held per thread: hidden <= 6 * 256 * 4 = 6144
 
+// sum over the K-split partials of 4 consecutive elements, in split order; four splits' loads in flight at a time
+DEVINL float4 sum_splits4(const float* base, size_t split_stride, int splits) {
+    float4 t = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    int s = 0;
+    for (; s + 4 <= splits; s += 4) {
+        float4 v[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) v[q] = __ldcg(reinterpret_cast<const float4*>(base + (size_t)(s + q) * split_stride));
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { t.x += v[q].x; t.y += v[q].y; t.z += v[q].z; t.w += v[q].w; }
+    }
+    for (; s < splits; ++s) {
+        const float4 v = __ldcg(reinterpret_cast<const float4*>(base + (size_t)s * split_stride));
+        t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
+    }
+    return t;
+}
+
+// One CTA per row; hidden size a multiple of 4. The row is read once: the pending projection output (its
+// K-split partials added in split order) and the residual stream stay in registers between the two reductions.
 __global__ void __launch_bounds__(kRowsThreads) rows_norm_kernel(const RowsNormArgs a) {
     __shared__ float red[32];
     pdl_wait();
     pdl_launch();
-    const int b = blockIdx.x, tid = threadIdx.x, H = a.H;
+    const int b = blockIdx.x, tid = threadIdx.x, H = a.H, H4 = a.H >> 2;
     const size_t ro = (size_t)b * H;
-    float hv[kRowsMaxJ];
+    float4 hv[kRowsMaxJ];
     if (a.embed != nullptr) {
         uint32_t tok = a.tokens[b];
         if (tok == kInactiveToken) tok = 0;
 #pragma unroll
         for (int j = 0; j < kRowsMaxJ; ++j) {
-            const int i = tid + j * kRowsThreads;
-            hv[j] = i < H ? __uint_as_float((uint32_t)a.embed[(size_t)tok * H + i] << 16) * a.embed_scale : 0.0f;
+            const int i4 = tid + j * kRowsThreads;
+            hv[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (i4 < H4) {
+                const uint2 e = *reinterpret_cast<const uint2*>(a.embed + (size_t)tok * H + 4 * i4);
+                hv[j] = make_float4(bf16lo(e.x) * a.embed_scale, bf16hi(e.x) * a.embed_scale, bf16lo(e.y) * a.embed_scale,
+                                    bf16hi(e.y) * a.embed_scale);
+            }
         }
     } else if (a.raw == nullptr) {
 #pragma unroll
         for (int j = 0; j < kRowsMaxJ; ++j) {
-            const int i = tid + j * kRowsThreads;
-            hv[j] = i < H ? a.h_in[ro + i] : 0.0f;
+            const int i4 = tid + j * kRowsThreads;
+            hv[j] = i4 < H4 ? *reinterpret_cast<const float4*>(a.h_in + ro + 4 * i4) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         }
     } else {
         if (a.px.tp > 1) {
             // wait (bounded) until every rank has published this exchange
             if (tid < a.px.tp) {
-                const unsigned int want = *a.px.seq;
-                const unsigned int* f = a.px.flags[a.px.rank] + tid;
-                unsigned int it = 0;
-                while (ld_acquire_sys(f) < want && ++it < kPeerSpinLimit) {}
-                if (it >= kPeerSpinLimit) atomicExch(a.px.status, 1);
+                if (!peer_flag_wait(a.px.flags[a.px.rank] + tid, *a.px.seq)) atomicExch(a.px.status, 1);
             }
             __syncthreads();
         }
-        // the row is read once: the pending projection output (its K-split partials added in split order) and the
-        // residual stream stay in registers between the two reductions
-        float t[kRowsMaxJ];
+        float4 t[kRowsMaxJ];
         float ss[1] = {0.0f};
+        const size_t split_stride = (size_t)a.B * H;
 #pragma unroll
         for (int j = 0; j < kRowsMaxJ; ++j) {
-            const int i = tid + j * kRowsThreads;
-            float v = 0.0f;
-            if (i < H) {
-                for (int s = 0; s < a.raw_splits; ++s) v += __ldcg(a.raw + ((size_t)s * a.B + b) * H + i);
-                hv[j] = a.h_in[ro + i];
-            } else {
-                hv[j] = 0.0f;
+            const int i4 = tid + j * kRowsThreads;
+            t[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            hv[j] = t[j];
+            if (i4 < H4) {
+                t[j] = sum_splits4(a.raw + ro + 4 * i4, split_stride, a.raw_splits);
+                hv[j] = *reinterpret_cast<const float4*>(a.h_in + ro + 4 * i4);
             }
-            t[j] = v;
-            ss[0] += v * v;
+            ss[0] += t[j].x * t[j].x;
+            ss[0] += t[j].y * t[j].y;
+            ss[0] += t[j].z * t[j].z;
+            ss[0] += t[j].w * t[j].w;
         }
         block_sum<1>(ss, red);
         const float r = 1.0f / sqrtf(ss[0] / (float)H + a.eps);
 #pragma unroll
         for (int j = 0; j < kRowsMaxJ; ++j) {
-            const int i = tid + j * kRowsThreads;
-            if (i < H) hv[j] = (hv[j] + t[j] * r * a.w_post[i]) * a.scalar;
+            const int i4 = tid + j * kRowsThreads;
+            if (i4 < H4) {
+                const float4 w = *reinterpret_cast<const float4*>(a.w_post + 4 * i4);
+                hv[j].x = (hv[j].x + t[j].x * r * w.x) * a.scalar;
+                hv[j].y = (hv[j].y + t[j].y * r * w.y) * a.scalar;
+                hv[j].z = (hv[j].z + t[j].z * r * w.z) * a.scalar;
+                hv[j].w = (hv[j].w + t[j].w * r * w.w) * a.scalar;
+            }
         }
     }
     float ss2[1] = {0.0f};
 #pragma unroll
     for (int j = 0; j < kRowsMaxJ; ++j) {
-        const int i = tid + j * kRowsThreads;
-        if (i < H) {
-            a.h_out[ro + i] = hv[j];
-            ss2[0] += hv[j] * hv[j];
+        const int i4 = tid + j * kRowsThreads;
+        if (i4 < H4) {
+            *reinterpret_cast<float4*>(a.h_out + ro + 4 * i4) = hv[j];
+            ss2[0] += hv[j].x * hv[j].x;
+            ss2[0] += hv[j].y * hv[j].y;
+            ss2[0] += hv[j].z * hv[j].z;
+            ss2[0] += hv[j].w * hv[j].w;
         }
     }
     block_sum<1>(ss2, red);
     const float r2 = 1.0f / sqrtf(ss2[0] / (float)H + a.eps);
 #pragma unroll
     for (int j = 0; j < kRowsMaxJ; ++j) {
-        const int i = tid + j * kRowsThreads;
-        if (i < H) a.x[ro + i] = (uint16_t)f32_to_bf16_bits(hv[j] * r2 * a.w_norm[i]);
+        const int i4 = tid + j * kRowsThreads;
+        if (i4 < H4) {
+            const float4 w = *reinterpret_cast<const float4*>(a.w_norm + 4 * i4);
+            uint2 o;
+            o.x = f32_to_bf16_bits(hv[j].x * r2 * w.x) | (f32_to_bf16_bits(hv[j].y * r2 * w.y) << 16);
+            o.y = f32_to_bf16_bits(hv[j].z * r2 * w.z) | (f32_to_bf16_bits(hv[j].w * r2 * w.w) << 16);
+            *reinterpret_cast<uint2*>(a.x + ro + 4 * i4) = o;
+        }
     }
 }
 
@@ -145,14 +189,13 @@ sum_splits_kernel(const float* part, int splits, size_t n, float* out, const Pee
     __shared__ unsigned int s_last;
     pdl_wait();
     pdl_launch();
-    const size_t i = (size_t)blockIdx.x * kRowsThreads + threadIdx.x;
+    const size_t i = ((size_t)blockIdx.x * kRowsThreads + threadIdx.x) * 4;      // n is a multiple of 4
     if (i < n) {
-        float t = 0.0f;
-        for (int s = 0; s < splits; ++s) t += part[(size_t)s * n + i];
+        const float4 t = sum_splits4(part + i, n, splits);
         if (px.tp > 1) {
-            for (int r = 0; r < px.tp; ++r) px.push[r][i] = t;
+            for (int r = 0; r < px.tp; ++r) *reinterpret_cast<float4*>(px.push[r] + i) = t;
         } else {
-            out[i] = t;
+            *reinterpret_cast<float4*>(out + i) = t;
         }
     }
     if (px.tp > 1) {
@@ -174,20 +217,38 @@ sum_splits_kernel(const float* part, int splits, size_t n, float* out, const Pee
     }
 }
 
+// Failure-path probe (one thread): the two kinds of bounded device-side wait this library uses, each on
+// something that nobody will ever signal, with a small polling budget. The wait must run out, raise the
+// status word and let the kernel return normally; nothing faults and the context stays usable.
+//   kind 1: mbarrier phase that never completes (the wait of the TMA / tcgen05 / attention pipelines)
+//   kind 2: peer flag that never reaches the expected sequence number (tensor-parallel exchange)
+__global__ void wait_probe_kernel(int kind, unsigned int limit, const unsigned int* never_set, int* status) {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x != 0) return;
+    if (kind == 1) {
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (!mbar_wait(&bar, 0, limit)) atomicExch(status, 21);
+    } else {
+        if (!peer_flag_wait(never_set, 1u, limit)) atomicExch(status, 22);
+    }
+}
+
 // x[b, i] = bf16(gelu_tanh(sum_s gu[s, b, i]) * sum_s gu[s, b, I + i]); grid (ceil(I / 256), B)
 __global__ void __launch_bounds__(kRowsThreads)
 geglu_rows_kernel(int B, int I, const float* gu, int splits, uint16_t* x) {
     pdl_wait();
     pdl_launch();
-    const int b = blockIdx.y, i = blockIdx.x * kRowsThreads + threadIdx.x;
+    const int b = blockIdx.y, i = (blockIdx.x * kRowsThreads + threadIdx.x) * 4;          // I is a multiple of 4
     if (i >= I) return;
-    float g = 0.0f, u = 0.0f;
-    for (int s = 0; s < splits; ++s) {
-        const float* row = gu + ((size_t)s * B + b) * (2 * (size_t)I);
-        g += row[i];
-        u += row[I + i];
-    }
-    x[(size_t)b * I + i] = (uint16_t)f32_to_bf16_bits(gelu_mul(g, u));
+    const size_t split_stride = (size_t)B * 2 * (size_t)I;
+    const float* row = gu + (size_t)b * (2 * (size_t)I);
+    const float4 g = sum_splits4(row + i, split_stride, splits);
+    const float4 u = sum_splits4(row + I + i, split_stride, splits);
+    uint2 o;
+    o.x = f32_to_bf16_bits(gelu_mul(g.x, u.x)) | (f32_to_bf16_bits(gelu_mul(g.y, u.y)) << 16);
+    o.y = f32_to_bf16_bits(gelu_mul(g.z, u.z)) | (f32_to_bf16_bits(gelu_mul(g.w, u.w)) << 16);
+    *reinterpret_cast<uint2*>(x + (size_t)b * I + i) = o;
 }
 
 }  // namespace oxg4

@@ -538,8 +538,8 @@ struct oxg4_cache {
           *gu_raw = nullptr, *down_raw = nullptr, *logits = nullptr, *attn_part = nullptr;
     unsigned int *attn_ticket = nullptr, *lm_ticket = nullptr;
     Cand *blk_best = nullptr, *topk_stage = nullptr;
-    uint32_t *best_ids = nullptr, *topk_ids = nullptr, *tp_ids = nullptr;
-    float* tp_scores = nullptr;
+    uint32_t *best_ids = nullptr, *topk_ids = nullptr, *tp_ids = nullptr, *loc_ids = nullptr, *tpk_ids = nullptr;
+    float *tp_scores = nullptr, *loc_scores = nullptr, *tpk_scores = nullptr;   // tensor-parallel top-k exchange
     float *best_scores = nullptr, *topk_scores = nullptr;
     // pinned staging
     uint32_t* h_tokens = nullptr;
@@ -583,10 +583,17 @@ struct oxg4_cache {
 };
 constexpr int kMaxTimeline = 1024;
 
+// Test hook: the n-th device allocation of a cache table from now on reports out-of-memory (0 = off).
+static int g_fail_alloc_after = 0;
+
+extern "C" void oxg4_debug_fail_alloc_after(int32_t n) { g_fail_alloc_after = n; }
+
 template <typename T>
 static int32_t dalloc(oxg4_cache* c, T** p, size_t count, bool zero = true) {
     void* d = nullptr;
     const size_t bytes = std::max<size_t>(count * sizeof(T), 16);
+    if (g_fail_alloc_after > 0 && --g_fail_alloc_after == 0)
+        return fail(OXG4_OOM, "Gemma 4 CUDA error: out of memory (injected by oxg4_debug_fail_alloc_after)");
     CK(cudaMalloc(&d, bytes));
     if (zero) CK(cudaMemset(d, 0, bytes));
     c->owned.push_back(d);
@@ -698,6 +705,10 @@ static int32_t cache_build(oxg4_cache* c) {
     TRY(dalloc(c, &c->topk_stage, (size_t)B * chunks * 64));
     TRY(dalloc(c, &c->tp_ids, (size_t)B * m->tp));
     TRY(dalloc(c, &c->tp_scores, (size_t)B * m->tp));
+    TRY(dalloc(c, &c->loc_ids, (size_t)B * 64));
+    TRY(dalloc(c, &c->loc_scores, (size_t)B * 64));
+    TRY(dalloc(c, &c->tpk_ids, (size_t)B * 64 * m->tp));
+    TRY(dalloc(c, &c->tpk_scores, (size_t)B * 64 * m->tp));
     TRY(dalloc(c, &c->best_ids, B));
     TRY(dalloc(c, &c->best_scores, B));
     TRY(dalloc(c, &c->topk_ids, (size_t)B * 64));
@@ -1396,7 +1407,7 @@ static void run_layers(oxg4_cache* c, Launcher& ln, const RowSet& rs, bool use_t
             launch_attention(ln, c, rs, l, c->qkv_part, s_qkv, c->x_a, true);
             ln.tc("o", c, R, p.wo, nullptr, c->x_a, H, qw, s_o, c->o_part, H, 0);
             const size_t bh = (size_t)R * H;
-            const dim3 sum_grid((unsigned)((bh + kRowsThreads - 1) / kRowsThreads));
+            const dim3 sum_grid((unsigned)((bh / 4 + kRowsThreads - 1) / kRowsThreads));
             PeerExchange none{};
             none.tp = 1;
             const float* xo = peer ? c->px[0].gathered : c->o_raw;        // what the next norm reads
@@ -1419,7 +1430,7 @@ static void run_layers(oxg4_cache* c, Launcher& ln, const RowSet& rs, bool use_t
             n2.x = c->x_h;
             ln.go("norm", rows_norm_kernel, dim3(R), dim3(kRowsThreads), 0, n2);
             ln.tc("gateup", c, R, p.wgate, p.wup, c->x_h, m->I, H, s_gu, c->gu_part, 2 * m->I, 0);
-            ln.go("geglu", geglu_rows_kernel, dim3((m->I + kRowsThreads - 1) / kRowsThreads, R), dim3(kRowsThreads), 0, R,
+            ln.go("geglu", geglu_rows_kernel, dim3((m->I / 4 + kRowsThreads - 1) / kRowsThreads, R), dim3(kRowsThreads), 0, R,
                   m->I, (const float*)c->gu_part, s_gu, c->x_i);
             ln.tc("down", c, R, p.wdown, nullptr, c->x_i, H, m->I, s_down, c->down_part, H, 0);
             if (m->tp > 1) {
@@ -1549,6 +1560,26 @@ static void lm_head(oxg4_cache* c, Launcher& ln, int kind, int top_k, float pena
     };
     if (use_tc) {
         trace_final();
+        const int k = (kind == STEP_TOPK) ? top_k : 1;
+        uint32_t* out_ids = k == 1 ? c->best_ids : c->topk_ids;
+        float* out_scores = k == 1 ? c->best_scores : c->topk_scores;
+        if (m->tp > 1 && kind == STEP_TOPK) {
+            // every rank ranks its own vocabulary slice; N * k (score, id) pairs per sequence cross the links
+            // instead of the [B, V] logits
+            ln.tc("lmhead", c, B, (const char*)m->embed + (size_t)m->v0 * H * m->es, nullptr, x, m->Vloc, H, 1,
+                  c->logits, m->V, m->v0);
+            const int chunks = (m->Vloc + kTopkChunk - 1) / kTopkChunk;
+            ln.go("topk1", topk_stage1_kernel, dim3(chunks, B), dim3(kTopkThreads), 0, (const float*)c->logits, m->V,
+                  m->v0, m->Vloc, (const uint8_t*)c->seen, penalty, k, c->topk_stage);
+            ln.go("topk2", topk_stage2_kernel, dim3(1, B), dim3(kTopkThreads), (size_t)chunks * k * 8,
+                  (const Cand*)c->topk_stage, chunks * k, k, c->loc_ids, c->loc_scores);
+            ln.allgather(c->loc_scores, c->tpk_scores, sizeof(float) * B * k);
+            ln.allgather(c->loc_ids, c->tpk_ids, sizeof(uint32_t) * B * k);
+            ln.go("tp_pick", tp_topk_merge_kernel, dim3(B), dim3(kTopkThreads), 0, B, m->tp, k,
+                  (const float*)c->tpk_scores, (const uint32_t*)c->tpk_ids, out_ids, out_scores);
+            return;
+        }
+        // full logits wanted on the host: every rank fills its vocabulary columns, the sum assembles the rows
         if (m->tp > 1 && cudaMemsetAsync(c->logits, 0, sizeof(float) * (size_t)B * m->V, m->stream) != cudaSuccess)
             ln.status = fail(OXG4_CUDA, "Gemma 4 CUDA error: cudaMemsetAsync failed");
         ln.tc("lmhead", c, B, (const char*)m->embed + (size_t)m->v0 * H * m->es, nullptr, x, m->Vloc, H, 1, c->logits,
@@ -1556,12 +1587,10 @@ static void lm_head(oxg4_cache* c, Launcher& ln, int kind, int top_k, float pena
         ln.allreduce(c->logits, (size_t)B * m->V);
         // top-k over the full logits (k = 1 is the arg-max the greedy loop feeds back)
         const int chunks = (m->V + kTopkChunk - 1) / kTopkChunk;
-        const int k = (kind == STEP_TOPK) ? top_k : 1;
-        ln.go("topk1", topk_stage1_kernel, dim3(chunks, B), dim3(kTopkThreads), 0, (const float*)c->logits, m->V,
-              (const uint8_t*)c->seen, penalty, k, c->topk_stage);
+        ln.go("topk1", topk_stage1_kernel, dim3(chunks, B), dim3(kTopkThreads), 0, (const float*)c->logits, m->V, 0,
+              m->V, (const uint8_t*)c->seen, penalty, k, c->topk_stage);
         ln.go("topk2", topk_stage2_kernel, dim3(1, B), dim3(kTopkThreads), (size_t)chunks * k * 8,
-              (const Cand*)c->topk_stage, chunks * k, k, k == 1 ? c->best_ids : c->topk_ids,
-              k == 1 ? c->best_scores : c->topk_scores);
+              (const Cand*)c->topk_stage, chunks * k, k, out_ids, out_scores);
         return;
     }
     // post-FF norm + residual + layer_scalar of the last layer, final norm, tied LM head with fused arg-max
@@ -1600,7 +1629,7 @@ static void lm_head(oxg4_cache* c, Launcher& ln, int kind, int top_k, float pena
     if (kind == STEP_TOPK && top_k > 1) {
         const int chunks = (m->V + kTopkChunk - 1) / kTopkChunk;
         ln.go("topk1", topk_stage1_kernel, dim3(chunks, B), dim3(kTopkThreads), 0, (const float*)c->logits,
-              m->V, (const uint8_t*)c->seen, penalty, top_k, c->topk_stage);
+              m->V, 0, m->V, (const uint8_t*)c->seen, penalty, top_k, c->topk_stage);
         ln.go("topk2", topk_stage2_kernel, dim3(1, B), dim3(kTopkThreads), (size_t)chunks * top_k * 8,
               (const Cand*)c->topk_stage, chunks * top_k, top_k, c->topk_ids, c->topk_scores);
     }
@@ -2244,6 +2273,26 @@ extern "C" int32_t oxg4_generate(oxg4_model* m, const uint32_t* prompt, int64_t 
     return OXG4_OK;
 }
 
+// Failure-path probe: runs a bounded device-side wait that nothing will ever satisfy, with a polling budget
+// of `spin_limit`, then reports through the same status word and check as every step does.
+extern "C" int32_t oxg4_debug_wait_timeout(oxg4_model* m, oxg4_cache* c, int32_t kind, uint32_t spin_limit) {
+    if (!m || !c || c->m != m) return fail(OXG4_INVALID_ARGUMENT, "null or mismatched handle");
+    if (kind != 1 && kind != 2) return fail(OXG4_INVALID_ARGUMENT, "kind must be 1 (mbarrier) or 2 (peer flag)");
+    if (spin_limit == 0 || spin_limit > 1000000u) return fail(OXG4_INVALID_ARGUMENT, "spin_limit must be 1..1000000");
+    TRY(bind_device(m));
+    // the flag that is waited on is the (zero) attention ticket array: nothing writes it during the probe
+    wait_probe_kernel<<<1, 32, 0, m->stream>>>(kind, spin_limit, c->attn_ticket, c->tc_err);
+    CK(cudaGetLastError());
+    CK(cudaStreamSynchronize(m->stream));
+    int err = 0;
+    CK(cudaMemcpy(&err, c->tc_err, sizeof err, cudaMemcpyDeviceToHost));
+    if (err) {
+        CK(cudaMemset(c->tc_err, 0, sizeof err));
+        return fail(OXG4_TIMEOUT, "%s: a bounded wait ran out (code %d)", err == 21 ? "mbarrier wait" : "peer flag wait", err);
+    }
+    return OXG4_OK;
+}
+
 // ------------------------------------------------------------------------------------------------
 // top-k without any allocation
 // ------------------------------------------------------------------------------------------------
@@ -2285,8 +2334,8 @@ extern "C" int32_t oxg4_topk_noalloc(const float* logits_dev, int32_t rows, int3
     const int chunks = (vocab + kTopkChunk - 1) / kTopkChunk;
     // every scratch entry the merge reads is written by the first stage of the same call, so nothing
     // has to be cleared between calls
-    topk_stage1_kernel<<<dim3(chunks, rows), kTopkThreads, 0, st>>>(logits_dev, vocab, seen_dev, repetition_penalty,
-                                                                    top_k, scratch);
+    topk_stage1_kernel<<<dim3(chunks, rows), kTopkThreads, 0, st>>>(logits_dev, vocab, 0, vocab, seen_dev,
+                                                                    repetition_penalty, top_k, scratch);
     CK(cudaGetLastError());
     topk_stage2_kernel<<<dim3(1, rows), kTopkThreads, (size_t)chunks * top_k * 8, st>>>(scratch, chunks * top_k, top_k,
                                                                                         ids_dev, scores_dev);
@@ -2350,3 +2399,5 @@ extern "C" int32_t oxg4_debug_tc_gemm(const uint16_t* w_host, const uint16_t* x_
     cudaFree(w); cudaFree(x); cudaFree(o); cudaFree(e);
     return s;
 }
+
+#include "tp_group.inl"

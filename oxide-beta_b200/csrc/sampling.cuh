@@ -173,9 +173,11 @@ DEVINL void topk_rounds(float* sc, uint32_t* id, int n, int top_k, Cand* wbest, 
     }
 }
 
-// grid (chunks, B): per-chunk sorted top-k
+// grid (chunks, B): per-chunk sorted top-k over columns [col0, col0 + n_cols) of the [B, ld] logits (a
+// tensor-parallel rank scans its own vocabulary slice); candidate ids are vocabulary ids
 __global__ void __launch_bounds__(kTopkThreads)
-topk_stage1_kernel(const float* logits, int V, const uint8_t* seen, float penalty, int top_k, Cand* stage) {
+topk_stage1_kernel(const float* logits, int ld, int col0, int n_cols, const uint8_t* seen, float penalty, int top_k,
+                   Cand* stage) {
     __shared__ float sc[kTopkChunk];
     __shared__ uint32_t id[kTopkChunk];
     __shared__ Cand wbest[kTopkThreads / 32];
@@ -183,15 +185,43 @@ topk_stage1_kernel(const float* logits, int V, const uint8_t* seen, float penalt
     pdl_launch();
     const int b = blockIdx.y;
     const int start = blockIdx.x * kTopkChunk;
-    const int n = min(kTopkChunk, V - start);
+    const int n = min(kTopkChunk, n_cols - start);
+    const size_t base = (size_t)b * ld + col0 + start;
     for (int i = threadIdx.x; i < n; i += kTopkThreads) {
-        float s = logits[(size_t)b * V + start + i];
-        if (seen != nullptr && penalty > 1.0f && seen[(size_t)b * V + start + i] != 0) s = s >= 0.0f ? s / penalty : s * penalty;
+        float s = logits[base + i];
+        if (seen != nullptr && penalty > 1.0f && seen[base + i] != 0) s = s >= 0.0f ? s / penalty : s * penalty;
         sc[i] = (s == s) ? s : -INFINITY;         // NaN is never selected
-        id[i] = (uint32_t)(start + i);
+        id[i] = (uint32_t)(col0 + start + i);
     }
     __syncthreads();
     topk_rounds(sc, id, n, top_k, wbest, stage + ((size_t)b * gridDim.x + blockIdx.x) * top_k);
+}
+
+// Tensor parallelism: every rank holds the sorted top-k of its vocabulary slice; after an all-gather
+// ([ranks][B][k] scores and ids) one block per sequence merges the ranks * k candidates into the global
+// top-k (descending score, lower id first among equal scores, as everywhere).
+__global__ void __launch_bounds__(kTopkThreads)
+tp_topk_merge_kernel(int B, int ranks, int k, const float* all_scores, const uint32_t* all_ids, uint32_t* ids,
+                     float* scores) {
+    __shared__ float sc[8 * 64];
+    __shared__ uint32_t id[8 * 64];
+    __shared__ Cand wbest[kTopkThreads / 32];
+    __shared__ Cand outc[64];
+    pdl_wait();
+    pdl_launch();
+    const int b = blockIdx.x, n = ranks * k;
+    for (int i = threadIdx.x; i < n; i += kTopkThreads) {
+        const int r = i / k, j = i % k;
+        sc[i] = all_scores[((size_t)r * B + b) * k + j];
+        id[i] = all_ids[((size_t)r * B + b) * k + j];
+    }
+    __syncthreads();
+    topk_rounds(sc, id, n, k, wbest, outc);
+    __syncthreads();
+    for (int r = threadIdx.x; r < k; r += kTopkThreads) {
+        ids[(size_t)b * k + r] = outc[r].i;
+        scores[(size_t)b * k + r] = outc[r].s;
+    }
 }
 
 // grid (1, B): merge of chunks * top_k candidates; dynamic shared memory = n * 8 bytes

@@ -53,9 +53,9 @@ DEVINL void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 // returns false if the phase did not complete within the polling budget
-DEVINL bool mbar_wait(uint64_t* bar, uint32_t parity) {
+DEVINL bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = kTcSpinLimit) {
     const uint32_t addr = smem_u32(bar);
-    for (uint32_t i = 0; i < kTcSpinLimit; ++i) {
+    for (uint32_t i = 0; i < limit; ++i) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"

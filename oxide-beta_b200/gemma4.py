@@ -118,6 +118,32 @@ def _ptr(a: np.ndarray):
     return a.ctypes.data_as(C.c_void_p)
 
 
+def _native_config(config: "Gemma4TextConfig", weight_dtype: int, norm_weight_offset: int, tp_rank: int, tp_size: int):
+    """oxg4_config for `config` plus the arrays it points into (keep them alive while it is used)."""
+    L = config.num_hidden_layers
+    sliding = np.array([1 if t == "sliding_attention" else 0 for t in config.layer_types], dtype=np.int32)
+    rot = np.zeros(L, dtype=np.int32)
+    theta = np.zeros(L, dtype=np.float32)
+    factor = np.zeros(L, dtype=np.float32)
+    for l, t in enumerate(config.layer_types):
+        rp = config.rope_parameters.get(t)
+        if rp is None:
+            raise Oxg4Error(2, f"RoPE parameters for {t} missing")
+        hd = config.head_dim if sliding[l] else config.global_head_dim
+        # mod.rs:404-405: rotary_dim = (partial_rotary_factor * head_dim as f32) as usize
+        rot[l] = int(np.float32(rp.get("partial_rotary_factor", 1.0)) * np.float32(hd))
+        theta[l] = rp.get("rope_theta", 10000.0)
+        factor[l] = rp.get("factor", 1.0)
+    c = N.Config(
+        config.vocab_size, config.hidden_size, L, config.num_attention_heads, config.num_key_value_heads,
+        config.head_dim, config.global_head_dim, config.intermediate_size, config.sliding_window,
+        config.rms_norm_eps, float(config.final_logit_softcapping or 0.0), weight_dtype, norm_weight_offset,
+        sliding.ctypes.data_as(C.POINTER(C.c_int32)), rot.ctypes.data_as(C.POINTER(C.c_int32)),
+        theta.ctypes.data_as(C.POINTER(C.c_float)), factor.ctypes.data_as(C.POINTER(C.c_float)),
+        tp_rank, tp_size)
+    return c, (sliding, rot, theta, factor)
+
+
 class Gemma4CudaCacheTable:
     """Owner of an oxg4_cache handle: KV pages, device decode state and the captured step graphs."""
 
@@ -182,28 +208,7 @@ class Gemma4CudaState:
     def __init__(self, config: Gemma4TextConfig, device_index: int = 0, weight_dtype: int = N.BF16,
                  norm_weight_offset: int = 0, tp_rank: int = 0, tp_size: int = 1):
         self.config = config
-        L = config.num_hidden_layers
-        sliding = np.array([1 if t == "sliding_attention" else 0 for t in config.layer_types], dtype=np.int32)
-        rot = np.zeros(L, dtype=np.int32)
-        theta = np.zeros(L, dtype=np.float32)
-        factor = np.zeros(L, dtype=np.float32)
-        for l, t in enumerate(config.layer_types):
-            rp = config.rope_parameters.get(t)
-            if rp is None:
-                raise Oxg4Error(2, f"RoPE parameters for {t} missing")
-            hd = config.head_dim if sliding[l] else config.global_head_dim
-            # mod.rs:404-405: rotary_dim = (partial_rotary_factor * head_dim as f32) as usize
-            rot[l] = int(np.float32(rp.get("partial_rotary_factor", 1.0)) * np.float32(hd))
-            theta[l] = rp.get("rope_theta", 10000.0)
-            factor[l] = rp.get("factor", 1.0)
-        self._keep = (sliding, rot, theta, factor)
-        c = N.Config(
-            config.vocab_size, config.hidden_size, L, config.num_attention_heads, config.num_key_value_heads,
-            config.head_dim, config.global_head_dim, config.intermediate_size, config.sliding_window,
-            config.rms_norm_eps, float(config.final_logit_softcapping or 0.0), weight_dtype, norm_weight_offset,
-            sliding.ctypes.data_as(C.POINTER(C.c_int32)), rot.ctypes.data_as(C.POINTER(C.c_int32)),
-            theta.ctypes.data_as(C.POINTER(C.c_float)), factor.ctypes.data_as(C.POINTER(C.c_float)),
-            tp_rank, tp_size)
+        c, self._keep = _native_config(config, weight_dtype, norm_weight_offset, tp_rank, tp_size)
         self._h = C.c_void_p()
         self.weight_dtype = weight_dtype
         N.check(N.lib().oxg4_model_create(C.byref(c), device_index, C.byref(self._h)))
@@ -361,6 +366,109 @@ class Gemma4CudaState:
                 ms = N.lib().oxg4_profile_ms(self._h, k.encode())
                 out[k] = ms * n if totals else ms
         return out
+
+
+class Gemma4TpCacheTable:
+    """Cache tables of every rank of a Gemma4TpState (oxg4_tp_cache)."""
+
+    def __init__(self, state: "Gemma4TpState", max_sequence, batch: int = 1, page_tokens: int = 256,
+                 kv_dtype: int = N.F32):
+        ms = np.ascontiguousarray(np.broadcast_to(np.asarray(max_sequence, dtype=np.int32), (batch,)))
+        self._state = state
+        self.batch = batch
+        self._h = C.c_void_p()
+        N.check(N.lib().oxg4_tp_cache_create(state._h, batch, ms.ctypes.data_as(C.POINTER(C.c_int32)), page_tokens,
+                                             kv_dtype, C.byref(self._h)))
+
+    def __del__(self):
+        self.close()
+
+    def close(self):
+        if getattr(self, "_h", None) and self._h.value:
+            N.lib().oxg4_tp_cache_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def position(self, b: int = 0):
+        return N.lib().oxg4_tp_cache_position(self._h, b)
+
+
+class Gemma4TpState:
+    """A tensor-parallel Gemma4CudaState driven by ONE host thread (oxg4_tp_model): one model per device in
+    `device_ordinals`, worker threads inside the library. Same calls as Gemma4CudaState."""
+
+    def __init__(self, config: Gemma4TextConfig, device_ordinals: Sequence[int], weight_dtype: int = N.BF16,
+                 norm_weight_offset: int = 0):
+        self.config = config
+        c, self._keep = _native_config(config, weight_dtype, norm_weight_offset, 0, len(device_ordinals))
+        dev = np.ascontiguousarray(device_ordinals, dtype=np.int32)
+        self._h = C.c_void_p()
+        N.check(N.lib().oxg4_tp_model_create(C.byref(c), dev.ctypes.data_as(C.POINTER(C.c_int32)), dev.size,
+                                             C.byref(self._h)))
+
+    @classmethod
+    def load(cls, config: Gemma4TextConfig, weights: Iterable, device_ordinals: Sequence[int],
+             weight_dtype: int = N.BF16, **kw) -> "Gemma4TpState":
+        st = cls(config, device_ordinals, weight_dtype, **kw)
+        for name, a in weights:
+            st.upload(name, a)
+        st.finalize()
+        return st
+
+    def upload(self, name: str, array):
+        a = np.ascontiguousarray(array)
+        dt = N.BF16 if a.dtype == np.uint16 else N.F32
+        shape = (C.c_int64 * a.ndim)(*a.shape)
+        N.check(N.lib().oxg4_tp_model_upload(self._h, name.encode(), dt, shape, a.ndim, _ptr(a), a.nbytes))
+
+    def finalize(self):
+        N.check(N.lib().oxg4_tp_model_finalize(self._h))
+
+    def __del__(self):
+        self.close()
+
+    def close(self):
+        if getattr(self, "_h", None) and self._h.value:
+            N.lib().oxg4_tp_model_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def weight_bytes(self):
+        return N.lib().oxg4_tp_weight_bytes(self._h)
+
+    def new_cache_table(self, max_sequence, batch: int = 1, page_tokens: int = 256, kv_dtype: int = N.F32):
+        return Gemma4TpCacheTable(self, max_sequence, batch, page_tokens, kv_dtype)
+
+    def prefill_prompt(self, tokens, table: Gemma4TpCacheTable, lens=None, want_logits=True):
+        t = _as_u32(tokens).reshape(-1)
+        ln = np.ascontiguousarray([t.size] if lens is None else lens, dtype=np.int32)
+        out = np.empty((table.batch, self.config.vocab_size), dtype=np.float32) if want_logits else None
+        N.check(N.lib().oxg4_tp_prefill(self._h, table._h, _ptr(t), _ptr(ln), None if out is None else _ptr(out)))
+        if out is None:
+            return None
+        return out[0] if table.batch == 1 else out
+
+    def decode_token(self, token, table: Gemma4TpCacheTable):
+        t = _as_u32(np.atleast_1d(token))
+        out = np.empty((table.batch, self.config.vocab_size), dtype=np.float32)
+        N.check(N.lib().oxg4_tp_decode_logits(self._h, table._h, _ptr(t), _ptr(out)))
+        return out[0] if table.batch == 1 else out
+
+    def decode_topk(self, token, table: Gemma4TpCacheTable, top_k: int, repetition_penalty: float, mark_seen: bool):
+        t = _as_u32(np.atleast_1d(token))
+        k = min(max(int(top_k), 1), 64, self.config.vocab_size)
+        ids = np.zeros((table.batch, k), dtype=np.uint32)
+        scores = np.zeros((table.batch, k), dtype=np.float32)
+        N.check(N.lib().oxg4_tp_decode_topk(self._h, table._h, _ptr(t), k, float(repetition_penalty),
+                                            int(bool(mark_seen)), _ptr(ids), _ptr(scores)))
+        if table.batch == 1:
+            return [(int(i), float(s)) for i, s in zip(ids[0], scores[0])]
+        return ids, scores
+
+    def decode_greedy(self, first_tokens, table: Gemma4TpCacheTable, steps: int):
+        t = _as_u32(np.atleast_1d(first_tokens))
+        out = np.zeros((steps, table.batch), dtype=np.uint32)
+        ms = C.c_float(0)
+        N.check(N.lib().oxg4_tp_decode_greedy(self._h, table._h, _ptr(t), steps, _ptr(out), C.byref(ms)))
+        return out, ms.value
 
 
 def tp_shard(name: str, rows: int, cols: int, tp_rank: int, tp_size: int, cfg: "Gemma4TextConfig"):

@@ -164,3 +164,25 @@ def test_workload_table_matches_specification():
     assert len(names) == 2 + 14 * 26
     lens = syn.ragged_lengths(64, 1024, 32768, seed=2)
     assert lens.min() >= 1024 and lens.max() <= 32768
+
+
+def test_tp_group_create_fails_loudly_without_a_device_or_on_bad_arguments():
+    """The single-process tensor-parallel handle reports its workers' failures to the calling thread."""
+    import ctypes as C
+    import torch
+    N = pkg._native
+    cfg = pkg.Gemma4TextConfig(syn.workload("c1")["cfg"])
+    from importlib import import_module
+    g4 = import_module("oxide-beta_b200.gemma4")
+    c, keep = g4._native_config(cfg, pkg.F32, 0, 0, 2)
+    h = C.c_void_p()
+    dev = (C.c_int32 * 2)(0, 0)
+    assert N.lib().oxg4_tp_model_create(C.byref(c), dev, 2, C.byref(h)) == 2          # same device twice
+    assert b"own device" in N.lib().oxg4_last_error()
+    dev = (C.c_int32 * 3)(0, 1, 2)
+    assert N.lib().oxg4_tp_model_create(C.byref(c), dev, 3, C.byref(h)) == 2          # tp must be 1, 2, 4 or 8
+    if not torch.cuda.is_available():
+        dev = (C.c_int32 * 1)(0)
+        st = N.lib().oxg4_tp_model_create(C.byref(c), dev, 1, C.byref(h))
+        assert N.STATUS_NAMES[st] == "CUDA" and not h.value
+        assert b"rank 0" in N.lib().oxg4_last_error() and b"no CPU path" in N.lib().oxg4_last_error()

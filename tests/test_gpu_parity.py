@@ -453,3 +453,44 @@ def test_device_sampled_loop_equals_host_sampling_with_softcap(capped, seed, top
     dev_ids, state, _ = gpu.decode_sampled(first, t_dev, steps, top_k, temperature, top_p, penalty, [seed])
     assert dev_ids.ravel().tolist() == host_ids
     assert int(state[0]) == int(rnd[0])
+
+
+# ---- failure paths, made on the host: no GPU fault, trap or hang ------------------------------------------
+
+@pytest.mark.parametrize("kind", [1, 2])
+def test_bounded_wait_runs_out_and_reports_timeout(c1, kind):
+    """A device-side wait on something nobody signals (kind 1: an mbarrier phase, the wait of the TMA /
+    tcgen05 / attention pipelines; kind 2: a tensor-parallel peer flag) with a small polling budget: the
+    kernel returns, the status word is raised, the call returns OXG4_TIMEOUT, and the next calls work."""
+    cfg, gpu, oracle = c1
+    N = pkg._native
+    table = gpu.new_cache_table(16, kv_dtype=pkg.F32)
+    before = gpu.decode_token(5, table)
+    st = N.lib().oxg4_debug_wait_timeout(gpu._h, table._h, kind, 2000)
+    assert N.STATUS_NAMES[st] == "TIMEOUT"
+    assert b"bounded wait ran out" in N.lib().oxg4_last_error()
+    table.reset()
+    after = gpu.decode_token(5, table)                    # the context and the table are still usable
+    assert np.array_equal(before, after)
+    assert N.lib().oxg4_debug_wait_timeout(gpu._h, table._h, 3, 2000) == 2      # INVALID_ARGUMENT
+
+
+def test_cache_create_out_of_memory_leaks_nothing(c1):
+    """An allocation that fails in the middle of oxg4_cache_create (injected on the host): OXG4_OOM comes
+    back, no handle is produced and the driver's free-memory figure returns to what it was."""
+    import torch
+    cfg, gpu, oracle = c1
+    N = pkg._native
+    gpu.new_cache_table(16, kv_dtype=pkg.F32).close()     # warm: kernels loaded, pools of the driver settled
+    torch.cuda.synchronize()
+    free0 = torch.cuda.mem_get_info()[0]
+    for nth in (1, 7, 23):
+        N.lib().oxg4_debug_fail_alloc_after(nth)
+        with pytest.raises(pkg.Oxg4Error) as e:
+            gpu.new_cache_table(16, kv_dtype=pkg.F32)
+        assert e.value.kind == "OOM"
+        N.lib().oxg4_debug_fail_alloc_after(0)
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free0, nth
+    t = gpu.new_cache_table(16, kv_dtype=pkg.F32)         # and creation works again
+    assert t.position() == 0

@@ -149,10 +149,50 @@ WORKER_GPU = textwrap.dedent("""
 
 
 @pytest.mark.gpu
-def test_tp2_matches_single_gpu():
+@pytest.mark.parametrize("world", [2, 4])
+def test_tp_matches_single_gpu(world, tmp_path):
+    """One process per rank (the launcher form): TP-2 and TP-4 against the single-GPU model."""
     import torch
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
-    r = _torchrun(WORKER_GPU, 2, extra_env={"NCCL_NVLS_ENABLE": "0"}, timeout=900)
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    r = _torchrun(WORKER_GPU, world, tmp_path, extra_env={"NCCL_NVLS_ENABLE": "0"}, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-6000:]
     assert r.stdout.count("tp parity ok") == 6
+    print(r.stdout[-1200:])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tp", [2, 4])
+def test_tp_single_process_group_matches_single_gpu(tp):
+    """The group handle (oxg4_tp_model): one host thread drives all ranks through worker threads inside the
+    library, as the reference's single-threaded generate loop would. f32: logits <= 1e-3 against the
+    single-GPU model, greedy tokens and top-k lists identical; BF16 (tcgen05 path, batch 9): <= 2e-2."""
+    import torch
+    if torch.cuda.device_count() < tp:
+        pytest.skip(f"needs {tp} GPUs")
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    cfg = syn._cfg(2048, 256, 3, 8, 4, 64, 512, 16, ["sliding_attention", "full_attention", "sliding_attention"])
+    for dtype, kv, tol, B in (("f32", pkg.F32, 1e-3, 3), ("bf16", pkg.BF16, 2e-2, 9)):
+        weights = list(syn.generate_weights(cfg, seed=0, dtype=dtype, norm_jitter=0.1))
+        wd = pkg.F32 if dtype == "f32" else pkg.BF16
+        group = pkg.Gemma4TpState.load(pkg.Gemma4TextConfig(cfg), weights, list(range(tp)), wd)
+        one = pkg.Gemma4CudaState.load(pkg.Gemma4TextConfig(cfg), weights, 0, wd)
+        lens = [3 + (5 * b) % 17 for b in range(B)]
+        lens[0] = 40
+        prompts = np.concatenate([syn.prompt_ids(cfg["vocab_size"], n, seed=70 + b) for b, n in enumerate(lens)])
+        tg = group.new_cache_table([60] * B, batch=B, page_tokens=16, kv_dtype=kv)
+        t1 = one.new_cache_table([60] * B, batch=B, page_tokens=16, kv_dtype=kv)
+        lg = group.prefill_prompt(prompts, tg, lens=lens)
+        l1 = one.prefill_prompt(prompts, t1, lens=lens)
+        assert np.abs(lg - l1).max() <= tol
+        og, _ = group.decode_greedy(l1.argmax(-1).astype(np.uint32), tg, 8)
+        o1, _ = one.decode_greedy(l1.argmax(-1).astype(np.uint32), t1, 8)
+        if dtype == "f32":
+            assert np.array_equal(og, o1)
+            topg = group.decode_topk(o1[-1], tg, 5, 1.2, True)
+            top1 = one.decode_topk(o1[-1], t1, 5, 1.2, True)
+            assert np.array_equal(topg[0], top1[0]) and np.abs(topg[1] - top1[1]).max() <= tol
+        assert [tg.position(b) for b in range(B)] == [t1.position(b) for b in range(B)]
+        del tg, t1
+        group.close()
+        one.close()
