@@ -98,12 +98,17 @@ struct oxg4_model {
     cudaStream_t stream = nullptr;
     int num_sms = 148;
     bool use_pdl = true;
-    bool far_prefetch = false;
+    int far_prefetch = 0;         // bit mask: which kernels pull a LATER kernel's weights into L2 (1 qkv, 2 attention, 4 gate/up, 8 down)
+    int far_prefetch_mb = 64;     // most MiB one kernel prefetches that way
     int pf_cap_kb = 128;          // KiB of its own weight block a CTA pulls into L2 before the dependency wait
     int pf_cap_gu_kb = -1, pf_cap_down_kb = -1;   // overrides for the gate/up and down projections (-1: pf_cap_kb)
     bool timeline = false;        // OXG4_TIMELINE: kernels stamp the global timer into the cache's buffer     // pull later kernels' weights into L2 during latency-bound kernels
     bool finalized = false;
     std::map<std::string, Tensor> tensors;
+    // upload path: two pinned staging slots; the host copy into one overlaps the DMA out of the other
+    void* stage[2] = {nullptr, nullptr};
+    cudaEvent_t stage_ev[2] = {nullptr, nullptr};
+    int stage_next = 0;
     std::vector<LayerPlan> layers;
     const void* embed = nullptr;
     const float* final_norm = nullptr;
@@ -115,6 +120,7 @@ struct oxg4_model {
     long long launches = 0;
     int tp = 1, tp_rank = 0;
     void* comm = nullptr;         // ncclComm_t once oxg4_model_tp_init has run
+    std::vector<struct oxg4_cache*> caches;     // live cache tables: destroyed with the model if the caller has not
     std::map<std::string, ProfileSlot> profile;
     bool profiling = false;
     std::vector<std::pair<std::string, std::pair<cudaEvent_t, cudaEvent_t>>> prof_events;
@@ -221,7 +227,8 @@ extern "C" int32_t oxg4_model_create(const oxg4_config* c, int32_t device, oxg4_
     if (const char* e = getenv("OXG4_PREFETCH_KB")) m->pf_cap_kb = std::max(0, atoi(e));
     if (const char* e = getenv("OXG4_PREFETCH_KB_GATEUP")) m->pf_cap_gu_kb = std::max(0, atoi(e));
     if (const char* e = getenv("OXG4_PREFETCH_KB_DOWN")) m->pf_cap_down_kb = std::max(0, atoi(e));
-    m->far_prefetch = getenv("OXG4_FAR_PREFETCH") != nullptr;   // measured slower on B200: off by default
+    if (const char* e = getenv("OXG4_FAR_PREFETCH")) m->far_prefetch = atoi(e);
+    if (const char* e = getenv("OXG4_FAR_PREFETCH_MB")) m->far_prefetch_mb = std::max(1, atoi(e));
     if (cudaSetDevice(device) != cudaSuccess) { delete m; return fail(OXG4_CUDA, "Gemma 4 CUDA error: cudaSetDevice"); }
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, device) == cudaSuccess) m->num_sms = prop.multiProcessorCount;
@@ -234,19 +241,26 @@ extern "C" int32_t oxg4_model_create(const oxg4_config* c, int32_t device, oxg4_
     return OXG4_OK;
 }
 
+extern "C" void oxg4_cache_destroy(oxg4_cache* c);
+
 extern "C" void oxg4_model_destroy(oxg4_model* m) {
     if (!m) return;
     cudaSetDevice(m->device);
     cudaStreamSynchronize(m->stream);
+    while (!m->caches.empty()) oxg4_cache_destroy(m->caches.back());   // a table points into its model: it goes first
     for (auto& kv : m->tensors) cudaFree(kv.second.d);
     for (auto& l : m->layers) cudaFree(l.inv_freq);
+    for (int i = 0; i < 2; ++i) {
+        if (m->stage[i]) cudaFreeHost(m->stage[i]);
+        if (m->stage_ev[i]) cudaEventDestroy(m->stage_ev[i]);
+    }
     if (m->comm) nccl().CommDestroy(m->comm);
     cudaStreamDestroy(m->stream);
     delete m;
 }
 
 // which slice of a checkpoint tensor a tensor-parallel rank keeps
-enum ShardKind { SH_FULL, SH_ROWS, SH_COLS, SH_ROWS_HEADS_Q, SH_ROWS_HEADS_KV, SH_COLS_HEADS_Q };
+constexpr size_t kStageBytes = 32u << 20;      // one pinned staging slot of the upload path
 
 extern "C" int32_t oxg4_model_upload(oxg4_model* m, const char* name, int32_t dtype, const int64_t* shape,
                                      int32_t rank, const void* data, size_t bytes) {
@@ -296,9 +310,39 @@ extern "C" int32_t oxg4_model_upload(oxg4_model* m, const char* name, int32_t dt
         t.shape = {sh.nrows, sh.ncols};
         t.bytes = (size_t)sh.nrows * sh.ncols * dst_es;
         CK(cudaMalloc(&t.d, t.bytes));
-        const char* s0 = (const char*)src + ((size_t)sh.row0 * shape[1] + sh.col0) * dst_es;
-        CK(cudaMemcpy2D(t.d, (size_t)sh.ncols * dst_es, s0, (size_t)shape[1] * dst_es, (size_t)sh.ncols * dst_es,
-                        (size_t)sh.nrows, cudaMemcpyHostToDevice));   // synchronous: done on return
+        // Loader fast path (stands in for the synchronous per-tensor copies of gemma4_cuda/mod.rs:236-279): the
+        // caller's bytes (an mmap view of the checkpoint, pageable) are copied block by block into one of two
+        // pinned slots and leave it by asynchronous DMA, so the host copy of block i + 1 overlaps the transfer of
+        // block i. The SOURCE is no longer needed once the call returns (every byte is in pinned memory or on
+        // the device), which is what SafeTensorLoader::with_view requires; the device is synchronised once, in
+        // oxg4_model_finalize.
+        const size_t row_b = (size_t)sh.ncols * dst_es, src_row_b = (size_t)shape[1] * dst_es;
+        const size_t rows_per_block = std::max<size_t>(1, kStageBytes / row_b);
+        if (row_b > kStageBytes) {
+            // a single row wider than a slot: plain synchronous copy
+            const char* s0 = (const char*)src + ((size_t)sh.row0 * shape[1] + sh.col0) * dst_es;
+            CK(cudaMemcpy2D(t.d, row_b, s0, src_row_b, row_b, (size_t)sh.nrows, cudaMemcpyHostToDevice));
+        } else {
+            for (size_t r0 = 0; r0 < (size_t)sh.nrows; r0 += rows_per_block) {
+                const size_t nr = std::min(rows_per_block, (size_t)sh.nrows - r0);
+                const int slot = m->stage_next;
+                m->stage_next ^= 1;
+                if (!m->stage[slot]) {
+                    CK(cudaMallocHost(&m->stage[slot], kStageBytes));
+                    CK(cudaEventCreateWithFlags(&m->stage_ev[slot], cudaEventDisableTiming));
+                } else {
+                    CK(cudaEventSynchronize(m->stage_ev[slot]));      // the slot's previous DMA has drained
+                }
+                const char* s0 = (const char*)src + ((size_t)(sh.row0 + r0) * shape[1] + sh.col0) * dst_es;
+                if (row_b == src_row_b) {
+                    memcpy(m->stage[slot], s0, nr * row_b);
+                } else {
+                    for (size_t r = 0; r < nr; ++r) memcpy((char*)m->stage[slot] + r * row_b, s0 + r * src_row_b, row_b);
+                }
+                CK(cudaMemcpyAsync((char*)t.d + r0 * row_b, m->stage[slot], nr * row_b, cudaMemcpyHostToDevice, m->stream));
+                CK(cudaEventRecord(m->stage_ev[slot], m->stream));
+            }
+        }
     }
     auto it = m->tensors.find(n);
     if (it != m->tensors.end()) { cudaFree(it->second.d); m->tensors.erase(it); }
@@ -378,6 +422,11 @@ extern "C" int32_t oxg4_model_finalize(oxg4_model* m) {
     if (!m) return fail(OXG4_INVALID_ARGUMENT, "null model");
     if (m->finalized) return OXG4_OK;
     TRY(bind_device(m));
+    CK(cudaStreamSynchronize(m->stream));          // every staged upload has landed
+    for (int i = 0; i < 2; ++i) {
+        if (m->stage[i]) { cudaFreeHost(m->stage[i]); m->stage[i] = nullptr; }
+        if (m->stage_ev[i]) { cudaEventDestroy(m->stage_ev[i]); m->stage_ev[i] = nullptr; }
+    }
     const oxg4_config& c = m->cfg;
     const int L = c.num_hidden_layers, H = m->H, D = m->D;
     const int64_t QW = (int64_t)m->Nq * D, KW = (int64_t)m->Nkv * D;
@@ -787,6 +836,10 @@ static int32_t cache_build(oxg4_cache* c) {
 
 extern "C" void oxg4_cache_destroy(oxg4_cache* c) {
     if (!c) return;
+    {
+        auto& live = c->m->caches;
+        live.erase(std::remove(live.begin(), live.end(), c), live.end());
+    }
     cudaSetDevice(c->m->device);
     cudaStreamSynchronize(c->m->stream);
     for (auto& g : c->graphs) {
@@ -826,6 +879,7 @@ extern "C" int32_t oxg4_cache_create(oxg4_model* m, int32_t batch, const int32_t
     c->kv_dtype = kv_dtype;
     c->max_seq.assign(max_seq, max_seq + batch);
     c->pos_host.assign(batch, 0);
+    m->caches.push_back(c);
     int32_t s = cache_build(c);
     if (s != OXG4_OK) {
         std::string keep = g_err;
@@ -1338,9 +1392,11 @@ static void launch_attention(Launcher& ln, oxg4_cache* c, const RowSet& rs, int 
     a.part = c->attn_part;
     a.ticket = c->attn_ticket;
     a.out = c->attn_out;
-    if (m->far_prefetch && !rs.chunk) {
+    if ((m->far_prefetch & 2) && !rs.chunk) {
+        // the attention kernel of a one-sequence step moves almost no bytes: HBM is idle, so it pulls the up
+        // projection's weights (or as much as the cap allows) into L2 for the kernel after next
         a.pf_ptr = p.wup;
-        a.pf_bytes = (unsigned long long)m->I * m->H * m->es;
+        a.pf_bytes = std::min<unsigned long long>((unsigned long long)m->I * m->H * m->es, (unsigned long long)m->far_prefetch_mb << 20);
     }
     a.ts = ln.ts();
     a.ts_mid = ln.ts_base ? ln.ts_base + 4 * (size_t)(kMaxTimeline - 1 - l) : nullptr;   // extra stamps, from the end of the buffer
@@ -1457,11 +1513,9 @@ static void run_layers(oxg4_cache* c, Launcher& ln, const RowSet& rs, bool use_t
                 a.scalar = m->layers[l - 1].layer_scalar;
             }
             a.out = c->qkv_raw;
-            if (m->far_prefetch) {
+            if (m->far_prefetch & 1) {
                 a.pf_ptr[0] = p.wo;
                 a.pf_bytes[0] = (unsigned long long)m->p_o.N * m->p_o.K * m->es;
-                a.pf_ptr[1] = p.wgate;
-                a.pf_bytes[1] = (unsigned long long)m->I * H * m->es;
             }
             auto copy_trace = [&]() {
                 if (tr && ln.status == OXG4_OK &&
@@ -1501,9 +1555,9 @@ static void run_layers(oxg4_cache* c, Launcher& ln, const RowSet& rs, bool use_t
             a.scalar = 1.0f;
             a.w_norm = p.pre_ff_ln;
             a.out = c->gu_raw;
-            if (m->far_prefetch) {
+            if (m->far_prefetch & 4) {
                 a.pf_ptr[0] = p.wdown;
-                a.pf_bytes[0] = (unsigned long long)m->p_down.N * m->p_down.K * m->es;
+                a.pf_bytes[0] = std::min<unsigned long long>((unsigned long long)m->p_down.N * m->p_down.K * m->es, (unsigned long long)m->far_prefetch_mb << 20);
             }
             launch_gemv(ln, "gateup", c, R, a, m->p_gateup, PRO_NORM, EPI_GATEUP);
         }
@@ -1512,7 +1566,7 @@ static void run_layers(oxg4_cache* c, Launcher& ln, const RowSet& rs, bool use_t
             a.W0 = p.wdown;
             a.in = c->gu_raw;
             a.out = c->down_raw;
-            if (m->far_prefetch) {
+            if (m->far_prefetch & 8) {
                 if (l + 1 < L) {
                     a.pf_ptr[0] = m->layers[l + 1].wqkv;
                     a.pf_bytes[0] = (unsigned long long)m->p_qkv.N * m->p_qkv.K * m->es;

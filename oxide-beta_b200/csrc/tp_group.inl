@@ -77,10 +77,13 @@ private:
 
 }  // namespace
 
+struct oxg4_tp_cache;
+
 struct oxg4_tp_model {
     int tp = 1;
     std::vector<oxg4_model*> rank;
     RankWorkers* workers = nullptr;
+    std::vector<oxg4_tp_cache*> caches;           // live tables: destroyed with the group if the caller has not
 };
 
 struct oxg4_tp_cache {
@@ -90,8 +93,11 @@ struct oxg4_tp_cache {
     std::vector<std::vector<uint32_t>> scratch_u;
 };
 
+extern "C" void oxg4_tp_cache_destroy(oxg4_tp_cache* c);
+
 extern "C" void oxg4_tp_model_destroy(oxg4_tp_model* g) {
     if (!g) return;
+    while (!g->caches.empty()) oxg4_tp_cache_destroy(g->caches.back());
     if (g->workers) {
         g->workers->run([&](int r) {
             if (g->rank[r]) oxg4_model_destroy(g->rank[r]);
@@ -154,6 +160,10 @@ extern "C" int64_t oxg4_tp_weight_bytes(const oxg4_tp_model* g) {
 
 extern "C" void oxg4_tp_cache_destroy(oxg4_tp_cache* c) {
     if (!c) return;
+    {
+        auto& live = c->g->caches;
+        live.erase(std::remove(live.begin(), live.end(), c), live.end());
+    }
     c->g->workers->run([&](int r) {
         if (c->rank[r]) oxg4_cache_destroy(c->rank[r]);
         return OXG4_OK;
@@ -178,6 +188,7 @@ extern "C" int32_t oxg4_tp_cache_create(oxg4_tp_model* g, int32_t batch, const i
         g_err = keep;
         return s;
     }
+    g->caches.push_back(c);
     *out = c;
     return OXG4_OK;
 }

@@ -160,8 +160,12 @@ class Gemma4CudaCacheTable:
         self.close()
 
     def close(self):
+        # Finalisers of objects caught in a reference cycle run in no particular order. If the state went first,
+        # oxg4_model_destroy has already destroyed this table with it: only forget the handle.
         if getattr(self, "_h", None) and self._h.value:
-            N.lib().oxg4_cache_destroy(self._h)
+            st = getattr(self, "_state", None)
+            if st is not None and getattr(st, "_h", None) and st._h.value:
+                N.lib().oxg4_cache_destroy(self._h)
             self._h = C.c_void_p()
 
     def _info(self) -> N.CacheInfo:
@@ -385,7 +389,9 @@ class Gemma4TpCacheTable:
 
     def close(self):
         if getattr(self, "_h", None) and self._h.value:
-            N.lib().oxg4_tp_cache_destroy(self._h)
+            st = getattr(self, "_state", None)
+            if st is not None and getattr(st, "_h", None) and st._h.value:
+                N.lib().oxg4_tp_cache_destroy(self._h)
             self._h = C.c_void_p()
 
     def position(self, b: int = 0):

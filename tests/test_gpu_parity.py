@@ -494,3 +494,18 @@ def test_cache_create_out_of_memory_leaks_nothing(c1):
         assert torch.cuda.mem_get_info()[0] == free0, nth
     t = gpu.new_cache_table(16, kv_dtype=pkg.F32)         # and creation works again
     assert t.position() == 0
+
+
+def test_state_closed_before_its_table_does_not_crash():
+    """Finalisers of objects in a reference cycle run in no particular order: a model that goes first takes
+    its live cache tables with it, and the table's own close then only forgets the handle."""
+    cfg = small_cfg(hidden=64, layers=1, heads=2, kv_heads=1, head_dim=64, inter=128, vocab=300, window=8,
+                    layer_types=["full_attention"])
+    gpu, _ = build_pair(cfg, "f32", kv_bf16=False, want_oracle=False)
+    t1 = gpu.new_cache_table(8, kv_dtype=pkg.F32)
+    t2 = gpu.new_cache_table(8, kv_dtype=pkg.BF16)
+    gpu.decode_token(3, t1)
+    t2.close()
+    gpu.close()
+    t1.close()
+    t1.close()
