@@ -164,12 +164,14 @@ DEVINL void attn_cta(const AttnArgs& a, float* sm, const int s, const int kvh, c
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int half = D / 2;
 
-    if (tid == 0 && a.pf_bytes) {
+    if (a.pf_bytes) {
+        // one 32 KiB bulk prefetch per thread at most (a single thread issuing dozens of them would sit on the
+        // CTA's critical path for microseconds)
         constexpr unsigned long long PIECE = 32 * 1024;
         const unsigned long long npieces = (a.pf_bytes + PIECE - 1) / PIECE;
         const unsigned long long ncta = (unsigned long long)gridDim.x * gridDim.y * gridDim.z;
         const unsigned long long me = ((unsigned long long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
-        for (unsigned long long pi = me; pi < npieces; pi += ncta) {
+        for (unsigned long long pi = me + ncta * tid; pi < npieces; pi += ncta * nthreads) {
             const unsigned long long off = pi * PIECE;
             prefetch_l2_bulk((const char*)a.pf_ptr + off, (size_t)min(PIECE, a.pf_bytes - off));
         }

@@ -192,16 +192,19 @@ __global__ void __launch_bounds__(kSimtThreads, 1) gemv_kernel(const GemvArgs a)
             }
         }
     }
-    // slices of later kernels' weights
-    if (tid >= 32 && tid < 34) {
-        const int which = tid - 32;
-        const unsigned long long total = a.pf_bytes[which];
-        if (total) {
-            constexpr unsigned long long PIECE = 32 * 1024;
-            const unsigned long long npieces = (total + PIECE - 1) / PIECE;
-            for (unsigned long long pi = blockIdx.x; pi < npieces; pi += gridDim.x) {
-                const unsigned long long off = pi * PIECE;
-                prefetch_l2_bulk((const char*)a.pf_ptr[which] + off, (size_t)min(PIECE, total - off));
+    // slices of later kernels' weights: one 32 KiB bulk prefetch per thread at most
+    if (tid >= 32) {
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+            const unsigned long long total = a.pf_bytes[which];
+            if (total) {
+                constexpr unsigned long long PIECE = 32 * 1024;
+                const unsigned long long npieces = (total + PIECE - 1) / PIECE;
+                for (unsigned long long pi = blockIdx.x + (unsigned long long)gridDim.x * (tid - 32); pi < npieces;
+                     pi += (unsigned long long)gridDim.x * (kSimtThreads - 32)) {
+                    const unsigned long long off = pi * PIECE;
+                    prefetch_l2_bulk((const char*)a.pf_ptr[which] + off, (size_t)min(PIECE, total - off));
+                }
             }
         }
     }

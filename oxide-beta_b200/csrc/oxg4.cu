@@ -654,7 +654,7 @@ constexpr int kPrefillRows = 256;             // most prompt tokens one pass ove
 
 static int32_t tc_gemm_setup();
 static int32_t attn_mma_setup();
-static int tc_pick_splits(int tiles, int kblocks, int grid, int B, int n_total, int K);
+static int tc_pick_splits(int tiles, int kblocks, int grid, int B, int n_total, int K, double max_extra = 0.3);
 static int32_t encode_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 
 static int32_t cache_build(oxg4_cache* c) {
@@ -802,13 +802,18 @@ static int32_t cache_build(oxg4_cache* c) {
         c->s_o = tc_pick_splits(tiles(H), kbs(qw), sms, Bd, H, qw);
         c->s_gu = tc_pick_splits(2 * tiles(m->I), kbs(H), sms, Bd, 2 * m->I, H);
         c->s_down = tc_pick_splits(tiles(H), kbs(m->I), sms, Bd, H, m->I);
-        // a full chunk has kPrefillRows / 64 row blocks per weight tile: far more units than SMs, so K-splits
-        // only where a projection has very few tiles
-        const int tb = kPrefillRows / 64;
-        c->ps_qkv = tc_pick_splits(tiles(nqkv) * tb, kbs(H), sms, kPrefillRows, nqkv, H);
-        c->ps_o = tc_pick_splits(tiles(H) * tb, kbs(qw), sms, kPrefillRows, H, qw);
-        c->ps_gu = tc_pick_splits(2 * tiles(m->I) * tb, kbs(H), sms, kPrefillRows, 2 * m->I, H);
-        c->ps_down = tc_pick_splits(tiles(H) * tb, kbs(m->I), sms, kPrefillRows, H, m->I);
+        if (m->tp > 1 && getenv("OXG4_TP_KSPLIT") == nullptr) {
+            // row-split projections: K has already shrunk by the rank count, and a split would need one more
+            // launch to add the partials before the all-reduce
+            c->s_o = 1;
+            c->s_down = 1;
+        }
+        // a full chunk is one 256-row block per weight tile (UMMA N = 256): K-splits fill the SMs where a projection
+        // has few tiles; their partial outputs are cheap next to the tensor-core work of 256 rows
+        c->ps_qkv = tc_pick_splits(tiles(nqkv), kbs(H), sms, kPrefillRows, nqkv, H, 1.0);
+        c->ps_o = tc_pick_splits(tiles(H), kbs(qw), sms, kPrefillRows, H, qw, 1.0);
+        c->ps_gu = tc_pick_splits(2 * tiles(m->I), kbs(H), sms, kPrefillRows, 2 * m->I, H, 1.0);
+        c->ps_down = tc_pick_splits(tiles(H), kbs(m->I), sms, kPrefillRows, H, m->I, 1.0);
         auto rows_splits = [&](int sd, int sp) { return (size_t)std::max(sd * B, sp * kPrefillRows); };
         TRY(dalloc(c, &c->x_h, (size_t)R * H));
         TRY(dalloc(c, &c->x_a, (size_t)R * qw));
@@ -999,7 +1004,7 @@ static int32_t encode_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows,
 // out[B, N] = x[B, K] . W[N, K]^T on device pointers (BF16 in, f32 out), B <= 64, K a multiple of 8.
 // K-splits for a tcgen05 projection: work units = tiles * S should fill the grid in whole rounds;
 // the S partial outputs cost S * B * n * 8 bytes of extra traffic, kept under ~30 % of the weights.
-static int tc_pick_splits(int tiles, int kblocks, int grid, int B, int n_total, int K) {
+static int tc_pick_splits(int tiles, int kblocks, int grid, int B, int n_total, int K, double max_extra) {
     int best = 1;
     double best_score = -1.0;
     for (int S = 1; S <= 16 && S <= kblocks / 2 + (kblocks < 2 ? 1 : 0); ++S) {
@@ -1007,7 +1012,7 @@ static int tc_pick_splits(int tiles, int kblocks, int grid, int B, int n_total, 
         const double rounds = std::ceil(units / grid);
         const double eff = units / (rounds * grid);
         const double extra = S == 1 ? 0.0 : (double)S * B * n_total * 8.0 / ((double)n_total * K * 2.0);
-        if (extra > 0.3) break;
+        if (extra > max_extra) break;
         const double score = eff / (1.0 + extra);
         if (score > best_score + 1e-9) { best_score = score; best = S; }
     }
@@ -1021,7 +1026,7 @@ static int32_t tc_gemm_launch(const void* w_dev, const void* w1_dev, const void*
                               float* out_dev, int ld, int col0, int* err_dev, int num_sms, cudaStream_t st, bool pdl) {
     if (B < 1 || B > kPrefillRows || K % 8 != 0)
         return fail(OXG4_INVALID_SHAPE, "tcgen05 projection: 1..%d rows and K %% 8 == 0 required", kPrefillRows);
-    const int bn = B <= 16 ? 16 : (B <= 32 ? 32 : 64);
+    const int bn = B <= 16 ? 16 : (B <= 32 ? 32 : (B <= 64 ? 64 : (B <= 128 ? 128 : 256)));
     CUtensorMap mw, mw1, mx;
     TRY(encode_bf16_2d(&mw, w_dev, (uint64_t)N, (uint64_t)K, kTcTileM));
     TRY(encode_bf16_2d(&mw1, w1_dev ? w1_dev : w_dev, (uint64_t)N, (uint64_t)K, kTcTileM));
@@ -1054,9 +1059,15 @@ static int32_t tc_gemm_launch(const void* w_dev, const void* w1_dev, const void*
     } else if (bn == 32) {
         cfg.dynamicSmemBytes = tc_gemm_smem_bytes<32>();
         e = cudaLaunchKernelEx(&cfg, tc_gemm_kernel<32>, mw, mw1, mx, a);
-    } else {
+    } else if (bn == 64) {
         cfg.dynamicSmemBytes = tc_gemm_smem_bytes<64>();
         e = cudaLaunchKernelEx(&cfg, tc_gemm_kernel<64>, mw, mw1, mx, a);
+    } else if (bn == 128) {
+        cfg.dynamicSmemBytes = tc_gemm_smem_bytes<128>();
+        e = cudaLaunchKernelEx(&cfg, tc_gemm_kernel<128>, mw, mw1, mx, a);
+    } else {
+        cfg.dynamicSmemBytes = tc_gemm_smem_bytes<256>();
+        e = cudaLaunchKernelEx(&cfg, tc_gemm_kernel<256>, mw, mw1, mx, a);
     }
     CK(e);
     return OXG4_OK;
@@ -1066,6 +1077,8 @@ static int32_t tc_gemm_setup() {
     TRY(allow_big_smem(tc_gemm_kernel<16>));
     TRY(allow_big_smem(tc_gemm_kernel<32>));
     TRY(allow_big_smem(tc_gemm_kernel<64>));
+    TRY(allow_big_smem(tc_gemm_kernel<128>));
+    TRY(allow_big_smem(tc_gemm_kernel<256>));
     return OXG4_OK;
 }
 
@@ -1461,16 +1474,21 @@ static void run_layers(oxg4_cache* c, Launcher& ln, const RowSet& rs, bool use_t
             }
             ln.tc("qkv", c, R, p.wqkv, nullptr, c->x_h, nqkv, H, s_qkv, c->qkv_part, nqkv, 0);
             launch_attention(ln, c, rs, l, c->qkv_part, s_qkv, c->x_a, true);
-            ln.tc("o", c, R, p.wo, nullptr, c->x_a, H, qw, s_o, c->o_part, H, 0);
+            // row-split projection under tensor parallelism: without K-splits the kernel writes the rank's partial
+            // sum straight into the buffer that is all-reduced (one launch less); with the peer-memory exchange
+            // the summation kernel is what pushes it to the peers
+            const bool direct = m->tp > 1 && !peer && s_o == 1;
+            ln.tc("o", c, R, p.wo, nullptr, c->x_a, H, qw, s_o, direct ? c->o_raw : c->o_part, H, 0);
             const size_t bh = (size_t)R * H;
             const dim3 sum_grid((unsigned)((bh / 4 + kRowsThreads - 1) / kRowsThreads));
             PeerExchange none{};
             none.tp = 1;
             const float* xo = peer ? c->px[0].gathered : c->o_raw;        // what the next norm reads
             const int xs = peer ? m->tp : 1;                              // partials to add there
-            if (m->tp > 1) {      // row-split projection: add the K-splits locally, then the ranks
-                ln.go("sum", sum_splits_kernel, sum_grid, dim3(kRowsThreads), 0, (const float*)c->o_part, s_o, bh, c->o_raw,
-                      peer ? c->px[0] : none);
+            if (m->tp > 1) {      // add the K-splits locally, then the ranks
+                if (!direct)
+                    ln.go("sum", sum_splits_kernel, sum_grid, dim3(kRowsThreads), 0, (const float*)c->o_part, s_o, bh,
+                          c->o_raw, peer ? c->px[0] : none);
                 if (!peer) ln.allreduce(c->o_raw, bh);
             }
             RowsNormArgs n2{};
@@ -1488,10 +1506,12 @@ static void run_layers(oxg4_cache* c, Launcher& ln, const RowSet& rs, bool use_t
             ln.tc("gateup", c, R, p.wgate, p.wup, c->x_h, m->I, H, s_gu, c->gu_part, 2 * m->I, 0);
             ln.go("geglu", geglu_rows_kernel, dim3((m->I / 4 + kRowsThreads - 1) / kRowsThreads, R), dim3(kRowsThreads), 0, R,
                   m->I, (const float*)c->gu_part, s_gu, c->x_i);
-            ln.tc("down", c, R, p.wdown, nullptr, c->x_i, H, m->I, s_down, c->down_part, H, 0);
+            const bool direct_d = m->tp > 1 && !peer && s_down == 1;
+            ln.tc("down", c, R, p.wdown, nullptr, c->x_i, H, m->I, s_down, direct_d ? c->down_raw : c->down_part, H, 0);
             if (m->tp > 1) {
-                ln.go("sum", sum_splits_kernel, sum_grid, dim3(kRowsThreads), 0, (const float*)c->down_part, s_down, bh,
-                      c->down_raw, peer ? c->px[1] : none);
+                if (!direct_d)
+                    ln.go("sum", sum_splits_kernel, sum_grid, dim3(kRowsThreads), 0, (const float*)c->down_part, s_down, bh,
+                          c->down_raw, peer ? c->px[1] : none);
                 if (!peer) ln.allreduce(c->down_raw, bh);
             }
             continue;

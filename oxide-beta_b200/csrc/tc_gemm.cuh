@@ -29,7 +29,8 @@ namespace oxg4 {
 constexpr int kTcThreads = 192;      // warp 0: TMA, warp 1: MMA, warps 2..5: epilogue (one per TMEM lane quadrant)
 constexpr int kTcTileM = 128;        // weight rows per tile (UMMA M)
 constexpr int kTcTileK = 64;         // BF16 elements per stage row = 128 bytes = one swizzle atom row
-constexpr int kTcStages = 6;
+// shared-memory stages of the TMA ring: 6 x 24 KiB for up to 64 activation rows per block, 4 x 48 KiB for 256
+template <int BN> struct TcStages { static constexpr int value = BN <= 64 ? 6 : (BN <= 128 ? 5 : 4); };
 constexpr uint32_t kTcSpinLimit = 2u * 1000u * 1000u;   // bounded mbarrier polling
 
 struct TcGemmArgs {
@@ -102,7 +103,8 @@ template <int BN>
 __global__ void __launch_bounds__(kTcThreads, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w1,
                const __grid_constant__ CUtensorMap map_x, const TcGemmArgs a) {
-    static_assert(BN == 16 || BN == 32 || BN == 64, "activation rows per tile");
+    static_assert(BN == 16 || BN == 32 || BN == 64 || BN == 128 || BN == 256, "activation rows per tile");
+    constexpr int kTcStages = TcStages<BN>::value;
     constexpr uint32_t A_BYTES = kTcTileM * kTcTileK * 2;     // 16 KiB
     constexpr uint32_t B_BYTES = BN * kTcTileK * 2;
     constexpr uint32_t STAGE = A_BYTES + ((B_BYTES + 1023) / 1024) * 1024;
@@ -236,7 +238,7 @@ template <int BN>
 inline size_t tc_gemm_smem_bytes() {
     const size_t a = (size_t)kTcTileM * kTcTileK * 2;
     const size_t b = (((size_t)BN * kTcTileK * 2 + 1023) / 1024) * 1024;
-    return (a + b) * kTcStages + 1024;
+    return (a + b) * TcStages<BN>::value + 1024;
 }
 
 }  // namespace oxg4

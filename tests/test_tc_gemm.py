@@ -25,7 +25,10 @@ def run(N, K, B, seed=0):
 
 
 @pytest.mark.parametrize("N,K,B", [(128, 64, 16), (256, 256, 16), (384, 2560, 16), (1000, 1152, 9), (4096, 2560, 32),
-                                   (2560, 10240, 64), (200, 136, 33)])
+                                   (2560, 10240, 64), (200, 136, 33),
+                                   # prompt chunks: blocks of 128 / 256 activation rows (UMMA N = 128 / 256)
+                                   (384, 256, 100), (1000, 1152, 128), (4096, 2560, 200), (2560, 10240, 256),
+                                   (300, 136, 255)])
 def test_tc_gemm_matches_float64(N, K, B):
     out, ref, ms = run(N, K, B)
     scale = np.abs(ref).max()
