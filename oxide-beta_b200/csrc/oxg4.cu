@@ -2142,6 +2142,8 @@ extern "C" int32_t oxg4_prefill(oxg4_model* m, oxg4_cache* c, const uint32_t* to
         CK(cudaMemcpyAsync(c->pf_seq, h_seq, sizeof(int32_t) * R, cudaMemcpyHostToDevice, st));
         CK(cudaMemcpyAsync(c->pf_grp_row0, h_g0, sizeof(int32_t) * NG, cudaMemcpyHostToDevice, st));
         CK(cudaMemcpyAsync(c->pf_grp_n, h_gn, sizeof(int32_t) * NG, cudaMemcpyHostToDevice, st));
+        const bool prof = getenv("GEMMA4_PROFILE") != nullptr && getenv("OXG4_PROFILE_PREFILL") != nullptr;
+        m->profiling = prof;           // events around every launch of the chunk (a measurement aid, like the reference's GEMMA4_PROFILE)
         Launcher ln{m};
         RowSet rs;
         rs.R = R;
@@ -2169,9 +2171,24 @@ extern "C" int32_t oxg4_prefill(oxg4_model* m, oxg4_cache* c, const uint32_t* to
                 }
             }
         }
+        m->profiling = false;
         TRY(ln.status);
         m->launches += ln.kernels;
         CK(cudaStreamSynchronize(st));                         // the pinned staging is reused by the next chunk
+        if (prof) {
+            std::map<std::string, double> sum;
+            for (auto& pe : m->prof_events) {
+                float ms = 0;
+                cudaEventElapsedTime(&ms, pe.second.first, pe.second.second);
+                sum[pe.first] += ms;
+                cudaEventDestroy(pe.second.first);
+                cudaEventDestroy(pe.second.second);
+            }
+            m->prof_events.clear();
+            fprintf(stderr, "Gemma4 prefill chunk (%d rows):", R);
+            for (auto& kv : sum) fprintf(stderr, " %s %.3f ms", kv.first.c_str(), kv.second);
+            fprintf(stderr, "\n");
+        }
         TRY(check_tc(c));
     }
     // device step state: every sequence continues at position lens[b]
