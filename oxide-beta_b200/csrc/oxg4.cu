@@ -802,12 +802,6 @@ static int32_t cache_build(oxg4_cache* c) {
         c->s_o = tc_pick_splits(tiles(H), kbs(qw), sms, Bd, H, qw);
         c->s_gu = tc_pick_splits(2 * tiles(m->I), kbs(H), sms, Bd, 2 * m->I, H);
         c->s_down = tc_pick_splits(tiles(H), kbs(m->I), sms, Bd, H, m->I);
-        if (m->tp > 1 && getenv("OXG4_TP_KSPLIT") == nullptr) {
-            // row-split projections: K has already shrunk by the rank count, and a split would need one more
-            // launch to add the partials before the all-reduce
-            c->s_o = 1;
-            c->s_down = 1;
-        }
         // a full chunk is one 256-row block per weight tile (UMMA N = 256): K-splits fill the SMs where a projection
         // has few tiles; their partial outputs are cheap next to the tensor-core work of 256 rows
         c->ps_qkv = tc_pick_splits(tiles(nqkv), kbs(H), sms, kPrefillRows, nqkv, H, 1.0);

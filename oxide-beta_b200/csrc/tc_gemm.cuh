@@ -139,28 +139,56 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = tmem_base;
 
-    pdl_wait();
-    pdl_launch();
-
     if (warp == 0 && lane == 0) {
         // ---- TMA producer ----
-        uint32_t it = 0;
-        for (int t = blockIdx.x; t < n_tiles && !failed; t += gridDim.x) {
-            const int tg = t / (a.S * a.TB);                      // tile over both matrices
+        // The walk over this CTA's (unit, k-block) sequence. The weight tiles depend on nothing the preceding
+        // kernel writes, so the first ring of them is requested BEFORE the dependency wait (the launch is
+        // programmatic: this CTA may be resident while the preceding kernel still runs) and only the
+        // activation tiles of those stages wait for it.
+        int t = blockIdx.x;
+        int kb = t < n_tiles ? kb_begin(t) : 0;
+        auto advance = [&]() {
+            if (++kb >= kb_end(t)) {
+                t += gridDim.x;
+                if (t < n_tiles) kb = kb_begin(t);
+            }
+        };
+        auto load_w = [&](int tt, int kk, int s) {
+            const int tg = tt / (a.S * a.TB);
             const bool second = tg >= tiles_per_mat;
             const int trow = (second ? tg - tiles_per_mat : tg) * kTcTileM;
-            const int xrow = (t % a.TB) * BN;                     // first activation row of this unit's block
-            for (int kb = kb_begin(t); kb < kb_end(t); ++kb, ++it) {
-                const int s = it % kTcStages;
-                const uint32_t ph = (it / kTcStages) & 1;
-                if (it >= (uint32_t)kTcStages && !mbar_wait(&empty[s], ph ^ 1)) { failed = 1; atomicExch(a.err, 1); break; }
-                unsigned char* sa = tiles + (size_t)s * STAGE;
-                mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-                tma_load_2d(sa, second ? &map_w1 : &map_w, kb * kTcTileK, trow, &full[s]);
-                tma_load_2d(sa + A_BYTES, &map_x, kb * kTcTileK, xrow, &full[s]);
-            }
+            tma_load_2d(tiles + (size_t)s * STAGE, second ? &map_w1 : &map_w, kk * kTcTileK, trow, &full[s]);
+        };
+        auto load_x = [&](int tt, int kk, int s) {
+            tma_load_2d(tiles + (size_t)s * STAGE + A_BYTES, &map_x, kk * kTcTileK, (tt % a.TB) * BN, &full[s]);
+        };
+        int pre_t[kTcStages], pre_kb[kTcStages];
+        int n_pre = 0;
+        while (n_pre < kTcStages && t < n_tiles) {
+            mbar_expect_tx(&full[n_pre], A_BYTES + B_BYTES);
+            load_w(t, kb, n_pre);
+            pre_t[n_pre] = t;
+            pre_kb[n_pre] = kb;
+            ++n_pre;
+            advance();
         }
-    } else if (warp == 1 && lane == 0) {
+        pdl_wait();
+        pdl_launch();
+        for (int i = 0; i < n_pre; ++i) load_x(pre_t[i], pre_kb[i], i);
+        for (uint32_t it = (uint32_t)n_pre; t < n_tiles && !failed; ++it) {
+            const int s = it % kTcStages;
+            const uint32_t ph = (it / kTcStages) & 1;
+            if (!mbar_wait(&empty[s], ph ^ 1)) { failed = 1; atomicExch(a.err, 1); break; }
+            mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+            load_w(t, kb, s);
+            load_x(t, kb, s);
+            advance();
+        }
+    } else {
+        pdl_wait();
+        pdl_launch();
+    }
+    if (warp == 1 && lane == 0) {
         // ---- MMA issuer ----
         const uint32_t idesc = umma_idesc_bf16(kTcTileM, BN);
         uint32_t it = 0, tile_i = 0;
