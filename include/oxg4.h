@@ -49,7 +49,7 @@ typedef struct {
     int32_t num_attention_heads;
     int32_t num_key_value_heads;
     int32_t head_dim;
-    int32_t global_head_dim;          /* must equal head_dim in this build                        */
+    int32_t global_head_dim;          /* head_dim of the global (full_attention) layers (mod.rs:391-395) */
     int32_t intermediate_size;
     int32_t sliding_window;
     float rms_norm_eps;
@@ -64,13 +64,21 @@ typedef struct {
     const float* rope_factor;         /* [num_hidden_layers]                                        */
     int32_t tp_rank;                  /* tensor-parallel rank of this process (0 when tp_size = 1)  */
     int32_t tp_size;                  /* 1, 2, 4 or 8; must divide the KV-head count               */
+    /* Gemma4-E fields (config.rs:116-139); zero = the feature is off */
+    int32_t num_global_key_value_heads; /* KV heads of the global layers when attention_k_eq_v is set
+                                           (cache.rs:63-68); 0 = num_key_value_heads                 */
+    int32_t attention_k_eq_v;
+    int32_t num_kv_shared_layers;     /* the last n layers read the K/V cache of the last earlier layer of
+                                         their own type and have a q projection only (cache.rs:43-86)  */
+    int32_t hidden_size_per_layer_input; /* width P of the per-layer embeddings (ple.rs); 0 = none      */
+    int32_t vocab_size_per_layer_input;  /* rows of embed_tokens_per_layer.weight                        */
 } oxg4_config;
 
 typedef struct {
     int32_t batch;
     int32_t layer_count;              /* Gemma4CudaCacheTable::layer_count                          */
     int32_t physical_cache_count;     /* ::physical_cache_count                                     */
-    int32_t shared_layer_count;       /* ::shared_layer_count (always 0: KV sharing unsupported)    */
+    int32_t shared_layer_count;       /* ::shared_layer_count (layers that read another layer's cache) */
     int32_t page_tokens;
     int32_t kv_dtype;
     int64_t kv_bytes;                 /* device bytes held by K and V pools                         */

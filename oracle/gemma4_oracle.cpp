@@ -85,11 +85,13 @@ struct Vec {               // norm weights / scalars, always widened to f32
 };
 
 struct LayerW {
-    Vec input_ln, post_attn_ln, pre_ff_ln, post_ff_ln, q_norm, k_norm;
-    Matrix q, k, v, o, gate, up, down;
+    Vec input_ln, post_attn_ln, pre_ff_ln, post_ff_ln, q_norm, k_norm, ple_norm;
+    Matrix q, k, v, o, gate, up, down, ple_gate, ple_proj;
     float layer_scalar = 1.0f;
     int sliding = 0;
     int head_dim = 0;
+    int kv_heads = 0;          // cache.rs:63-68: num_global_key_value_heads on global layers with attention_k_eq_v
+    int source = 0;            // cache.rs:43-86: the layer whose cache this layer reads (itself unless KV-shared)
     int rotary_dim = 0;
     float theta = 10000.0f;
     float factor = 1.0f;
@@ -98,13 +100,14 @@ struct LayerW {
 struct Config {
     int32_t vocab, hidden, layers, heads, kv_heads, head_dim, global_head_dim, intermediate;
     int32_t sliding_window, mode, kv_bf16;
+    int32_t global_kv_heads, k_eq_v, kv_shared_layers, ple_dim, ple_vocab;   // Gemma4-E fields (config.rs:116-139)
     float eps;
 };
 
 struct Model {
     Config c;
-    Matrix embed;
-    Vec final_norm;
+    Matrix embed, ple_embed, ple_model_proj;
+    Vec final_norm, ple_proj_norm;
     std::vector<LayerW> L;
     std::string err;
 };
@@ -289,28 +292,54 @@ void forward_token(const Model& m, Cache& cache, uint32_t token, std::vector<flo
     }
     const int64_t pos = cache.position;
     std::vector<float> x(H), tmp, q, k, v, qn, kn, vn, att, proj, gate, up, act, down;
+    // packed_ple_state (ple.rs:55-99): per-layer inputs of this token, [layers, P]
+    const int P = c.ple_dim;
+    std::vector<float> packed;
+    if (P > 0) {
+        const int LP = c.layers * P;
+        std::vector<float> xe(H), ctx(LP), nctx(LP);
+        for (int i = 0; i < H; ++i) xe[i] = bf ? round_bf16(hidden[i]) : hidden[i];      // linear() casts its input
+        gemv(m.ple_model_proj, xe.data(), ctx.data());
+        const float inv_sqrt_h = 1.0f / sqrtf((float)H);
+        for (auto& v_ : ctx) v_ = v_ * inv_sqrt_h;
+        rms_norm_rows(ctx.data(), m.ple_proj_norm.v.data(), nctx.data(), c.layers, P, c.eps, false);
+        packed.resize(LP);
+        const float token_scale = sqrtf((float)P);
+        for (int i = 0; i < LP; ++i) {
+            float t = m.ple_embed.is_bf16 ? bf16_bits_to_f32(m.ple_embed.h[(int64_t)token * LP + i])
+                                          : m.ple_embed.f[(int64_t)token * LP + i];
+            packed[i] = (nctx[i] + t * token_scale) * 0.70710678118654752440f;
+        }
+    }
     for (int l = 0; l < c.layers; ++l) {
         const LayerW& w = m.L[l];
-        LayerCache& lc = cache.L[l];
+        LayerCache& lc = cache.L[w.source];
+        const bool owns_kv = w.source == l;
         const int D = w.head_dim;
         // layer-wise teacher forcing for tests: replace / record the layer's input hidden state
         if (inject) std::memcpy(hidden.data(), inject + (size_t)l * H, sizeof(float) * H);
         if (trace) std::memcpy(trace + (size_t)l * H, hidden.data(), sizeof(float) * H);
-        const int QW = c.heads * D, KW = c.kv_heads * D;
+        const int QW = c.heads * D, KW = w.kv_heads * D;
         // attention block
         rms_norm_rows(hidden.data(), w.input_ln.v.data(), x.data(), 1, H, c.eps, bf);
-        q.resize(QW); k.resize(KW); v.resize(KW);
+        q.resize(QW);
         gemv(w.q, x.data(), q.data());
-        gemv(w.k, x.data(), k.data());
-        gemv(w.v, x.data(), v.data());
-        qn.resize(QW); kn.resize(KW); vn.resize(KW);
+        qn.resize(QW);
         rms_norm_rows(q.data(), w.q_norm.v.data(), qn.data(), c.heads, D, c.eps, false);
         rope_rows(qn.data(), q.data(), c.heads, D, w.rotary_dim, w.theta, w.factor, pos);
-        rms_norm_rows(k.data(), w.k_norm.v.data(), kn.data(), c.kv_heads, D, c.eps, false);
-        rope_rows(kn.data(), k.data(), c.kv_heads, D, w.rotary_dim, w.theta, w.factor, pos);
-        rms_norm_rows(v.data(), nullptr, vn.data(), c.kv_heads, D, c.eps, false);
+        // a KV-shared layer has no K/V of its own: its source layer appended this position earlier in the step
+        // (decode.rs:82-98, 117-157)
+        if (owns_kv) {
+            k.resize(KW); v.resize(KW);
+            gemv(w.k, x.data(), k.data());
+            gemv(w.v, x.data(), v.data());
+            kn.resize(KW); vn.resize(KW);
+            rms_norm_rows(k.data(), w.k_norm.v.data(), kn.data(), w.kv_heads, D, c.eps, false);
+            rope_rows(kn.data(), k.data(), w.kv_heads, D, w.rotary_dim, w.theta, w.factor, pos);
+            rms_norm_rows(v.data(), nullptr, vn.data(), w.kv_heads, D, c.eps, false);
+        }
         // cache_write_f32_state: slot = position % capacity
-        {
+        if (owns_kv) {
             int64_t slot = pos % lc.capacity;
             for (int i = 0; i < KW; ++i) {
                 float kk = k[i], vv = vn[i];
@@ -341,6 +370,19 @@ void forward_token(const Model& m, Cache& cache, uint32_t token, std::vector<flo
         gemv(w.down, act.data(), down.data());
         rms_norm_rows(down.data(), w.post_ff_ln.v.data(), tmp.data(), 1, H, c.eps, false);
         for (int i = 0; i < H; ++i) hidden[i] = hidden[i] + tmp[i];
+        // apply_ple (ple.rs:151-185): gate -> gelu -> * per-layer input -> projection -> norm -> residual
+        if (P > 0) {
+            std::vector<float> xg(H), g(P), a2(P), pr(H);
+            for (int i = 0; i < H; ++i) xg[i] = bf ? round_bf16(hidden[i]) : hidden[i];
+            gemv(w.ple_gate, xg.data(), g.data());
+            for (int i = 0; i < P; ++i) {
+                float t = gelu_mul(g[i], packed[(size_t)l * P + i]);
+                a2[i] = bf ? round_bf16(t) : t;
+            }
+            gemv(w.ple_proj, a2.data(), pr.data());
+            rms_norm_rows(pr.data(), w.ple_norm.v.data(), tmp.data(), 1, H, c.eps, false);
+            for (int i = 0; i < H; ++i) hidden[i] = hidden[i] + tmp[i];
+        }
         // layer_scalar (tensor_ops.rs:244-267)
         for (int i = 0; i < H; ++i) hidden[i] = hidden[i] * w.layer_scalar;
     }
@@ -584,7 +626,7 @@ int64_t orc_sample_topk_candidates(const uint32_t* ids, const float* scores, int
 
 // ---- model -----------------------------------------------------------------------------------
 
-void* orc_model_create(const int32_t* cfg_i32 /*11 ints*/, float eps, const int32_t* layer_sliding,
+void* orc_model_create(const int32_t* cfg_i32 /*16 ints*/, float eps, const int32_t* layer_sliding,
                        const int32_t* rotary_dim, const float* theta, const float* factor) {
     Model* m = new Model();
     Config& c = m->c;
@@ -592,12 +634,24 @@ void* orc_model_create(const int32_t* cfg_i32 /*11 ints*/, float eps, const int3
     c.kv_heads = cfg_i32[4]; c.head_dim = cfg_i32[5]; c.global_head_dim = cfg_i32[6];
     c.intermediate = cfg_i32[7]; c.sliding_window = cfg_i32[8]; c.mode = cfg_i32[9];
     c.kv_bf16 = cfg_i32[10];
+    c.global_kv_heads = cfg_i32[11]; c.k_eq_v = cfg_i32[12]; c.kv_shared_layers = cfg_i32[13];
+    c.ple_dim = cfg_i32[14]; c.ple_vocab = cfg_i32[15];
     c.eps = eps;
     m->L.resize(c.layers);
+    const int first_shared = c.layers - c.kv_shared_layers;        // cache.rs:43-45
+    int last_sliding = -1, last_full = -1;
     for (int l = 0; l < c.layers; ++l) {
         LayerW& w = m->L[l];
         w.sliding = layer_sliding[l];
         w.head_dim = w.sliding ? c.head_dim : c.global_head_dim;   // mod.rs:391-395
+        w.kv_heads = (!w.sliding && c.k_eq_v && c.global_kv_heads > 0) ? c.global_kv_heads : c.kv_heads;   // cache.rs:63-68
+        if (l < first_shared) {
+            w.source = l;
+            (w.sliding ? last_sliding : last_full) = l;
+        } else {
+            w.source = w.sliding ? last_sliding : last_full;       // cache.rs:70-84
+            if (w.source < 0) { delete m; return nullptr; }
+        }
         w.rotary_dim = rotary_dim[l];
         w.theta = theta[l];
         w.factor = factor[l];
@@ -638,6 +692,9 @@ int orc_model_set_weight(void* model, const char* name, int dtype, const void* d
     };
     if (n == "embed_tokens.weight") { fill_matrix(m->embed); return 0; }
     if (n == "norm.weight") { fill_vec(m->final_norm); return 0; }
+    if (n == "embed_tokens_per_layer.weight") { fill_matrix(m->ple_embed); return 0; }
+    if (n == "per_layer_model_projection.weight") { fill_matrix(m->ple_model_proj); return 0; }
+    if (n == "per_layer_projection_norm.weight") { fill_vec(m->ple_proj_norm); return 0; }
     if (n.rfind("layers.", 0) == 0) {
         size_t dot = n.find('.', 7);
         if (dot == std::string::npos) return -1;
@@ -658,6 +715,9 @@ int orc_model_set_weight(void* model, const char* name, int dtype, const void* d
         else if (r == "mlp.gate_proj.weight") fill_matrix(w.gate);
         else if (r == "mlp.up_proj.weight") fill_matrix(w.up);
         else if (r == "mlp.down_proj.weight") fill_matrix(w.down);
+        else if (r == "per_layer_input_gate.weight") fill_matrix(w.ple_gate);
+        else if (r == "per_layer_projection.weight") fill_matrix(w.ple_proj);
+        else if (r == "post_per_layer_input_norm.weight") fill_vec(w.ple_norm);
         else if (r == "layer_scalar") {
             Vec t; fill_vec(t); w.layer_scalar = t.v[0];
         } else return -1;
@@ -675,8 +735,9 @@ void* orc_cache_create(void* model, int64_t max_sequence) {
         const LayerW& w = m->L[l];
         LayerCache& lc = c->L[l];
         lc.capacity = w.sliding ? std::min<int64_t>(m->c.sliding_window, max_sequence) : max_sequence;
-        lc.kv_heads = m->c.kv_heads;
+        lc.kv_heads = w.kv_heads;
         lc.head_dim = w.head_dim;
+        if (w.source != l) continue;          // a KV-shared layer reads its source layer's cache
         lc.k.assign((size_t)(lc.capacity * lc.kv_heads * lc.head_dim), 0.0f);
         lc.v.assign((size_t)(lc.capacity * lc.kv_heads * lc.head_dim), 0.0f);
     }

@@ -191,9 +191,15 @@ class OracleModel:
         ints = np.array([cfg["vocab_size"], cfg["hidden_size"], L, cfg["num_attention_heads"],
                          cfg["num_key_value_heads"], cfg["head_dim"],
                          cfg.get("global_head_dim", cfg["head_dim"]), cfg["intermediate_size"],
-                         cfg["sliding_window"], mode, int(kv_bf16)], dtype=np.int32)
-        self._h = C.c_void_p(lib().orc_model_create(_fp(ints), C.c_float(cfg["rms_norm_eps"]),
-                                                    _fp(sliding), _fp(rot), _fp(theta), _fp(factor)))
+                         cfg["sliding_window"], mode, int(kv_bf16),
+                         int(cfg.get("num_global_key_value_heads") or 0), int(bool(cfg.get("attention_k_eq_v"))),
+                         int(cfg.get("num_kv_shared_layers") or 0), int(cfg.get("hidden_size_per_layer_input") or 0),
+                         int(cfg.get("vocab_size_per_layer_input") or 0)], dtype=np.int32)
+        h = lib().orc_model_create(_fp(ints), C.c_float(cfg["rms_norm_eps"]), _fp(sliding), _fp(rot), _fp(theta),
+                                   _fp(factor))
+        if not h:
+            raise ValueError("shared layer has no preceding KV source")      # cache.rs:76-80
+        self._h = C.c_void_p(h)
 
     def __del__(self):
         if getattr(self, "_h", None):

@@ -24,7 +24,10 @@ class Config(C.Structure):
         ("rms_norm_eps", C.c_float), ("final_logit_softcapping", C.c_float), ("weight_dtype", C.c_int32),
         ("norm_weight_offset", C.c_int32), ("layer_is_sliding", C.POINTER(C.c_int32)),
         ("rotary_dim", C.POINTER(C.c_int32)), ("rope_theta", C.POINTER(C.c_float)),
-        ("rope_factor", C.POINTER(C.c_float)), ("tp_rank", C.c_int32), ("tp_size", C.c_int32)]
+        ("rope_factor", C.POINTER(C.c_float)), ("tp_rank", C.c_int32), ("tp_size", C.c_int32),
+        ("num_global_key_value_heads", C.c_int32), ("attention_k_eq_v", C.c_int32),
+        ("num_kv_shared_layers", C.c_int32), ("hidden_size_per_layer_input", C.c_int32),
+        ("vocab_size_per_layer_input", C.c_int32)]
 
 
 class CacheInfo(C.Structure):

@@ -424,7 +424,7 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnMmaArgs a) {
 // Per (row, head) warp: q/k RMS norm with weight + RoPE, v unit RMS norm (kernel_module.rs:1133-1246,
 // 1510-1550), K/V append at slot position % capacity (kernel_module.rs:1423-1439), and the query written as
 // BF16 high and low parts for attn_mma_kernel. With `q_hl` null only the K/V rows are produced (the
-// SIMT attention kernel norms its own queries).
+// SIMT attention kernel norms its own queries); with `write_kv` 0 only the queries (KV-shared layers).
 struct QkvPostArgs {
     const float* qkv;            // [splits, R, qkv_n] projection output (K-split partials), columns q | k | v
     int qkv_n, splits, R, Nq, Nkv;
@@ -442,6 +442,7 @@ struct QkvPostArgs {
     int pages_per_seq, page_tokens;
     const int32_t* cap;
     uint16_t* q_hl;              // [R][Nq][2][D] or null
+    int write_kv;                // 0: a KV-shared layer (its source layer has appended K/V; the projection holds q only)
 };
 
 template <typename KT, int D>
@@ -450,11 +451,11 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostArgs a) {
     pdl_wait();
     pdl_launch();
     const int lane = threadIdx.x & 31;
-    const int heads = a.Nq + 2 * a.Nkv;
     const int first_task = a.q_hl ? 0 : a.Nq;
-    const int per_row = heads - first_task;
+    const int last_task = a.write_kv ? a.Nq + 2 * a.Nkv : a.Nq;      // tasks: q heads, then k heads, then v heads
+    const int per_row = last_task - first_task;
     const int job = blockIdx.x * 4 + (threadIdx.x >> 5);
-    if (job >= a.R * per_row) return;
+    if (per_row <= 0 || job >= a.R * per_row) return;
     const int row = job / per_row, task = first_task + job % per_row;
     if (a.row_tok != nullptr && a.row_tok[row] == kInactiveToken) return;
     const int pos = a.row_pos[row];

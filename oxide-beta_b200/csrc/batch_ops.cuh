@@ -217,6 +217,101 @@ sum_splits_kernel(const float* part, int splits, size_t n, float* out, const Pee
     }
 }
 
+// ---- per-layer embeddings of the Gemma4-E models (crates/oxide-torch-models/src/gemma4_cuda/ple.rs) ---------
+// out[r, :] = embedding row of the row's token widened to f32, times sqrt(hidden) (kernel_module.rs:1272-1285);
+// the input of the context projection. grid (R), any block size.
+template <typename WT>
+__global__ void ple_embed_rows_kernel(int H, const WT* embed, const uint32_t* tokens, float scale, float* out) {
+    pdl_wait();
+    pdl_launch();
+    const int r = blockIdx.x;
+    uint32_t tok = tokens[r];
+    if (tok == kInactiveToken) tok = 0;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v;
+        if constexpr (sizeof(WT) == 2) v = __uint_as_float((uint32_t)embed[(size_t)tok * H + i] << 16);
+        else v = embed[(size_t)tok * H + i];
+        out[(size_t)r * H + i] = v * scale;
+    }
+}
+
+// packed_ple_state / packed_ple_rows (ple.rs:55-99, 100-150): one warp per (row, layer):
+//   context = rmsnorm_P(ctx[r, l*P ..] * (1 / sqrt(hidden))) * w         (the norm runs over the layer's P values)
+//   token   = table[token, l*P ..] widened to f32 * sqrt(P)
+//   packed  = (context + token) * FRAC_1_SQRT_2
+template <typename WT>
+__global__ void __launch_bounds__(128)
+ple_pack_kernel(int R, int L, int P, const float* ctx, const float* w, const WT* table, const uint32_t* tokens, float eps,
+                float inv_sqrt_h, float sqrt_p, float* packed) {
+    pdl_wait();
+    pdl_launch();
+    const int job = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (job >= R * L) return;
+    const int r = job / L, l = job % L;
+    uint32_t tok = tokens[r];
+    if (tok == kInactiveToken) return;
+    const size_t base = (size_t)r * L * P + (size_t)l * P;
+    float ss = 0.0f;
+    for (int i = lane; i < P; i += 32) {
+        const float v = ctx[base + i] * inv_sqrt_h;
+        ss += v * v;
+    }
+    ss = warp_sum(ss);
+    const float s = 1.0f / sqrtf(ss / (float)P + eps);
+    for (int i = lane; i < P; i += 32) {
+        const float c = ctx[base + i] * inv_sqrt_h * s * w[i];
+        float t;
+        if constexpr (sizeof(WT) == 2) t = __uint_as_float((uint32_t)table[(size_t)tok * L * P + (size_t)l * P + i] << 16);
+        else t = table[(size_t)tok * L * P + (size_t)l * P + i];
+        packed[base + i] = (c + t * sqrt_p) * 0.70710678118654752440f;
+    }
+}
+
+// apply_ple, first half (ple.rs:151-170 with the closing adds of decode.rs:19-20): one CTA per row closes the MLP
+// block's residual, h' = h_in + rmsnorm(raw, w_post) (no layer_scalar yet), and stores it; it is both the input of
+// the gate projection and the residual the branch is added to. Hidden size a multiple of 4.
+__global__ void __launch_bounds__(kRowsThreads)
+ple_close_kernel(int H, const float* h_in, const float* raw, const float* w_post, float eps, float* h_out) {
+    __shared__ float red[32];
+    pdl_wait();
+    pdl_launch();
+    const int b = blockIdx.x, tid = threadIdx.x, H4 = H >> 2;
+    const size_t ro = (size_t)b * H;
+    float4 t[kRowsMaxJ];
+    float ss[1] = {0.0f};
+#pragma unroll
+    for (int j = 0; j < kRowsMaxJ; ++j) {
+        const int i4 = tid + j * kRowsThreads;
+        t[j] = i4 < H4 ? *reinterpret_cast<const float4*>(raw + ro + 4 * i4) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        ss[0] += t[j].x * t[j].x;
+        ss[0] += t[j].y * t[j].y;
+        ss[0] += t[j].z * t[j].z;
+        ss[0] += t[j].w * t[j].w;
+    }
+    block_sum<1>(ss, red);
+    const float r = 1.0f / sqrtf(ss[0] / (float)H + eps);
+#pragma unroll
+    for (int j = 0; j < kRowsMaxJ; ++j) {
+        const int i4 = tid + j * kRowsThreads;
+        if (i4 < H4) {
+            const float4 h = *reinterpret_cast<const float4*>(h_in + ro + 4 * i4);
+            const float4 w = *reinterpret_cast<const float4*>(w_post + 4 * i4);
+            *reinterpret_cast<float4*>(h_out + ro + 4 * i4) =
+                make_float4(h.x + t[j].x * r * w.x, h.y + t[j].y * r * w.y, h.z + t[j].z * r * w.z, h.w + t[j].w * r * w.w);
+        }
+    }
+}
+
+// apply_ple, middle (ple.rs:171-172): act[r, i] = gelu(gate[r, i]) * packed[r, l*P + i]; grid (ceil(P / 256), R)
+__global__ void __launch_bounds__(kRowsThreads)
+ple_act_kernel(int P, int LP, int layer, const float* gate, const float* packed, float* act) {
+    pdl_wait();
+    pdl_launch();
+    const int r = blockIdx.y, i = blockIdx.x * kRowsThreads + threadIdx.x;
+    if (i >= P) return;
+    act[(size_t)r * P + i] = gelu_mul(gate[(size_t)r * P + i], packed[(size_t)r * LP + (size_t)layer * P + i]);
+}
+
 // Failure-path probe (one thread): the two kinds of bounded device-side wait this library uses, each on
 // something that nobody will ever signal, with a small polling budget. The wait must run out, raise the
 // status word and let the kernel return normally; nothing faults and the context stays usable.

@@ -71,18 +71,29 @@ struct Tensor {
     size_t bytes = 0;
 };
 
+struct GemvPlan {             // how a projection is cut into CTA row blocks and warp runs
+    int N = 0, K = 0, cpr = 0, grid = 0, slots = 1, rows_max = 0;
+};
+
 struct LayerPlan {            // Gemma4DecodeLayerPlan (gemma4_cuda/mod.rs:65-93)
     bool sliding = false;
+    // head geometry of this layer (local to the tensor-parallel rank): sliding layers use head_dim and
+    // num_key_value_heads, global layers global_head_dim and, with attention_k_eq_v, num_global_key_value_heads
+    // (mod.rs:391-395, cache.rs:63-68)
+    int D = 0, Nkv = 0, G = 1;
+    int qkv_n = 0, qw = 0;    // rows of the fused projection ((Nq + 2 Nkv) D, or Nq D for a KV-shared layer), Nq * D
+    int source = 0;           // the layer whose K/V cache this layer reads: itself, or for the last
+    bool shared = false;      // num_kv_shared_layers layers the last earlier layer of the same type (cache.rs:43-86)
+    GemvPlan p_qkv, p_o;
+    // per-layer embeddings (ple.rs:151-185), null when hidden_size_per_layer_input == 0
+    const void *w_ple_gate = nullptr, *w_ple_proj = nullptr;
+    const float* ple_norm = nullptr;
     int rotary_dim = 0;
     float theta = 0, factor = 1, layer_scalar = 1;
     const void *wqkv = nullptr, *wo = nullptr, *wgate = nullptr, *wup = nullptr, *wdown = nullptr;
     const float *input_ln = nullptr, *post_attn_ln = nullptr, *pre_ff_ln = nullptr,
                 *post_ff_ln = nullptr, *q_norm = nullptr, *k_norm = nullptr;
     float* inv_freq = nullptr;
-};
-
-struct GemvPlan {             // how a projection is cut into CTA row blocks and warp runs
-    int N = 0, K = 0, cpr = 0, grid = 0, slots = 1, rows_max = 0;
 };
 
 struct ProfileSlot {
@@ -113,9 +124,14 @@ struct oxg4_model {
     const void* embed = nullptr;
     const float* final_norm = nullptr;
     // local (per tensor-parallel rank) sizes
-    int H = 0, D = 0, Nq = 0, Nkv = 0, I = 0, V = 0, Vloc = 0, v0 = 0, G = 0;
+    int H = 0, Nq = 0, I = 0, V = 0, Vloc = 0, v0 = 0;
+    int Dmax = 0, qkv_n_max = 0, qw_max = 0, kvw_max = 0;   // largest head_dim / fused rows / Nq*D / Nkv*D over the layers
+    int P = 0;                // hidden_size_per_layer_input (0: no per-layer embeddings)
+    const void *ple_embed = nullptr, *ple_model_proj = nullptr;
+    const float* ple_proj_norm = nullptr;
+    GemvPlan p_ple_ctx, p_ple_gate, p_ple_proj;
     int es = 2;               // bytes per weight element
-    GemvPlan p_qkv, p_o, p_gateup, p_down, p_lm;
+    GemvPlan p_gateup, p_down, p_lm;
     int p_lm_simt_grid = 1;    // the SIMT logits kernel deals row pairs to warps across the grid
     long long launches = 0;
     int tp = 1, tp_rank = 0;
@@ -150,6 +166,20 @@ static inline float host_bf16_to_f32(uint16_t h) {
     return f;
 }
 
+// full-model head geometry of layer l (before tensor-parallel sharding)
+static int layer_head_dim(const oxg4_config& c, const int32_t* sliding, int l) {
+    return sliding[l] ? c.head_dim : c.global_head_dim;
+}
+static int layer_kv_heads(const oxg4_config& c, const int32_t* sliding, int l) {
+    if (!sliding[l] && c.attention_k_eq_v && c.num_global_key_value_heads > 0) return c.num_global_key_value_heads;
+    return c.num_key_value_heads;
+}
+// layer index of a canonical tensor name "layers.N....", or -1
+static int layer_of_name(const std::string& n) {
+    if (n.rfind("layers.", 0) != 0) return -1;
+    return atoi(n.c_str() + 7);
+}
+
 static GemvPlan make_plan(int N, int K, int es, int num_sms, int group /*rows that stay in one CTA*/) {
     GemvPlan p;
     p.N = N;
@@ -176,18 +206,27 @@ extern "C" int32_t oxg4_model_create(const oxg4_config* c, int32_t device, oxg4_
         return fail(OXG4_INVALID_ARGUMENT, "per-layer plan arrays are missing");
     if (c->weight_dtype != OXG4_F32 && c->weight_dtype != OXG4_BF16)
         return fail(OXG4_INVALID_ARGUMENT, "weight_dtype must be OXG4_F32 or OXG4_BF16");
-    if (c->global_head_dim != c->head_dim)
-        return fail(OXG4_UNSUPPORTED, "global_head_dim != head_dim is not supported");
-    if (c->head_dim != 64 && c->head_dim != 128 && c->head_dim != 256)
-        return fail(OXG4_UNSUPPORTED, "head_dim must be 64, 128 or 256");
     const int tp = c->tp_size <= 0 ? 1 : c->tp_size;
     if (tp != 1 && tp != 2 && tp != 4 && tp != 8) return fail(OXG4_INVALID_ARGUMENT, "tp_size must be 1, 2, 4 or 8");
     if (c->tp_rank < 0 || c->tp_rank >= tp) return fail(OXG4_INVALID_ARGUMENT, "tp_rank out of range");
-    if (c->num_key_value_heads % tp != 0 || c->intermediate_size % tp != 0 || c->vocab_size % tp != 0)
+    if (c->intermediate_size % tp != 0 || c->vocab_size % tp != 0)
         return fail(OXG4_INVALID_SHAPE, "tp_size must divide kv heads, intermediate size and vocabulary");
-    const int g = c->num_attention_heads / c->num_key_value_heads;
-    if (g != 1 && g != 2 && g != 4 && g != 8)
-        return fail(OXG4_UNSUPPORTED, "query heads per KV head must be 1, 2, 4 or 8");
+    if (c->num_kv_shared_layers < 0 || c->num_kv_shared_layers >= c->num_hidden_layers)
+        return fail(OXG4_INVALID_SHAPE, "num_kv_shared_layers must leave at least one layer with its own cache");
+    if (c->hidden_size_per_layer_input < 0 || (c->hidden_size_per_layer_input > 0 && c->vocab_size_per_layer_input <= 0))
+        return fail(OXG4_INVALID_SHAPE, "per-layer embeddings need vocab_size_per_layer_input");
+    for (int l = 0; l < c->num_hidden_layers; ++l) {           // head geometry of both layer kinds
+        const int d = layer_head_dim(*c, c->layer_is_sliding, l), kvh = layer_kv_heads(*c, c->layer_is_sliding, l);
+        if (d != 64 && d != 128 && d != 256)
+            return fail(OXG4_UNSUPPORTED, "head_dim / global_head_dim must be 64, 128 or 256");
+        if (kvh <= 0 || c->num_attention_heads % kvh != 0)
+            return fail(OXG4_INVALID_SHAPE, "invalid Gemma 4 attention configuration");
+        if (kvh % tp != 0 || c->num_attention_heads % tp != 0)
+            return fail(OXG4_INVALID_SHAPE, "tp_size must divide kv heads, intermediate size and vocabulary");
+        const int g = c->num_attention_heads / kvh;
+        if (g != 1 && g != 2 && g != 4 && g != 8)
+            return fail(OXG4_UNSUPPORTED, "query heads per KV head must be 1, 2, 4 or 8");
+    }
     const int esz = c->weight_dtype == OXG4_BF16 ? 2 : 4;
     if ((c->hidden_size * esz) % 16 || (c->intermediate_size / tp * esz) % 16)
         return fail(OXG4_INVALID_SHAPE, "hidden and intermediate sizes must be multiples of 16 bytes");
@@ -211,10 +250,8 @@ extern "C" int32_t oxg4_model_create(const oxg4_config* c, int32_t device, oxg4_
     m->cfg.tp_size = tp;
     m->device = device;
     m->H = c->hidden_size;
-    m->D = c->head_dim;
     m->Nq = c->num_attention_heads / tp;
-    m->Nkv = c->num_key_value_heads / tp;
-    m->G = g;
+    m->P = c->hidden_size_per_layer_input;
     m->I = c->intermediate_size / tp;
     m->V = c->vocab_size;
     m->Vloc = c->vocab_size / tp;
@@ -305,8 +342,12 @@ extern "C" int32_t oxg4_model_upload(oxg4_model* m, const char* name, int32_t dt
         }
         t.dtype = dst_dtype;
         // tensor parallelism: keep only this rank's rows / columns (csrc/tp.h)
+        const int ln_ = layer_of_name(n);
+        const bool has_layer = ln_ >= 0 && ln_ < m->cfg.num_hidden_layers;
         const ShardSpec sh = shard_of(n, shape[0], shape[1], m->tp_rank, m->tp, m->cfg.num_attention_heads,
-                                      m->cfg.num_key_value_heads, m->cfg.head_dim, m->cfg.intermediate_size);
+                                      has_layer ? layer_kv_heads(m->cfg, m->cfg.layer_is_sliding, ln_) : m->cfg.num_key_value_heads,
+                                      has_layer ? layer_head_dim(m->cfg, m->cfg.layer_is_sliding, ln_) : m->cfg.head_dim,
+                                      m->cfg.intermediate_size);
         t.shape = {sh.nrows, sh.ncols};
         t.bytes = (size_t)sh.nrows * sh.ncols * dst_es;
         CK(cudaMalloc(&t.d, t.bytes));
@@ -428,42 +469,82 @@ extern "C" int32_t oxg4_model_finalize(oxg4_model* m) {
         if (m->stage_ev[i]) { cudaEventDestroy(m->stage_ev[i]); m->stage_ev[i] = nullptr; }
     }
     const oxg4_config& c = m->cfg;
-    const int L = c.num_hidden_layers, H = m->H, D = m->D;
-    const int64_t QW = (int64_t)m->Nq * D, KW = (int64_t)m->Nkv * D;
+    const int L = c.num_hidden_layers, H = m->H;
     const Tensor* t = nullptr;
     TRY(need(m, "embed_tokens.weight", {c.vocab_size, H}, &t));
     m->embed = t->d;
     TRY(need(m, "norm.weight", {H}, &t));
     m->final_norm = (const float*)t->d;
+    if (m->P > 0) {
+        // per-layer embeddings (ple.rs:14-21,41-48): token table [V_ple, L * P], context projection [L * P, H], norm [P]
+        TRY(need(m, "embed_tokens_per_layer.weight", {c.vocab_size_per_layer_input, (int64_t)L * m->P}, &t));
+        m->ple_embed = t->d;
+        TRY(need(m, "per_layer_model_projection.weight", {(int64_t)L * m->P, H}, &t));
+        m->ple_model_proj = t->d;
+        TRY(need(m, "per_layer_projection_norm.weight", {m->P}, &t));
+        m->ple_proj_norm = (const float*)t->d;
+        m->p_ple_ctx = make_plan(L * m->P, H, m->es, m->num_sms, 1);
+        m->p_ple_gate = make_plan(m->P, H, m->es, m->num_sms, 1);
+        m->p_ple_proj = make_plan(H, m->P, m->es, m->num_sms, 1);
+    }
     m->layers.resize(L);
+    const int first_shared = L - c.num_kv_shared_layers;       // cache.rs:43-45
+    int last_sliding = -1, last_full = -1;
+    m->Dmax = m->qkv_n_max = m->qw_max = m->kvw_max = 0;
     for (int l = 0; l < L; ++l) {
         LayerPlan& p = m->layers[l];
         const std::string pre = "layers." + std::to_string(l) + ".";
         p.sliding = m->layer_sliding[l] != 0;
+        p.D = layer_head_dim(c, m->layer_sliding.data(), l);
+        p.Nkv = layer_kv_heads(c, m->layer_sliding.data(), l) / m->tp;
+        p.G = m->Nq / p.Nkv;
+        p.qw = m->Nq * p.D;
+        p.shared = l >= first_shared;
+        if (!p.shared) {
+            p.source = l;
+            (p.sliding ? last_sliding : last_full) = l;
+        } else {
+            p.source = p.sliding ? last_sliding : last_full;
+            if (p.source < 0)
+                return fail(OXG4_INVALID_ARGUMENT, "shared layer %d has no preceding %s KV source", l,
+                            p.sliding ? "sliding_attention" : "full_attention");       // cache.rs:76-80
+        }
+        const int D = p.D;
+        const int64_t QW = p.qw, KW = (int64_t)p.Nkv * D;
         p.rotary_dim = m->rotary_dim[l];
         p.theta = m->rope_theta[l];
         p.factor = m->rope_factor[l];
         if (p.rotary_dim < 0 || p.rotary_dim > D) return fail(OXG4_INVALID_SHAPE, "layer %d: rotary_dim out of range", l);
-        // fuse q/k/v rows into one [q;k;v, H] matrix (mod.rs:283-350)
-        const Tensor *q, *k, *v;
-        TRY(need(m, pre + "self_attn.q_proj.weight", {QW, H}, &q));
-        TRY(need(m, pre + "self_attn.k_proj.weight", {KW, H}, &k));
-        TRY(need(m, pre + "self_attn.v_proj.weight", {KW, H}, &v));
-        Tensor f;
-        f.dtype = q->dtype;
-        f.shape = {QW + 2 * KW, H};
-        f.bytes = q->bytes + k->bytes + v->bytes;
-        CK(cudaMalloc(&f.d, f.bytes));
-        CK(cudaMemcpy(f.d, q->d, q->bytes, cudaMemcpyDeviceToDevice));
-        CK(cudaMemcpy((char*)f.d + q->bytes, k->d, k->bytes, cudaMemcpyDeviceToDevice));
-        CK(cudaMemcpy((char*)f.d + q->bytes + k->bytes, v->d, v->bytes, cudaMemcpyDeviceToDevice));
-        for (const char* nm : {"self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn.v_proj.weight"}) {
-            auto it = m->tensors.find(pre + nm);
-            cudaFree(it->second.d);
-            m->tensors.erase(it);
+        if (p.shared) {
+            // a KV-shared layer keeps its q projection only (mod.rs:287, 420-424)
+            const Tensor* q;
+            TRY(need(m, pre + "self_attn.q_proj.weight", {QW, H}, &q));
+            p.wqkv = q->d;
+            p.qkv_n = (int)QW;
+        } else {
+            // fuse q/k/v rows into one [q;k;v, H] matrix (mod.rs:283-350)
+            const Tensor *q, *k, *v;
+            TRY(need(m, pre + "self_attn.q_proj.weight", {QW, H}, &q));
+            TRY(need(m, pre + "self_attn.k_proj.weight", {KW, H}, &k));
+            TRY(need(m, pre + "self_attn.v_proj.weight", {KW, H}, &v));
+            Tensor f;
+            f.dtype = q->dtype;
+            f.shape = {QW + 2 * KW, H};
+            f.bytes = q->bytes + k->bytes + v->bytes;
+            CK(cudaMalloc(&f.d, f.bytes));
+            CK(cudaMemcpy(f.d, q->d, q->bytes, cudaMemcpyDeviceToDevice));
+            CK(cudaMemcpy((char*)f.d + q->bytes, k->d, k->bytes, cudaMemcpyDeviceToDevice));
+            CK(cudaMemcpy((char*)f.d + q->bytes + k->bytes, v->d, v->bytes, cudaMemcpyDeviceToDevice));
+            for (const char* nm : {"self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn.v_proj.weight"}) {
+                auto it = m->tensors.find(pre + nm);
+                cudaFree(it->second.d);
+                m->tensors.erase(it);
+            }
+            m->tensors[pre + "self_attn.qkv_proj.weight"] = f;
+            p.wqkv = f.d;
+            p.qkv_n = (int)(QW + 2 * KW);
+            TRY(need(m, pre + "self_attn.k_norm.weight", {D}, &t)); p.k_norm = (const float*)t->d;
         }
-        m->tensors[pre + "self_attn.qkv_proj.weight"] = f;
-        p.wqkv = f.d;
         TRY(need(m, pre + "self_attn.o_proj.weight", {H, QW}, &t)); p.wo = t->d;
         TRY(need(m, pre + "mlp.gate_proj.weight", {m->I, H}, &t)); p.wgate = t->d;
         TRY(need(m, pre + "mlp.up_proj.weight", {m->I, H}, &t)); p.wup = t->d;
@@ -473,7 +554,11 @@ extern "C" int32_t oxg4_model_finalize(oxg4_model* m) {
         TRY(need(m, pre + "pre_feedforward_layernorm.weight", {H}, &t)); p.pre_ff_ln = (const float*)t->d;
         TRY(need(m, pre + "post_feedforward_layernorm.weight", {H}, &t)); p.post_ff_ln = (const float*)t->d;
         TRY(need(m, pre + "self_attn.q_norm.weight", {D}, &t)); p.q_norm = (const float*)t->d;
-        TRY(need(m, pre + "self_attn.k_norm.weight", {D}, &t)); p.k_norm = (const float*)t->d;
+        if (m->P > 0) {
+            TRY(need(m, pre + "per_layer_input_gate.weight", {m->P, H}, &t)); p.w_ple_gate = t->d;
+            TRY(need(m, pre + "per_layer_projection.weight", {H, m->P}, &t)); p.w_ple_proj = t->d;
+            TRY(need(m, pre + "post_per_layer_input_norm.weight", {H}, &t)); p.ple_norm = (const float*)t->d;
+        }
         TRY(need(m, pre + "layer_scalar", {1}, &t));          // mandatory, mod.rs:447
         CK(cudaMemcpy(&p.layer_scalar, t->d, 4, cudaMemcpyDeviceToHost));
         // kernel_module.rs:1539-1540: frequency = powf(theta, -(2 i)/head_dim) / factor, in f32
@@ -484,9 +569,13 @@ extern "C" int32_t oxg4_model_finalize(oxg4_model* m) {
         }
         CK(cudaMalloc(&p.inv_freq, sizeof(float) * (D / 2)));
         CK(cudaMemcpy(p.inv_freq, inv.data(), sizeof(float) * (D / 2), cudaMemcpyHostToDevice));
+        p.p_qkv = make_plan(p.qkv_n, H, m->es, m->num_sms, 1);
+        p.p_o = make_plan(H, (int)QW, m->es, m->num_sms, 1);
+        m->Dmax = std::max(m->Dmax, D);
+        m->qkv_n_max = std::max(m->qkv_n_max, p.qkv_n);
+        m->qw_max = std::max(m->qw_max, p.qw);
+        m->kvw_max = std::max(m->kvw_max, p.Nkv * D);
     }
-    m->p_qkv = make_plan((int)(QW + 2 * KW), H, m->es, m->num_sms, 1);
-    m->p_o = make_plan(H, (int)QW, m->es, m->num_sms, 1);
     m->p_gateup = make_plan(2 * m->I, H, m->es, m->num_sms, 2);
     m->p_down = make_plan(H, m->I, m->es, m->num_sms, 1);
     m->p_lm = make_plan(m->Vloc, H, m->es, m->num_sms, 1);
@@ -571,7 +660,10 @@ struct oxg4_cache {
     int B = 0, PT = 256, kv_dtype = OXG4_BF16;
     std::vector<int32_t> max_seq, pos_host;
     int pps_full = 0, pps_slide = 0;
-    int splits_full = 1, splits_slide = 1, min_split = 32;
+    int min_split = 32;
+    std::vector<int> attn_splits;             // per layer: split-KV CTAs per (sequence, kv head) of the one-row attention kernel
+    std::vector<int> ls_qkv, ls_o, lps_qkv, lps_o;   // per layer: K-splits of the tcgen05 QKV / O projections (decode, prompt chunk)
+    int physical_caches = 0;
     bool attn_cluster = true;     // merge split-KV partials through a thread-block cluster's shared memory
     std::vector<void*> kpool, vpool;          // per layer
     int64_t kv_bytes = 0;
@@ -606,7 +698,12 @@ struct oxg4_cache {
     int rows_cap = 0;
     // prompt chunks: per-row metadata (token, position, sequence) and the attention groups, device + pinned host
     uint32_t *pf_tok = nullptr, *h_pf_tok = nullptr;
-    int32_t *pf_pos = nullptr, *pf_seq = nullptr, *pf_grp_row0 = nullptr, *pf_grp_n = nullptr, *h_pf_meta = nullptr;
+    int32_t *pf_pos = nullptr, *pf_seq = nullptr, *h_pf_meta = nullptr;
+    int32_t *pf_grp_row0[2] = {nullptr, nullptr}, *pf_grp_n[2] = {nullptr, nullptr};   // attention groups of a chunk, per layer kind (sliding, global)
+    // per-layer embeddings: embedding rows (f32 + BF16), context projection output, packed per-layer inputs, scratch
+    float *ple_emb = nullptr, *ple_ctx = nullptr, *ple_packed = nullptr, *ple_h = nullptr, *ple_gate = nullptr, *ple_act = nullptr,
+          *ple_raw = nullptr;
+
     int32_t *dec_grp_row0 = nullptr, *dec_grp_n = nullptr;      // decode: one group per sequence
     float *last_h = nullptr, *last_raw = nullptr;               // [B, H] residual stream / pending update of every sequence's last prompt token
     uint16_t* last_x = nullptr;                                 // [B, H] tcgen05 path: its normed BF16 activations
@@ -618,8 +715,8 @@ struct oxg4_cache {
     // tcgen05 path (decode with eight or more sequences, and every prompt chunk of a BF16 model): BF16
     // activations, K-split partial outputs, error flag
     bool use_tc = false, tc_ok = false;
-    int s_qkv = 1, s_o = 1, s_gu = 1, s_down = 1;              // K-splits for a decode step (B rows)
-    int ps_qkv = 1, ps_o = 1, ps_gu = 1, ps_down = 1;          // K-splits for a full prompt chunk
+    int s_gu = 1, s_down = 1;                                  // K-splits for a decode step (B rows)
+    int ps_gu = 1, ps_down = 1;                                // K-splits for a full prompt chunk
     uint16_t *x_h = nullptr, *x_a = nullptr, *x_i = nullptr;
     float *qkv_part = nullptr, *o_part = nullptr, *gu_part = nullptr, *down_part = nullptr;
     int* tc_err = nullptr;
@@ -659,7 +756,7 @@ static int32_t encode_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows,
 
 static int32_t cache_build(oxg4_cache* c) {
     oxg4_model* m = c->m;
-    const int B = c->B, L = m->cfg.num_hidden_layers, H = m->H, D = m->D, PT = c->PT;
+    const int B = c->B, L = m->cfg.num_hidden_layers, H = m->H, PT = c->PT;
     const size_t kes = c->kv_dtype == OXG4_BF16 ? 2 : 4;
     // Ring capacities. The reference keeps min(window, max_seq) rows on sliding layers and max_seq on global
     // ones (cache.rs:58-62) and lets the ring itself implement the window. Here a sliding ring keeps
@@ -685,7 +782,6 @@ static int32_t cache_build(oxg4_cache* c) {
         for (int i = 0; i < (capf[b] + PT - 1) / PT; ++i) ptf[(size_t)b * c->pps_full + i] = pages_full++;
         for (int i = 0; i < (caps[b] + PT - 1) / PT; ++i) pts[(size_t)b * c->pps_slide + i] = pages_slide++;
     }
-    // a ring never spans a partial last page: slot -> page look-ups stay inside the sequence's own pages
     TRY(dalloc(c, &c->pt_full, ptf.size()));
     TRY(dalloc(c, &c->pt_slide, pts.size()));
     TRY(dalloc(c, &c->cap_full, B));
@@ -695,44 +791,54 @@ static int32_t cache_build(oxg4_cache* c) {
     CK(cudaMemcpy(c->cap_full, capf.data(), B * 4, cudaMemcpyHostToDevice));
     CK(cudaMemcpy(c->cap_slide, caps.data(), B * 4, cudaMemcpyHostToDevice));
     c->mma_attn = c->kv_dtype == OXG4_BF16 && PT % kAmTile == 0 && getenv("OXG4_DISABLE_MMA_ATTN") == nullptr;
-    c->kpool.resize(L);
-    c->vpool.resize(L);
+    c->kpool.assign(L, nullptr);
+    c->vpool.assign(L, nullptr);
     c->kmap.resize(L);
     c->vmap.resize(L);
-    for (int l = 0; l < L; ++l) {
-        const int pages = m->layers[l].sliding ? pages_slide : pages_full;
-        const size_t bytes = (size_t)pages * m->Nkv * PT * D * kes;
-        uint8_t *k, *v;
-        TRY(dalloc(c, &k, bytes));      // zeroed like the reference's DeviceBuffer::zeroed
-        TRY(dalloc(c, &v, bytes));
-        c->kpool[l] = k;
-        c->vpool[l] = v;
-        c->kv_bytes += 2 * (int64_t)bytes;
-        if (c->mma_attn) {
-            // the pool as a [pages * kv_heads * page_tokens, head_dim] BF16 matrix; boxes of 64 elements x 16 rows
-            TRY(encode_bf16_2d(&c->kmap[l], k, (uint64_t)pages * m->Nkv * PT, (uint64_t)D, kAmTile));
-            TRY(encode_bf16_2d(&c->vmap[l], v, (uint64_t)pages * m->Nkv * PT, (uint64_t)D, kAmTile));
-        }
-    }
-    // split-KV geometry of the one-row attention kernel: enough CTAs to fill the GPU a few times over at the longest context
-    const int pairs = std::max(1, m->Nkv * B);
-    const int want = std::max(1, (8 * m->num_sms + pairs - 1) / pairs);
+    c->attn_splits.assign(L, 1);
     c->min_split = 16;
     c->attn_cluster = true;
-    // clusters of 16 CTAs (non-portable size) only while one CTA per SM is enough for the whole step
-    int cluster_max = 16;
-    if (const char* e = getenv("OXG4_ATTN_CLUSTER_MAX")) cluster_max = std::max(1, std::min(16, atoi(e)));
-    const int cap_splits = pairs * 16 <= m->num_sms ? cluster_max : std::min(cluster_max, 8);
-    auto pow2_floor = [](int v) { int p = 1; while (p * 2 <= v) p *= 2; return p; };
-    c->splits_full = std::max(1, std::min({want, cap_splits, (maxf + c->min_split - 1) / c->min_split}));
-    c->splits_slide = std::max(1, std::min({want, cap_splits, (vis_s + c->min_split - 1) / c->min_split}));
-    if (c->attn_cluster) {
-        c->splits_full = pow2_floor(c->splits_full);
-        c->splits_slide = pow2_floor(c->splits_slide);
+    int smax = 1, part_floats = 1, ticket_n = 1;
+    for (int l = 0; l < L; ++l) {
+        const LayerPlan& p = m->layers[l];
+        if (p.shared) {
+            // a KV-shared layer reads the pools of its source layer (cache.rs:70-84)
+            c->kpool[l] = c->kpool[p.source];
+            c->vpool[l] = c->vpool[p.source];
+            c->kmap[l] = c->kmap[p.source];
+            c->vmap[l] = c->vmap[p.source];
+        } else {
+            const int pages = p.sliding ? pages_slide : pages_full;
+            const size_t bytes = (size_t)pages * p.Nkv * PT * p.D * kes;
+            uint8_t *k, *v;
+            TRY(dalloc(c, &k, bytes));      // zeroed like the reference's DeviceBuffer::zeroed
+            TRY(dalloc(c, &v, bytes));
+            c->kpool[l] = k;
+            c->vpool[l] = v;
+            c->kv_bytes += 2 * (int64_t)bytes;
+            ++c->physical_caches;
+            if (c->mma_attn) {
+                // the pool as a [pages * kv_heads * page_tokens, head_dim] BF16 matrix; boxes of 64 elements x 16 rows
+                TRY(encode_bf16_2d(&c->kmap[l], k, (uint64_t)pages * p.Nkv * PT, (uint64_t)p.D, kAmTile));
+                TRY(encode_bf16_2d(&c->vmap[l], v, (uint64_t)pages * p.Nkv * PT, (uint64_t)p.D, kAmTile));
+            }
+        }
+        // split-KV geometry of the one-row attention kernel: enough CTAs to fill the GPU a few times over at the longest context
+        const int pairs = std::max(1, p.Nkv * B);
+        const int want = std::max(1, (8 * m->num_sms + pairs - 1) / pairs);
+        // clusters of 16 CTAs (non-portable size) only while one CTA per SM is enough for the whole step
+        int cluster_max = 16;
+        if (const char* e = getenv("OXG4_ATTN_CLUSTER_MAX")) cluster_max = std::max(1, std::min(16, atoi(e)));
+        const int cap_splits = pairs * 16 <= m->num_sms ? cluster_max : std::min(cluster_max, 8);
+        auto pow2_floor = [](int v) { int q = 1; while (q * 2 <= v) q *= 2; return q; };
+        const int vis = p.sliding ? vis_s : maxf;
+        c->attn_splits[l] = pow2_floor(std::max(1, std::min({want, cap_splits, (vis + c->min_split - 1) / c->min_split})));
+        smax = std::max(smax, c->attn_splits[l]);
+        part_floats = std::max(part_floats, p.Nkv * c->attn_splits[l] * p.G * (p.D + 2));
+        ticket_n = std::max(ticket_n, p.Nkv);
     }
-    const int smax = std::max(c->splits_full, c->splits_slide);
     const int R = c->rows_cap = std::max(B, kPrefillRows);
-    const int qw = m->Nq * D;
+    const int qw = m->qw_max;
     TRY(dalloc(c, &c->tokens, B));
     TRY(dalloc(c, &c->pos, B));
     TRY(dalloc(c, &c->seen, (size_t)B * m->V));
@@ -740,14 +846,14 @@ static int32_t cache_build(oxg4_cache* c) {
     TRY(dalloc(c, &c->rng, B));
     TRY(dalloc(c, &c->hA, (size_t)R * H));
     TRY(dalloc(c, &c->hB, (size_t)R * H));
-    TRY(dalloc(c, &c->qkv_raw, (size_t)R * m->p_qkv.N));
+    TRY(dalloc(c, &c->qkv_raw, (size_t)R * m->qkv_n_max));
     TRY(dalloc(c, &c->attn_out, (size_t)R * qw));
     TRY(dalloc(c, &c->o_raw, (size_t)R * H));
     TRY(dalloc(c, &c->gu_raw, (size_t)R * m->I));
     TRY(dalloc(c, &c->down_raw, (size_t)R * H));
     TRY(dalloc(c, &c->logits, (size_t)B * m->V));
-    TRY(dalloc(c, &c->attn_part, (size_t)R * m->Nkv * smax * m->G * (D + 2)));
-    TRY(dalloc(c, &c->attn_ticket, (size_t)R * m->Nkv));
+    TRY(dalloc(c, &c->attn_part, (size_t)R * part_floats));
+    TRY(dalloc(c, &c->attn_ticket, (size_t)R * ticket_n));
     TRY(dalloc(c, &c->lm_ticket, (size_t)B + 1));
     TRY(dalloc(c, &c->blk_best, (size_t)B * m->num_sms));
     const int chunks = (m->V + kTopkChunk - 1) / kTopkChunk;
@@ -767,13 +873,15 @@ static int32_t cache_build(oxg4_cache* c) {
     TRY(dalloc(c, &c->pf_tok, kPrefillRows));
     TRY(dalloc(c, &c->pf_pos, kPrefillRows));
     TRY(dalloc(c, &c->pf_seq, kPrefillRows));
-    TRY(dalloc(c, &c->pf_grp_row0, kAmMaxGroups));
-    TRY(dalloc(c, &c->pf_grp_n, kAmMaxGroups));
+    for (int k = 0; k < 2; ++k) {
+        TRY(dalloc(c, &c->pf_grp_row0[k], kAmMaxGroups));
+        TRY(dalloc(c, &c->pf_grp_n[k], kAmMaxGroups));
+    }
     TRY(dalloc(c, &c->last_h, (size_t)B * H));
     TRY(dalloc(c, &c->last_raw, (size_t)B * H));
     TRY(dalloc(c, &c->last_x, (size_t)B * H));
     CK(cudaMallocHost(&c->h_pf_tok, sizeof(uint32_t) * kPrefillRows));
-    CK(cudaMallocHost(&c->h_pf_meta, sizeof(int32_t) * (2 * kPrefillRows + 2 * kAmMaxGroups)));
+    CK(cudaMallocHost(&c->h_pf_meta, sizeof(int32_t) * (2 * kPrefillRows + 4 * kAmMaxGroups)));
     {
         std::vector<int32_t> r0(B), ones(B, 1);
         for (int b = 0; b < B; ++b) r0[b] = b;
@@ -785,35 +893,58 @@ static int32_t cache_build(oxg4_cache* c) {
     TRY(dalloc(c, &c->tc_err, 1));
     if (c->mma_attn) {
         TRY(attn_mma_setup());
-        TRY(dalloc(c, &c->q_hl, (size_t)R * m->Nq * 2 * D));
+        int kvh_max = 1;
+        for (auto& p : m->layers) kvh_max = std::max(kvh_max, p.Nkv);
+        TRY(dalloc(c, &c->q_hl, (size_t)R * 2 * m->qw_max));
         const int warps = m->num_sms * 4;                       // upper bound of the consumer warps of a launch
-        TRY(dalloc(c, &c->am_part, ((size_t)std::min(R, kAmMaxGroups) * m->Nkv + warps) * kAmRows * (D + 2)));
+        TRY(dalloc(c, &c->am_part, ((size_t)std::min(R, kAmMaxGroups) * kvh_max + warps) * kAmRows * (m->Dmax + 2)));
     }
-    c->tc_ok = m->es == 2 && getenv("OXG4_DISABLE_TCGEN05") == nullptr;
+    // models with per-layer embeddings run through the small-batch kernels only (the extra projections per layer
+    // are tiny and have no tcgen05 variant)
+    c->tc_ok = m->es == 2 && m->P == 0 && getenv("OXG4_DISABLE_TCGEN05") == nullptr;
     c->use_tc = c->tc_ok && B >= 8 && B <= 64;
+    c->ls_qkv.assign(L, 1);
+    c->ls_o.assign(L, 1);
+    c->lps_qkv.assign(L, 1);
+    c->lps_o.assign(L, 1);
+    if (m->P > 0) {
+        const size_t lp = (size_t)L * m->P;
+        TRY(dalloc(c, &c->ple_emb, (size_t)R * H));
+        TRY(dalloc(c, &c->ple_ctx, (size_t)R * lp));
+        TRY(dalloc(c, &c->ple_packed, (size_t)R * lp));
+        TRY(dalloc(c, &c->ple_h, (size_t)R * H));
+        TRY(dalloc(c, &c->ple_gate, (size_t)R * m->P));
+        TRY(dalloc(c, &c->ple_act, (size_t)R * m->P));
+        TRY(dalloc(c, &c->ple_raw, (size_t)R * H));
+    }
     if (c->tc_ok) {
         TRY(tc_gemm_setup());
         const int sms = m->num_sms;
         auto tiles = [](int n) { return (n + kTcTileM - 1) / kTcTileM; };
         auto kbs = [](int k) { return (k + kTcTileK - 1) / kTcTileK; };
-        const int nqkv = m->p_qkv.N;
         const int Bd = std::min(B, 64);
-        c->s_qkv = tc_pick_splits(tiles(nqkv), kbs(H), sms, Bd, nqkv, H);
-        c->s_o = tc_pick_splits(tiles(H), kbs(qw), sms, Bd, H, qw);
+        size_t qkv_part_n = 1, o_part_n = 1;
+        auto rows_splits = [&](int sd, int sp) { return (size_t)std::max(sd * B, sp * kPrefillRows); };
+        for (int l = 0; l < L; ++l) {
+            const LayerPlan& p = m->layers[l];
+            c->ls_qkv[l] = tc_pick_splits(tiles(p.qkv_n), kbs(H), sms, Bd, p.qkv_n, H);
+            c->ls_o[l] = tc_pick_splits(tiles(H), kbs(p.qw), sms, Bd, H, p.qw);
+            // a full chunk is one 256-row block per weight tile (UMMA N = 256): K-splits fill the SMs where a projection
+            // has few tiles; their partial outputs are cheap next to the tensor-core work of 256 rows
+            c->lps_qkv[l] = tc_pick_splits(tiles(p.qkv_n), kbs(H), sms, kPrefillRows, p.qkv_n, H, 1.0);
+            c->lps_o[l] = tc_pick_splits(tiles(H), kbs(p.qw), sms, kPrefillRows, H, p.qw, 1.0);
+            qkv_part_n = std::max(qkv_part_n, rows_splits(c->ls_qkv[l], c->lps_qkv[l]) * p.qkv_n);
+            o_part_n = std::max(o_part_n, rows_splits(c->ls_o[l], c->lps_o[l]) * H);
+        }
         c->s_gu = tc_pick_splits(2 * tiles(m->I), kbs(H), sms, Bd, 2 * m->I, H);
         c->s_down = tc_pick_splits(tiles(H), kbs(m->I), sms, Bd, H, m->I);
-        // a full chunk is one 256-row block per weight tile (UMMA N = 256): K-splits fill the SMs where a projection
-        // has few tiles; their partial outputs are cheap next to the tensor-core work of 256 rows
-        c->ps_qkv = tc_pick_splits(tiles(nqkv), kbs(H), sms, kPrefillRows, nqkv, H, 1.0);
-        c->ps_o = tc_pick_splits(tiles(H), kbs(qw), sms, kPrefillRows, H, qw, 1.0);
         c->ps_gu = tc_pick_splits(2 * tiles(m->I), kbs(H), sms, kPrefillRows, 2 * m->I, H, 1.0);
         c->ps_down = tc_pick_splits(tiles(H), kbs(m->I), sms, kPrefillRows, H, m->I, 1.0);
-        auto rows_splits = [&](int sd, int sp) { return (size_t)std::max(sd * B, sp * kPrefillRows); };
         TRY(dalloc(c, &c->x_h, (size_t)R * H));
         TRY(dalloc(c, &c->x_a, (size_t)R * qw));
         TRY(dalloc(c, &c->x_i, (size_t)R * m->I));
-        TRY(dalloc(c, &c->qkv_part, rows_splits(c->s_qkv, c->ps_qkv) * nqkv));
-        TRY(dalloc(c, &c->o_part, rows_splits(c->s_o, c->ps_o) * H));
+        TRY(dalloc(c, &c->qkv_part, qkv_part_n));
+        TRY(dalloc(c, &c->o_part, o_part_n));
         TRY(dalloc(c, &c->gu_part, rows_splits(c->s_gu, c->ps_gu) * 2 * m->I));
         TRY(dalloc(c, &c->down_part, rows_splits(c->s_down, c->ps_down) * H));
         if (m->tp > 1 && c->use_tc) {
@@ -944,8 +1075,8 @@ extern "C" int32_t oxg4_cache_info_get(const oxg4_cache* c, oxg4_cache_info* o) 
     if (!c || !o) return fail(OXG4_INVALID_ARGUMENT, "null argument");
     o->batch = c->B;
     o->layer_count = c->m->cfg.num_hidden_layers;
-    o->physical_cache_count = c->m->cfg.num_hidden_layers;
-    o->shared_layer_count = 0;
+    o->physical_cache_count = c->physical_caches;
+    o->shared_layer_count = c->m->cfg.num_hidden_layers - c->physical_caches;
     o->page_tokens = c->PT;
     o->kv_dtype = c->kv_dtype;
     o->kv_bytes = c->kv_bytes;
@@ -1309,9 +1440,11 @@ struct RowSet {
     const int32_t* pos = nullptr;        // device [R]
     const int32_t* seq = nullptr;        // device [R], or null: row r is sequence r
     bool chunk = false;                  // prompt chunk: all K/V rows are appended before any token attends
-    const int32_t* grp_row0 = nullptr;   // attention groups (consecutive tokens of one sequence)
-    const int32_t* grp_n = nullptr;
-    int NG = 0, part_rows = 0;
+    // attention groups (consecutive tokens of one sequence), per layer kind (0 sliding, 1 global): a group holds
+    // up to 8 / G tokens and G (query heads per KV head) may differ between the kinds
+    const int32_t* grp_row0[2] = {nullptr, nullptr};
+    const int32_t* grp_n[2] = {nullptr, nullptr};
+    int NG[2] = {0, 0};
 };
 
 // Launches every kernel of one step on the model's stream (eagerly or under stream capture).
@@ -1326,24 +1459,28 @@ static void launch_attention(Launcher& ln, oxg4_cache* c, const RowSet& rs, int 
                              uint16_t* out_bf16, bool many_rows) {
     oxg4_model* m = c->m;
     const LayerPlan& p = m->layers[l];
-    const int D = m->D, R = rs.R;
+    const int D = p.D, R = rs.R, kind = p.sliding ? 0 : 1;
     const int32_t* page_table = p.sliding ? c->pt_slide : c->pt_full;
     const int pps = p.sliding ? c->pps_slide : c->pps_full;
     const int32_t* cap = p.sliding ? c->cap_slide : c->cap_full;
     const int window = p.sliding ? m->cfg.sliding_window : 0x7fffffff;
     const bool use_mma = c->mma_attn && (many_rows || rs.chunk);
-    if (use_mma || rs.chunk) {
+    // K and V of the rows are in the cache before the attention kernel starts: rows of a prompt chunk (appended by
+    // qkv_post_kernel), and every row of a KV-shared layer (its source layer appended them earlier in the step)
+    const bool kv_in_cache = rs.chunk || p.shared;
+    if (use_mma || (rs.chunk && !p.shared)) {
         // norms, RoPE and the K/V append of every row first (a chunk's later tokens are visible to none of its earlier ones
         // only through the causal mask, so all rows may be in the cache before attention starts)
         QkvPostArgs q{};
-        q.qkv = qkv; q.qkv_n = m->p_qkv.N; q.splits = qkv_splits; q.R = R; q.Nq = m->Nq; q.Nkv = m->Nkv;
+        q.qkv = qkv; q.qkv_n = p.qkv_n; q.splits = qkv_splits; q.R = R; q.Nq = m->Nq; q.Nkv = p.Nkv;
         q.q_norm = p.q_norm; q.k_norm = p.k_norm; q.inv_freq = p.inv_freq; q.rotary_half = p.rotary_dim / 2;
         q.eps = m->cfg.rms_norm_eps;
         q.row_pos = rs.pos; q.row_seq = rs.seq; q.row_tok = rs.tok;
         q.kpool = c->kpool[l]; q.vpool = c->vpool[l];
         q.page_table = page_table; q.pages_per_seq = pps; q.page_tokens = c->PT; q.cap = cap;
         q.q_hl = use_mma ? c->q_hl : nullptr;
-        const int per_row = use_mma ? m->Nq + 2 * m->Nkv : 2 * m->Nkv;
+        q.write_kv = p.shared ? 0 : 1;
+        const int per_row = (use_mma ? m->Nq : 0) + (p.shared ? 0 : 2 * p.Nkv);
         void (*fn)(const QkvPostArgs) = nullptr;
         if (c->kv_dtype == OXG4_BF16) fn = D == 64 ? qkv_post_kernel<uint16_t, 64> : D == 128 ? qkv_post_kernel<uint16_t, 128> : qkv_post_kernel<uint16_t, 256>;
         else fn = D == 64 ? qkv_post_kernel<float, 64> : D == 128 ? qkv_post_kernel<float, 128> : qkv_post_kernel<float, 256>;
@@ -1351,12 +1488,12 @@ static void launch_attention(Launcher& ln, oxg4_cache* c, const RowSet& rs, int 
     }
     if (use_mma) {
         AttnMmaArgs a{};
-        a.q_hl = c->q_hl; a.Nq = m->Nq; a.Nkv = m->Nkv; a.NG = rs.NG;
-        a.grp_row0 = rs.grp_row0; a.grp_n = rs.grp_n;
+        a.q_hl = c->q_hl; a.Nq = m->Nq; a.Nkv = p.Nkv; a.NG = rs.NG[kind];
+        a.grp_row0 = rs.grp_row0[kind]; a.grp_n = rs.grp_n[kind];
         a.row_pos = rs.pos; a.row_seq = rs.seq; a.row_tok = rs.tok;
         a.page_table = page_table; a.pages_per_seq = pps; a.page_tokens = c->PT; a.cap = cap;
         a.window = window;
-        a.part_rows = rs.part_rows;
+        a.part_rows = rs.chunk ? kAmRows : p.G;
         a.part = c->am_part;
         a.err = c->tc_err;
         a.out = c->attn_out;
@@ -1365,20 +1502,20 @@ static void launch_attention(Launcher& ln, oxg4_cache* c, const RowSet& rs, int 
         AttnMergeFn merge;
         size_t smem;
         int ncw;
-        pick_attn_mma(D, m->G, &fn, &merge, &smem, &ncw);
+        pick_attn_mma(D, p.G, &fn, &merge, &smem, &ncw);
         a.total_warps = m->num_sms * ncw;
         ln.go("attn", fn, dim3(m->num_sms), dim3((ncw + 1) * 32), smem, c->kmap[l], c->vmap[l], a);
-        ln.go("attn_merge", merge, dim3(rs.NG * m->Nkv), dim3(128), 0, a);
+        ln.go("attn_merge", merge, dim3(rs.NG[kind] * p.Nkv), dim3(128), 0, a);
         return;
     }
     AttnArgs a{};
     a.qkv = qkv;
     a.qkv_splits = qkv_splits;
     a.out_bf16 = out_bf16;
-    a.qkv_n = m->p_qkv.N;
+    a.qkv_n = p.qkv_n;
     a.B = R;
     a.Nq = m->Nq;
-    a.Nkv = m->Nkv;
+    a.Nkv = p.Nkv;
     a.q_norm = p.q_norm;
     a.k_norm = p.k_norm;
     a.inv_freq = p.inv_freq;
@@ -1394,7 +1531,7 @@ static void launch_attention(Launcher& ln, oxg4_cache* c, const RowSet& rs, int 
     a.pages_per_seq = pps;
     a.page_tokens = c->PT;
     a.cap = cap;
-    a.n_splits = p.sliding ? c->splits_slide : c->splits_full;
+    a.n_splits = c->attn_splits[l];
     a.min_split = c->min_split;
     a.part = c->attn_part;
     a.ticket = c->attn_ticket;
@@ -1407,18 +1544,69 @@ static void launch_attention(Launcher& ln, oxg4_cache* c, const RowSet& rs, int 
     }
     a.ts = ln.ts();
     a.ts_mid = ln.ts_base ? ln.ts_base + 4 * (size_t)(kMaxTimeline - 1 - l) : nullptr;   // extra stamps, from the end of the buffer
-    const bool cl = !rs.chunk;                   // decode: cluster merge; chunk rows: K/V already appended, ticket merge
+    const bool cl = !kv_in_cache;                // decode: cluster merge; K/V already in the cache: ticket merge
     // few CTAs (one sequence): 16 warps each to cut latency; many CTAs: 4 warps each so that several
     // fit on an SM (the kernel needs ~90 registers per thread)
-    const int aw = (a.n_splits * m->Nkv * R <= m->num_sms) ? kAttnWarps : 4;
+    const int aw = (a.n_splits * p.Nkv * R <= m->num_sms) ? kAttnWarps : 4;
     // more K/V rows in flight per warp when latency is all that counts (with more than two query heads
     // per kv head the extra rows would spill registers)
-    const bool deep = cl && aw == kAttnWarps && m->G <= 2;
-    auto fn = c->kv_dtype == OXG4_BF16 ? pick_attn<uint16_t>(D, m->G, cl, deep) : pick_attn<float>(D, m->G, cl, deep);
-    const size_t smem = sizeof(float) * (size_t)(m->G * D + 2 * D + 2 * aw * m->G + aw * m->G * D + m->G * (D + 2) + D);
+    const bool deep = cl && aw == kAttnWarps && p.G <= 2;
+    auto fn = c->kv_dtype == OXG4_BF16 ? pick_attn<uint16_t>(D, p.G, cl, deep) : pick_attn<float>(D, p.G, cl, deep);
+    const size_t smem = sizeof(float) * (size_t)(p.G * D + 2 * D + 2 * aw * p.G + aw * p.G * D + p.G * (D + 2) + D);
     ln.cluster_x = cl ? a.n_splits : 0;
-    ln.go("attn", fn, dim3(a.n_splits, m->Nkv, R), dim3(aw * 32), smem, a);
+    ln.go("attn", fn, dim3(a.n_splits, p.Nkv, R), dim3(aw * 32), smem, a);
     ln.cluster_x = 0;
+}
+
+// Per-layer embeddings (Gemma4-E; ple.rs). Once per pass: the packed per-layer inputs of every row.
+static void ple_prepare(oxg4_cache* c, Launcher& ln, const RowSet& rs) {
+    oxg4_model* m = c->m;
+    const int R = rs.R, H = m->H, L = m->cfg.num_hidden_layers, P = m->P;
+    const float scale = sqrtf((float)H);
+    if (m->es == 2)
+        ln.go("ple", ple_embed_rows_kernel<uint16_t>, dim3(R), dim3(256), 0, H, (const uint16_t*)m->embed, rs.tok, scale, c->ple_emb);
+    else
+        ln.go("ple", ple_embed_rows_kernel<float>, dim3(R), dim3(256), 0, H, (const float*)m->embed, rs.tok, scale, c->ple_emb);
+    GemvArgs a{};                       // context = bf16(embedding) . per_layer_model_projection^T (ple.rs:85)
+    a.W0 = m->ple_model_proj;
+    a.in = c->ple_emb;
+    a.out = c->ple_ctx;
+    launch_gemv(ln, "ple", c, R, a, m->p_ple_ctx, PRO_PLAIN, EPI_STORE);
+    const float inv_sqrt_h = 1.0f / sqrtf((float)H), sqrt_p = sqrtf((float)P);
+    const dim3 grid((R * L + 3) / 4);
+    if (m->es == 2)
+        ln.go("ple", ple_pack_kernel<uint16_t>, grid, dim3(128), 0, R, L, P, (const float*)c->ple_ctx, m->ple_proj_norm,
+              (const uint16_t*)m->ple_embed, rs.tok, m->cfg.rms_norm_eps, inv_sqrt_h, sqrt_p, c->ple_packed);
+    else
+        ln.go("ple", ple_pack_kernel<float>, grid, dim3(128), 0, R, L, P, (const float*)c->ple_ctx, m->ple_proj_norm,
+              (const float*)m->ple_embed, rs.tok, m->cfg.rms_norm_eps, inv_sqrt_h, sqrt_p, c->ple_packed);
+}
+
+// apply_ple of layer l (ple.rs:151-185) after the MLP block: h' = h + rmsnorm(down) is closed here, the branch
+// gate -> gelu * per-layer input -> projection is left pending in c->ple_raw; the next kernel's prologue adds
+// rmsnorm(branch, post_per_layer_input_norm) and applies layer_scalar.
+static void ple_layer(oxg4_cache* c, Launcher& ln, const RowSet& rs, int l) {
+    oxg4_model* m = c->m;
+    const LayerPlan& p = m->layers[l];
+    const int R = rs.R, H = m->H, P = m->P;
+    ln.go("ple", ple_close_kernel, dim3(R), dim3(kRowsThreads), 0, H, (const float*)c->hA, (const float*)c->down_raw,
+          p.post_ff_ln, m->cfg.rms_norm_eps, c->ple_h);
+    {
+        GemvArgs a{};
+        a.W0 = p.w_ple_gate;
+        a.in = c->ple_h;
+        a.out = c->ple_gate;
+        launch_gemv(ln, "ple", c, R, a, m->p_ple_gate, PRO_PLAIN, EPI_STORE);
+    }
+    ln.go("ple", ple_act_kernel, dim3((P + kRowsThreads - 1) / kRowsThreads, R), dim3(kRowsThreads), 0, P,
+          m->cfg.num_hidden_layers * P, l, (const float*)c->ple_gate, (const float*)c->ple_packed, c->ple_act);
+    {
+        GemvArgs a{};
+        a.W0 = p.w_ple_proj;
+        a.in = c->ple_act;
+        a.out = c->ple_raw;
+        launch_gemv(ln, "ple", c, R, a, m->p_ple_proj, PRO_PLAIN, EPI_STORE);
+    }
 }
 
 // All layers for the rows of `rs`. On return the last layer's residual update is still pending:
@@ -1426,14 +1614,15 @@ static void launch_attention(Launcher& ln, oxg4_cache* c, const RowSet& rs, int 
 static void run_layers(oxg4_cache* c, Launcher& ln, const RowSet& rs, bool use_tc, bool peer, bool last_layer_prefetch,
                        const TraceCtx* tr) {
     oxg4_model* m = c->m;
-    const int R = rs.R, L = m->cfg.num_hidden_layers, H = m->H, D = m->D;
-    const int s_qkv = rs.chunk ? c->ps_qkv : c->s_qkv, s_o = rs.chunk ? c->ps_o : c->s_o;
+    const int R = rs.R, L = m->cfg.num_hidden_layers, H = m->H;
     const int s_gu = rs.chunk ? c->ps_gu : c->s_gu, s_down = rs.chunk ? c->ps_down : c->s_down;
+    if (m->P > 0) ple_prepare(c, ln, rs);
     for (int l = 0; l < L; ++l) {
         const LayerPlan& p = m->layers[l];
+        const int s_qkv = rs.chunk ? c->lps_qkv[l] : c->ls_qkv[l], s_o = rs.chunk ? c->lps_o[l] : c->ls_o[l];
         if (use_tc) {
             // ---- many rows: tcgen05 projections fed by TMA, per-row kernels around them ----
-            const int nqkv = m->p_qkv.N, qw = m->Nq * D;
+            const int nqkv = p.qkv_n, qw = p.qw;
             auto copy_trace_tc = [&]() {
                 if (tr && ln.status == OXG4_OK &&
                     cudaMemcpyAsync(tr->trace_dev + (size_t)l * R * H, c->hB, sizeof(float) * R * H,
@@ -1521,6 +1710,12 @@ static void run_layers(oxg4_cache* c, Launcher& ln, const RowSet& rs, bool use_t
                 a.embed = m->embed;
                 a.tokens = rs.tok;
                 a.embed_scale = sqrtf((float)H);
+            } else if (m->P > 0) {
+                // the previous layer ended with its per-layer-embedding branch: h = (h' + rmsnorm(branch)) * scalar
+                a.h_in = c->ple_h;
+                a.raw = c->ple_raw;
+                a.w_post = m->layers[l - 1].ple_norm;
+                a.scalar = m->layers[l - 1].layer_scalar;
             } else {
                 a.raw = c->down_raw;
                 a.w_post = m->layers[l - 1].post_ff_ln;
@@ -1529,7 +1724,7 @@ static void run_layers(oxg4_cache* c, Launcher& ln, const RowSet& rs, bool use_t
             a.out = c->qkv_raw;
             if (m->far_prefetch & 1) {
                 a.pf_ptr[0] = p.wo;
-                a.pf_bytes[0] = (unsigned long long)m->p_o.N * m->p_o.K * m->es;
+                a.pf_bytes[0] = (unsigned long long)p.p_o.N * p.p_o.K * m->es;
             }
             auto copy_trace = [&]() {
                 if (tr && ln.status == OXG4_OK &&
@@ -1537,7 +1732,7 @@ static void run_layers(oxg4_cache* c, Launcher& ln, const RowSet& rs, bool use_t
                                     cudaMemcpyDeviceToDevice, m->stream) != cudaSuccess)
                     ln.status = fail(OXG4_CUDA, "Gemma 4 CUDA error: trace copy failed");
             };
-            launch_gemv(ln, "qkv", c, R, a, m->p_qkv, PRO_NORM, EPI_STORE);
+            launch_gemv(ln, "qkv", c, R, a, p.p_qkv, PRO_NORM, EPI_STORE);
             copy_trace();          // the layer's input as this library computed it
             if (tr && tr->inject_dev) {
                 // layer-wise teacher forcing: redo the projection from the forced input, nothing pending
@@ -1546,7 +1741,7 @@ static void run_layers(oxg4_cache* c, Launcher& ln, const RowSet& rs, bool use_t
                 a.w_post = nullptr;
                 a.scalar = 1.0f;
                 a.h_in = tr->inject_dev + (size_t)l * R * H;
-                launch_gemv(ln, "qkv", c, R, a, m->p_qkv, PRO_NORM, EPI_STORE);
+                launch_gemv(ln, "qkv", c, R, a, p.p_qkv, PRO_NORM, EPI_STORE);
             }
         }
         launch_attention(ln, c, rs, l, c->qkv_raw, 1, nullptr, false);
@@ -1555,7 +1750,7 @@ static void run_layers(oxg4_cache* c, Launcher& ln, const RowSet& rs, bool use_t
             a.W0 = p.wo;
             a.in = c->attn_out;
             a.out = c->o_raw;
-            launch_gemv(ln, "o", c, R, a, m->p_o, PRO_PLAIN, EPI_STORE);
+            launch_gemv(ln, "o", c, R, a, p.p_o, PRO_PLAIN, EPI_STORE);
             ln.allreduce(c->o_raw, (size_t)R * H);        // row-split projection: sum the ranks' partial outputs
         }
         {   // post-attention norm + residual, pre-FF norm, gate and up projections (decode.rs:161-171, 14-16)
@@ -1583,7 +1778,7 @@ static void run_layers(oxg4_cache* c, Launcher& ln, const RowSet& rs, bool use_t
             if (m->far_prefetch & 8) {
                 if (l + 1 < L) {
                     a.pf_ptr[0] = m->layers[l + 1].wqkv;
-                    a.pf_bytes[0] = (unsigned long long)m->p_qkv.N * m->p_qkv.K * m->es;
+                    a.pf_bytes[0] = (unsigned long long)m->layers[l + 1].p_qkv.N * m->layers[l + 1].p_qkv.K * m->es;
                 } else if (last_layer_prefetch) {
                     a.pf_ptr[0] = (const char*)m->embed + (size_t)m->v0 * H * m->es;
                     a.pf_bytes[0] = std::min<unsigned long long>((unsigned long long)m->Vloc * H * m->es, 64ull << 20);
@@ -1592,6 +1787,7 @@ static void run_layers(oxg4_cache* c, Launcher& ln, const RowSet& rs, bool use_t
             launch_gemv(ln, "down", c, R, a, m->p_down, PRO_PLAIN, EPI_STORE);
             ln.allreduce(c->down_raw, (size_t)R * H);
         }
+        if (m->P > 0) ple_layer(c, ln, rs, l);
     }
 }
 
@@ -1667,7 +1863,7 @@ static void lm_head(oxg4_cache* c, Launcher& ln, int kind, int top_k, float pena
     a.h_in = h_in;
     a.h_out = c->hB;
     a.raw = raw;
-    a.w_post = m->layers[L - 1].post_ff_ln;
+    a.w_post = m->P > 0 ? m->layers[L - 1].ple_norm : m->layers[L - 1].post_ff_ln;
     a.scalar = m->layers[L - 1].layer_scalar;
     a.w_norm = m->final_norm;
     const bool want_logits = (kind == STEP_LOGITS) || top_k > 1;
@@ -1719,14 +1915,16 @@ static int32_t run_step(oxg4_cache* c, int kind, int top_k, float penalty, int* 
     rs.R = B;
     rs.tok = c->tokens;
     rs.pos = c->pos;
-    rs.grp_row0 = c->dec_grp_row0;
-    rs.grp_n = c->dec_grp_n;
-    rs.NG = B;
-    rs.part_rows = m->G;
+    for (int k = 0; k < 2; ++k) {        // decode: one token per group, whatever the layer kind
+        rs.grp_row0[k] = c->dec_grp_row0;
+        rs.grp_n[k] = c->dec_grp_n;
+        rs.NG[k] = B;
+    }
     run_layers(c, ln, rs, c->use_tc, peer, kind != STEP_PREFILL, tr);
     if (kind != STEP_PREFILL) {
         if (c->use_tc) closing_norm_tc(c, ln, B, false, peer);
-        lm_head(c, ln, kind, top_k, penalty, c->use_tc, c->x_h, c->hA, c->down_raw, tr);
+        const bool ple = m->P > 0;       // the last layer's pending update is then its per-layer-embedding branch
+        lm_head(c, ln, kind, top_k, penalty, c->use_tc, c->x_h, ple ? c->ple_h : c->hA, ple ? c->ple_raw : c->down_raw, tr);
     }
     if (kind == STEP_TOPK && top_k > 1)      // a no-op unless the step's control words ask for a sampled token
         ln.go("sample", sample_candidates_kernel, dim3(1), dim3(64), 0, B, top_k, m->cfg.final_logit_softcapping,
@@ -1785,6 +1983,8 @@ static int32_t check_tokens(oxg4_cache* c, const uint32_t* tokens, bool allow_in
         }
         if (tokens[b] >= (uint32_t)c->m->V)
             return fail(OXG4_INVALID_ARGUMENT, "token id exceeds CUDA decode vocabulary");     // decode.rs:675-679
+        if (c->m->P > 0 && tokens[b] >= (uint32_t)c->m->cfg.vocab_size_per_layer_input)
+            return fail(OXG4_INVALID_SHAPE, "invalid batched PLE input");                       // ple.rs:113-119
         if (c->pos_host[b] >= c->max_seq[b])
             return fail(OXG4_INVALID_SHAPE, "sequence %d is longer than the cache table's max_sequence", b);
     }
@@ -2092,8 +2292,11 @@ extern "C" int32_t oxg4_prefill(oxg4_model* m, oxg4_cache* c, const uint32_t* to
         if (lens[b] > c->max_seq[b]) return fail(OXG4_INVALID_SHAPE, "prompt does not fit the cache table");
         off[b + 1] = off[b] + lens[b];
     }
-    for (int64_t i = 0; i < off[B]; ++i)
+    for (int64_t i = 0; i < off[B]; ++i) {
         if (tokens[i] >= (uint32_t)m->V) return fail(OXG4_INVALID_ARGUMENT, "token id exceeds CUDA decode vocabulary");
+        if (m->P > 0 && tokens[i] >= (uint32_t)m->cfg.vocab_size_per_layer_input)
+            return fail(OXG4_INVALID_SHAPE, "invalid batched PLE input");                       // ple.rs:113-119
+    }
     TRY(bind_device(m));
     if (getenv("OXG4_PREFILL_BY_TOKEN")) {
         // the reference's sequential alternative (prefill_token, decode.rs:464-472): one token per sequence and step
@@ -2109,14 +2312,16 @@ extern "C" int32_t oxg4_prefill(oxg4_model* m, oxg4_cache* c, const uint32_t* to
         return oxg4_prefill_token(m, c, step_tokens.data());
     }
     const bool use_tc = c->tc_ok;
-    const int tg = std::max(1, kAmRows / m->G);               // tokens per attention group
+    // tokens per attention group, per layer kind (0 sliding, 1 global): 8 / (query heads per KV head)
+    int tg[2] = {1, 1};
+    for (auto& lp : m->layers) tg[lp.sliding ? 0 : 1] = std::max(1, kAmRows / lp.G);
     int32_t* h_pos = c->h_pf_meta;
     int32_t* h_seq = h_pos + kPrefillRows;
-    int32_t* h_g0 = h_seq + kPrefillRows;
-    int32_t* h_gn = h_g0 + kAmMaxGroups;
+    int32_t* h_g0[2] = {h_seq + kPrefillRows, h_seq + kPrefillRows + 2 * kAmMaxGroups};
+    int32_t* h_gn[2] = {h_g0[0] + kAmMaxGroups, h_g0[1] + kAmMaxGroups};
     int b = 0, p = 0;                                          // next token to place: sequence b, position p
     while (b < B) {
-        int R = 0, NG = 0;
+        int R = 0, NG[2] = {0, 0};
         std::vector<std::pair<int, int>> finishing;            // (sequence, row) of every last prompt token in this chunk
         while (b < B && R < kPrefillRows) {
             const int take = std::min(kPrefillRows - R, lens[b] - p);
@@ -2125,7 +2330,12 @@ extern "C" int32_t oxg4_prefill(oxg4_model* m, oxg4_cache* c, const uint32_t* to
                 h_pos[R + i] = p + i;
                 h_seq[R + i] = b;
             }
-            for (int i = 0; i < take; i += tg) { h_g0[NG] = R + i; h_gn[NG] = std::min(tg, take - i); ++NG; }
+            for (int k = 0; k < 2; ++k)
+                for (int i = 0; i < take; i += tg[k]) {
+                    h_g0[k][NG[k]] = R + i;
+                    h_gn[k][NG[k]] = std::min(tg[k], take - i);
+                    ++NG[k];
+                }
             R += take;
             p += take;
             if (p == lens[b]) { finishing.push_back({b, R - 1}); ++b; p = 0; }
@@ -2134,8 +2344,10 @@ extern "C" int32_t oxg4_prefill(oxg4_model* m, oxg4_cache* c, const uint32_t* to
         CK(cudaMemcpyAsync(c->pf_tok, c->h_pf_tok, sizeof(uint32_t) * R, cudaMemcpyHostToDevice, st));
         CK(cudaMemcpyAsync(c->pf_pos, h_pos, sizeof(int32_t) * R, cudaMemcpyHostToDevice, st));
         CK(cudaMemcpyAsync(c->pf_seq, h_seq, sizeof(int32_t) * R, cudaMemcpyHostToDevice, st));
-        CK(cudaMemcpyAsync(c->pf_grp_row0, h_g0, sizeof(int32_t) * NG, cudaMemcpyHostToDevice, st));
-        CK(cudaMemcpyAsync(c->pf_grp_n, h_gn, sizeof(int32_t) * NG, cudaMemcpyHostToDevice, st));
+        for (int k = 0; k < 2; ++k) {
+            CK(cudaMemcpyAsync(c->pf_grp_row0[k], h_g0[k], sizeof(int32_t) * NG[k], cudaMemcpyHostToDevice, st));
+            CK(cudaMemcpyAsync(c->pf_grp_n[k], h_gn[k], sizeof(int32_t) * NG[k], cudaMemcpyHostToDevice, st));
+        }
         const bool prof = getenv("GEMMA4_PROFILE") != nullptr && getenv("OXG4_PROFILE_PREFILL") != nullptr;
         m->profiling = prof;           // events around every launch of the chunk (a measurement aid, like the reference's GEMMA4_PROFILE)
         Launcher ln{m};
@@ -2145,10 +2357,11 @@ extern "C" int32_t oxg4_prefill(oxg4_model* m, oxg4_cache* c, const uint32_t* to
         rs.pos = c->pf_pos;
         rs.seq = c->pf_seq;
         rs.chunk = true;
-        rs.grp_row0 = c->pf_grp_row0;
-        rs.grp_n = c->pf_grp_n;
-        rs.NG = NG;
-        rs.part_rows = kAmRows;
+        for (int k = 0; k < 2; ++k) {
+            rs.grp_row0[k] = c->pf_grp_row0[k];
+            rs.grp_n[k] = c->pf_grp_n[k];
+            rs.NG[k] = NG[k];
+        }
         run_layers(c, ln, rs, use_tc, false, false, nullptr);
         if (last_logits && !finishing.empty() && ln.status == OXG4_OK) {
             // keep what the LM head will need of every sequence that ends in this chunk
@@ -2158,9 +2371,12 @@ extern "C" int32_t oxg4_prefill(oxg4_model* m, oxg4_cache* c, const uint32_t* to
                     CK(cudaMemcpyAsync(c->last_x + (size_t)f.first * H, c->x_h + (size_t)f.second * H, sizeof(uint16_t) * H,
                                        cudaMemcpyDeviceToDevice, st));
                 } else {
-                    CK(cudaMemcpyAsync(c->last_h + (size_t)f.first * H, c->hA + (size_t)f.second * H, sizeof(float) * H,
+                    // the last layer's pending update: the MLP block's output, or with per-layer embeddings that branch
+                    const float* h_src = m->P > 0 ? c->ple_h : c->hA;
+                    const float* raw_src = m->P > 0 ? c->ple_raw : c->down_raw;
+                    CK(cudaMemcpyAsync(c->last_h + (size_t)f.first * H, h_src + (size_t)f.second * H, sizeof(float) * H,
                                        cudaMemcpyDeviceToDevice, st));
-                    CK(cudaMemcpyAsync(c->last_raw + (size_t)f.first * H, c->down_raw + (size_t)f.second * H,
+                    CK(cudaMemcpyAsync(c->last_raw + (size_t)f.first * H, raw_src + (size_t)f.second * H,
                                        sizeof(float) * H, cudaMemcpyDeviceToDevice, st));
                 }
             }

@@ -82,8 +82,10 @@ class Gemma4TextConfig:
         self.rope_parameters = d.get("rope_parameters")
         self.final_logit_softcapping = d.get("final_logit_softcapping")
         self.hidden_size_per_layer_input = d.get("hidden_size_per_layer_input", 256)
+        self.vocab_size_per_layer_input = d.get("vocab_size_per_layer_input", 262144)
         self.num_kv_shared_layers = d.get("num_kv_shared_layers", 0)
         self.attention_k_eq_v = d.get("attention_k_eq_v", False)
+        self.num_global_key_value_heads = d.get("num_global_key_value_heads")
         self.tie_word_embeddings = d.get("tie_word_embeddings", True)
         self.finish()
 
@@ -140,7 +142,9 @@ def _native_config(config: "Gemma4TextConfig", weight_dtype: int, norm_weight_of
         config.rms_norm_eps, float(config.final_logit_softcapping or 0.0), weight_dtype, norm_weight_offset,
         sliding.ctypes.data_as(C.POINTER(C.c_int32)), rot.ctypes.data_as(C.POINTER(C.c_int32)),
         theta.ctypes.data_as(C.POINTER(C.c_float)), factor.ctypes.data_as(C.POINTER(C.c_float)),
-        tp_rank, tp_size)
+        tp_rank, tp_size, int(config.num_global_key_value_heads or 0), int(bool(config.attention_k_eq_v)),
+        int(config.num_kv_shared_layers or 0), int(config.hidden_size_per_layer_input or 0),
+        int(config.vocab_size_per_layer_input or 0))
     return c, (sliding, rot, theta, factor)
 
 

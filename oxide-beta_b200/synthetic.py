@@ -72,6 +72,19 @@ CONFIGS = {
 }
 
 
+def e_tiny_cfg() -> dict:
+    """A tiny configuration with the Gemma4-E features switched on (parity tests and the HF fixture): six layers
+    (s, s, g, s, s, g), head_dim 64 / global_head_dim 128 with proportional RoPE at a quarter of the dimensions on
+    the global layers, the last two layers KV-shared (layer 4 reads layer 3's cache, layer 5 reads layer 2's),
+    per-layer embeddings of width 32."""
+    c = _cfg(512, 128, 6, 4, 2, 64, 256, 16, ["sliding_attention", "sliding_attention", "full_attention",
+                                             "sliding_attention", "sliding_attention", "full_attention"])
+    c.update(global_head_dim=128, num_kv_shared_layers=2, hidden_size_per_layer_input=32,
+             vocab_size_per_layer_input=512)
+    c["rope_parameters"]["full_attention"].update(rope_type="proportional", partial_rotary_factor=0.25)
+    return c
+
+
 def workload(name: str) -> dict:
     w = CONFIGS[name]
     return dict(w, cfg=json.loads(json.dumps(w["cfg"])))
@@ -88,20 +101,41 @@ def scaled_down(cfg: dict, layers=None, vocab=None) -> dict:
     return c
 
 
+def layer_geometry(cfg: dict, l: int):
+    """(head_dim, kv_heads, shares_kv) of layer l: global layers use global_head_dim and, with
+    attention_k_eq_v, num_global_key_value_heads (gemma4_cuda/mod.rs:391-395, cache.rs:63-68); the last
+    num_kv_shared_layers layers read an earlier layer's cache and have a q projection only (cache.rs:43-86)."""
+    sliding = cfg["layer_types"][l] == "sliding_attention"
+    D = cfg["head_dim"] if sliding else cfg.get("global_head_dim", cfg["head_dim"])
+    kvh = cfg["num_key_value_heads"]
+    if not sliding and cfg.get("attention_k_eq_v") and cfg.get("num_global_key_value_heads"):
+        kvh = cfg["num_global_key_value_heads"]
+    shared = l >= cfg["num_hidden_layers"] - int(cfg.get("num_kv_shared_layers") or 0)
+    return D, kvh, shared
+
+
 def weight_names(cfg: dict):
     """(name, shape, kind) in generation order. kind: 'matrix' | 'ones'."""
-    H, D = cfg["hidden_size"], cfg["head_dim"]
-    Nq, Nkv, I = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["intermediate_size"]
+    H = cfg["hidden_size"]
+    Nq, I, L = cfg["num_attention_heads"], cfg["intermediate_size"], cfg["num_hidden_layers"]
+    P = int(cfg.get("hidden_size_per_layer_input") or 0)
     out = [("embed_tokens.weight", (cfg["vocab_size"], H), "matrix")]
-    for l in range(cfg["num_hidden_layers"]):
+    if P:
+        out += [("embed_tokens_per_layer.weight", (cfg["vocab_size_per_layer_input"], L * P), "matrix"),
+                ("per_layer_model_projection.weight", (L * P, H), "matrix"),
+                ("per_layer_projection_norm.weight", (P,), "ones")]
+    for l in range(L):
         p = f"layers.{l}."
+        D, Nkv, shared = layer_geometry(cfg, l)
+        out += [(p + "input_layernorm.weight", (H,), "ones"),
+                (p + "self_attn.q_proj.weight", (Nq * D, H), "matrix")]
+        if not shared:
+            out += [(p + "self_attn.k_proj.weight", (Nkv * D, H), "matrix"),
+                    (p + "self_attn.v_proj.weight", (Nkv * D, H), "matrix")]
+        out.append((p + "self_attn.q_norm.weight", (D,), "ones"))
+        if not shared:
+            out.append((p + "self_attn.k_norm.weight", (D,), "ones"))
         out += [
-            (p + "input_layernorm.weight", (H,), "ones"),
-            (p + "self_attn.q_proj.weight", (Nq * D, H), "matrix"),
-            (p + "self_attn.k_proj.weight", (Nkv * D, H), "matrix"),
-            (p + "self_attn.v_proj.weight", (Nkv * D, H), "matrix"),
-            (p + "self_attn.q_norm.weight", (D,), "ones"),
-            (p + "self_attn.k_norm.weight", (D,), "ones"),
             (p + "self_attn.o_proj.weight", (H, Nq * D), "matrix"),
             (p + "post_attention_layernorm.weight", (H,), "ones"),
             (p + "pre_feedforward_layernorm.weight", (H,), "ones"),
@@ -109,8 +143,12 @@ def weight_names(cfg: dict):
             (p + "mlp.up_proj.weight", (I, H), "matrix"),
             (p + "mlp.down_proj.weight", (H, I), "matrix"),
             (p + "post_feedforward_layernorm.weight", (H,), "ones"),
-            (p + "layer_scalar", (1,), "ones"),
         ]
+        if P:
+            out += [(p + "per_layer_input_gate.weight", (P, H), "matrix"),
+                    (p + "per_layer_projection.weight", (H, P), "matrix"),
+                    (p + "post_per_layer_input_norm.weight", (H,), "ones")]
+        out.append((p + "layer_scalar", (1,), "ones"))
     out.append(("norm.weight", (H,), "ones"))
     return out
 

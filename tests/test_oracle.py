@@ -287,3 +287,34 @@ def test_softcap_applied_to_returned_scores():
     ids_b, sc_b = capped.new_cache(4).decode_topk(5, 8, 1.0, True)
     assert ids_a.tolist() == ids_b.tolist()          # monotonic: the order of the candidates is unchanged
     np.testing.assert_allclose(sc_b, np.tanh(sc_a / np.float32(0.5)) * np.float32(0.5), rtol=0, atol=1e-6)
+
+
+# ---- Gemma4-E features, pinned by Hugging Face Transformers --------------------------------------------------
+
+def test_e_features_match_hf_fixture():
+    """global_head_dim != head_dim with proportional partial RoPE, KV-shared layers and per-layer embeddings
+    (gemma4_cuda/mod.rs:371-413, cache.rs:43-86, ple.rs:55-185) against tests/golden/e_tiny_hf_gemma4.npz, made by
+    tests/golden/make_hf_fixture.py from Hugging Face's Gemma4ForCausalLM on the same seeded weights: logits
+    at all 40 prompt positions and the 12 greedy tokens that follow."""
+    from util import build_pair
+    gold = np.load(os.path.join(GOLDEN, "e_tiny_hf_gemma4.npz"))
+    cfg = syn.e_tiny_cfg()
+    _, oracle = build_pair(cfg, "f32", kv_bf16=False, norm_jitter=0.1, want_gpu=False)
+    cache = oracle.new_cache(64)
+    worst = 0.0
+    for i, t in enumerate(gold["prompt"]):
+        lg = cache.decode_logits(int(t))
+        worst = max(worst, float(np.abs(lg - gold["logits"][i]).max()))
+    assert worst <= 2e-4, worst
+    toks = []
+    for _ in range(12):
+        toks.append(int(np.argmax(lg)))
+        lg = cache.decode_logits(toks[-1])
+    assert toks == gold["tokens"].tolist()
+
+
+def test_shared_layer_without_source_is_rejected():
+    cfg = syn._cfg(64, 32, 2, 2, 1, 64, 64, 8, ["sliding_attention", "full_attention"])
+    cfg["num_kv_shared_layers"] = 1          # the only full_attention layer is shared: no earlier source
+    with pytest.raises(ValueError):
+        orc.OracleModel(cfg, orc.F32)

@@ -37,3 +37,33 @@ def build_pair(cfg, dtype, kv_bf16, seed=0, norm_jitter=0.0, want_gpu=True, want
 def margin(logits):
     top = np.sort(logits)[-2:]
     return float(top[1] - top[0])
+
+
+def layerwise_compare(gpu, oracle, cfg, prompts, kv_dtype, page_tokens, logits_every=1):
+    """Layer-wise teacher forcing over a batch of ragged prompts: one oracle per sequence runs freely, the CUDA path
+    gets the oracle's input of every layer injected (oxg4_decode_trace). Returns (worst layer-output difference,
+    worst logits difference, largest hidden magnitude, cache table)."""
+    L, H = cfg["num_hidden_layers"], cfg["hidden_size"]
+    batch = len(prompts)
+    lens = [len(p) for p in prompts]
+    table = gpu.new_cache_table([n + 2 for n in lens], batch=batch, page_tokens=page_tokens, kv_dtype=kv_dtype)
+    caches = [oracle.new_cache(n + 2) for n in lens]
+    worst_h = worst_logit = scale = 0.0
+    for t in range(max(lens)):
+        toks = np.full(batch, pkg.INACTIVE, dtype=np.uint32)
+        inject = np.zeros((L, batch, H), dtype=np.float32)
+        refs = {}
+        for b in range(batch):
+            if t >= lens[b]:
+                continue
+            toks[b] = prompts[b][t]
+            tr_o, lg_o = caches[b].decode_trace(int(prompts[b][t]), want_logits=(t % logits_every == 0 or t >= lens[b] - 2))
+            inject[:, b] = tr_o[:L]
+            refs[b] = (tr_o, lg_o)
+        tr_g, lg_g = gpu.decode_trace(toks, table, inject=inject)
+        for b, (tr_o, lg_o) in refs.items():
+            worst_h = max(worst_h, float(np.abs(tr_g[:, b] - tr_o).max()))
+            scale = max(scale, float(np.abs(tr_o).max()))
+            if lg_o is not None:
+                worst_logit = max(worst_logit, float(np.abs(lg_g[b] - lg_o).max()))
+    return worst_h, worst_logit, scale, table
