@@ -365,8 +365,9 @@ inline size_t attn_mma_smem_bytes() {
 // meets the unit's.
 template <int D, int G>
 __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnMmaArgs a) {
+    constexpr int CH = 64;                                     // partials handled per round
     __shared__ int pre[kAmMaxGroups + 1];
-    __shared__ float s_scale[kAmRows][64], s_L[kAmRows], s_M[kAmRows];
+    __shared__ float s_m[kAmRows][CH], s_e[kAmRows][CH], s_l[kAmRows][CH], s_L[kAmRows], s_M[kAmRows];
     pdl_wait();
     pdl_launch();
     am_prefix(a, pre);
@@ -380,13 +381,48 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnMmaArgs a) {
     const int tid = threadIdx.x;
     const float* base = a.part + (size_t)(u + w0) * a.part_rows * (D + 2);
     const size_t slot = (size_t)a.part_rows * (D + 2);
-    // running maximum and denominator of every row over the partials (in warp order)
+    const int np = w1 - w0 + 1;
+    if (np <= CH) {
+        // the usual case: every (m, l) pair in one round of loads, scale factors from shared memory, one round of
+        // loads for the weighted sums, normalised and written once
+        for (int i = tid; i < nrows * np; i += blockDim.x) {
+            const int r = i / np, w = i % np;
+            const float* p = base + (size_t)w * slot + (size_t)r * (D + 2);
+            s_m[r][w] = p[D];
+            s_l[r][w] = p[D + 1];
+        }
+        __syncthreads();
+        if (tid < nrows) {
+            float M = -INFINITY;
+            for (int w = 0; w < np; ++w) M = fmaxf(M, s_m[tid][w]);
+            float L = 0.0f;
+            for (int w = 0; w < np; ++w) {
+                const float e = (s_m[tid][w] == -INFINITY) ? 0.0f : expf(s_m[tid][w] - M);
+                s_e[tid][w] = e;
+                L += e * s_l[tid][w];
+            }
+            s_L[tid] = L;
+        }
+        __syncthreads();
+        for (int idx = tid; idx < nrows * D; idx += blockDim.x) {
+            const int r = idx / D, d = idx % D;
+            float acc = 0.0f;
+            for (int w = 0; w < np; ++w) acc += s_e[r][w] * base[(size_t)w * slot + (size_t)r * (D + 2) + d];
+            const size_t oi = (size_t)(row0 + r / G) * a.Nq * D + (size_t)(kvh * G + r % G) * D + d;
+            const float ov = acc / s_L[r];
+            a.out[oi] = ov;
+            if (a.out_bf16) a.out_bf16[oi] = (uint16_t)f32_to_bf16_bits(ov);
+        }
+        return;
+    }
+    // many partials (one long sequence spread over most of the grid): running maximum and denominator first,
+    // then the weighted sums CH partials at a time through the output buffer
     if (tid < nrows) {
         float M = -INFINITY;
-        for (int w = w0; w <= w1; ++w) M = fmaxf(M, base[(size_t)(w - w0) * slot + (size_t)tid * (D + 2) + D]);
+        for (int w = 0; w < np; ++w) M = fmaxf(M, base[(size_t)w * slot + (size_t)tid * (D + 2) + D]);
         float L = 0.0f;
-        for (int w = w0; w <= w1; ++w) {
-            const float* p = base + (size_t)(w - w0) * slot + (size_t)tid * (D + 2);
+        for (int w = 0; w < np; ++w) {
+            const float* p = base + (size_t)w * slot + (size_t)tid * (D + 2);
             const float e = (p[D] == -INFINITY) ? 0.0f : expf(p[D] - M);
             L += e * p[D + 1];
         }
@@ -394,21 +430,21 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnMmaArgs a) {
         s_L[tid] = L;
     }
     __syncthreads();
-    for (int c0 = w0; c0 <= w1; c0 += 64) {                    // scale factors, 64 partials at a time
-        const int nc = min(64, w1 - c0 + 1);
+    for (int c0 = 0; c0 < np; c0 += CH) {
+        const int nc = min(CH, np - c0);
         __syncthreads();
         for (int i = tid; i < nrows * nc; i += blockDim.x) {
             const int r = i / nc, w = c0 + i % nc;
-            const float mw = base[(size_t)(w - w0) * slot + (size_t)r * (D + 2) + D];
-            s_scale[r][i % nc] = (mw == -INFINITY) ? 0.0f : expf(mw - s_M[r]);
+            const float mw = base[(size_t)w * slot + (size_t)r * (D + 2) + D];
+            s_e[r][i % nc] = (mw == -INFINITY) ? 0.0f : expf(mw - s_M[r]);
         }
         __syncthreads();
         for (int idx = tid; idx < nrows * D; idx += blockDim.x) {
             const int r = idx / D, d = idx % D;
             float acc = 0.0f;
-            for (int w = 0; w < nc; ++w) acc += s_scale[r][w] * base[(size_t)(c0 + w - w0) * slot + (size_t)r * (D + 2) + d];
+            for (int w = 0; w < nc; ++w) acc += s_e[r][w] * base[(size_t)(c0 + w) * slot + (size_t)r * (D + 2) + d];
             const size_t oi = (size_t)(row0 + r / G) * a.Nq * D + (size_t)(kvh * G + r % G) * D + d;
-            if (c0 == w0) a.out[oi] = acc; else a.out[oi] += acc;
+            if (c0 == 0) a.out[oi] = acc; else a.out[oi] += acc;
         }
     }
     __syncthreads();
