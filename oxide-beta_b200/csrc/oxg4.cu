@@ -902,7 +902,7 @@ static int32_t cache_build(oxg4_cache* c) {
     // models with per-layer embeddings run through the small-batch kernels only (the extra projections per layer
     // are tiny and have no tcgen05 variant)
     c->tc_ok = m->es == 2 && m->P == 0 && getenv("OXG4_DISABLE_TCGEN05") == nullptr;
-    c->use_tc = c->tc_ok && B >= 8 && B <= 64;
+    c->use_tc = c->tc_ok && B >= 8 && B <= kPrefillRows;       // up to 256 sequences: row blocks of 128 / 256 (UMMA N)
     c->ls_qkv.assign(L, 1);
     c->ls_o.assign(L, 1);
     c->lps_qkv.assign(L, 1);
@@ -922,7 +922,7 @@ static int32_t cache_build(oxg4_cache* c) {
         const int sms = m->num_sms;
         auto tiles = [](int n) { return (n + kTcTileM - 1) / kTcTileM; };
         auto kbs = [](int k) { return (k + kTcTileK - 1) / kTcTileK; };
-        const int Bd = std::min(B, 64);
+        const int Bd = std::min(B, kPrefillRows);
         size_t qkv_part_n = 1, o_part_n = 1;
         auto rows_splits = [&](int sd, int sp) { return (size_t)std::max(sd * B, sp * kPrefillRows); };
         for (int l = 0; l < L; ++l) {
@@ -947,7 +947,7 @@ static int32_t cache_build(oxg4_cache* c) {
         TRY(dalloc(c, &c->o_part, o_part_n));
         TRY(dalloc(c, &c->gu_part, rows_splits(c->s_gu, c->ps_gu) * 2 * m->I));
         TRY(dalloc(c, &c->down_part, rows_splits(c->s_down, c->ps_down) * H));
-        if (m->tp > 1 && c->use_tc) {
+        if (m->tp > 1 && c->use_tc && B <= 64) {
             const size_t bytes = sizeof(float) * 2 * (size_t)m->tp * B * H + sizeof(unsigned int) * 2 * kMaxTp;
             CK(cudaMalloc(&c->px_block, bytes));          // own allocation: its IPC handle is exported
             CK(cudaMemset(c->px_block, 0, bytes));

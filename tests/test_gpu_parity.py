@@ -336,7 +336,7 @@ def test_layerwise_trace_without_injection_matches_oracle_f32():
 
 # ---- tensor-core projection kernel: 2..16 rows per pass, several passes --------------------------------------------
 
-@pytest.mark.parametrize("batch", [8, 16, 21])
+@pytest.mark.parametrize("batch", [8, 16, 21, 80, 130])
 def test_large_batches_tensor_core_path(batch):
     cfg = small_cfg(hidden=256, layers=2, heads=4, kv_heads=2, head_dim=64, inter=520, vocab=1000, window=10,
                     layer_types=["sliding_attention", "full_attention"])
