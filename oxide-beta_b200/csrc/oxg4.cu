@@ -2234,7 +2234,9 @@ extern "C" int32_t oxg4_decode_trace(oxg4_model* m, oxg4_cache* c, const uint32_
     CK(cudaMalloc(&d_trace, sizeof(float) * per * (L + 1)));
     if (inject) {
         if (cudaMalloc(&d_inject, sizeof(float) * per * L) != cudaSuccess) { cudaFree(d_trace); return fail(OXG4_OOM, "out of device memory"); }
-        cudaMemcpy(d_inject, inject, sizeof(float) * per * L, cudaMemcpyHostToDevice);
+        // ordered on the model's stream: a blocking copy from pageable memory may return before its DMA has
+        // landed, and the model's non-blocking stream does not wait for the default stream
+        cudaMemcpyAsync(d_inject, inject, sizeof(float) * per * L, cudaMemcpyHostToDevice, m->stream);
     }
     int32_t s = stage_inputs(c, tokens, 0, 0);
     TraceCtx tr{d_inject, d_trace};
@@ -2403,7 +2405,8 @@ extern "C" int32_t oxg4_prefill(oxg4_model* m, oxg4_cache* c, const uint32_t* to
     }
     // device step state: every sequence continues at position lens[b]
     std::vector<int32_t> np(lens, lens + B);
-    CK(cudaMemcpy(c->pos, np.data(), sizeof(int32_t) * B, cudaMemcpyHostToDevice));
+    CK(cudaMemcpyAsync(c->pos, np.data(), sizeof(int32_t) * B, cudaMemcpyHostToDevice, m->stream));
+    CK(cudaStreamSynchronize(m->stream));      // np leaves scope; later steps read c->pos in stream order
     for (int i = 0; i < B; ++i) c->pos_host[i] = lens[i];
     if (last_logits) {
         Launcher ln{m};
