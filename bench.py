@@ -150,7 +150,7 @@ def cpu_oracle_run(cfg, weights_iter, prompt, steps, warmup):
 
 
 def run_workload(pkg, dist, rank, local_rank, world, name, tp, prompt_len, steps, warmup, layers=None, vocab=None,
-                 keep_host=False, e2e=True, sampler=None):
+                 keep_host=False, e2e=True, sampler=None, cache_fill="prefill"):
     """Loads workload `name` (tensor-parallel over `tp` ranks, or one replica per rank), ingests the
     prompts, then times `steps` decode steps after `warmup`. Returns the measurements of this rank
     (times already reduced to the maximum over ranks)."""
@@ -193,11 +193,16 @@ def run_workload(pkg, dist, rank, local_rank, world, name, tp, prompt_len, steps
         dist.all_gather_object(handles, table.tp_export())
         table.tp_connect(handles)
         tp_exchange = "peer-memory"
-    prompts = [syn.prompt_ids(cfg["vocab_size"], n, seed=1 + b) for b, n in enumerate(lens)]
     t_pre = time.perf_counter()
-    logits = state.prefill_prompt(np.concatenate(prompts), table, lens=lens)
+    if cache_fill == "synthetic":
+        # the K/V pools receive a pseudo-random pattern instead of the prompts' K/V: same bytes per step, no prefill
+        table.fill_synthetic(lens)
+        first = (np.arange(B, dtype=np.uint32) * 7919 + 11) % cfg["vocab_size"]
+    else:
+        prompts = [syn.prompt_ids(cfg["vocab_size"], n, seed=1 + b) for b, n in enumerate(lens)]
+        logits = state.prefill_prompt(np.concatenate(prompts), table, lens=lens)
+        first = np.atleast_2d(logits).argmax(-1).astype(np.uint32)
     prefill_s = time.perf_counter() - t_pre
-    first = np.atleast_2d(logits).argmax(-1).astype(np.uint32)
 
     # device-resident loop: warm-up, then the timed K steps bracketed by barrier + synchronize
     ids, _ = state.decode_greedy(first, table, warmup)
@@ -269,6 +274,9 @@ def main():
     ap.add_argument("--no-tp-record", action="store_true",
                     help="skip the tensor-parallel ~12B measurement that accompanies the default workload")
     ap.add_argument("--tp-prompt", type=int, default=TP_RECORD_PROMPT, help="prompt length of the tensor-parallel record")
+    ap.add_argument("--cache-fill", default="prefill", choices=["prefill", "synthetic"],
+                    help="synthetic: K/V pools filled with a pseudo-random pattern at the prompt lengths instead of "
+                         "ingesting the prompts (decode timing at long contexts without the prefill time)")
     ap.add_argument("--layers", type=int, default=None, help="profiling aid: keep only the first LAYERS layers")
     ap.add_argument("--vocab", type=int, default=None, help="profiling aid: shrink the vocabulary")
     args = ap.parse_args()
@@ -325,7 +333,8 @@ def main():
     tp = world if (world > 1 and args.workload in ("c4", "c5")) else 1
     keep_host = (rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload in ("c1", "c2", "c3"))
     r = run_workload(pkg, dist, rank, local_rank, world, args.workload, tp, args.prompt, args.steps, warmup,
-                     args.layers, args.vocab, keep_host=keep_host, sampler=ClockSampler(local_rank))
+                     args.layers, args.vocab, keep_host=keep_host, sampler=ClockSampler(local_rank),
+                     cache_fill=args.cache_fill)
     clocks = r["clocks"]
     cfg, B, lens, ms_step = r["cfg"], r["B"], r["lens"], r["ms_step"]
     replicas = world // tp
@@ -373,7 +382,11 @@ def main():
         "config": {"workload": args.workload + (f" (reduced: layers={args.layers} vocab={args.vocab})"
                                                  if (args.layers or args.vocab) else ""),
                    "batch": B, "prompt": lens[0] if len(set(lens)) == 1 else "ragged",
-                   "context_at_timing": r["contexts"][0], "kv_dtype": "bf16", "page_tokens": 256,
+                   "context_at_timing": r["contexts"][0] if len(set(lens)) == 1 else
+                   {"min": min(r["contexts"]), "mean": round(sum(r["contexts"]) / B), "max": max(r["contexts"])},
+                   "cache_fill": ("prompts ingested by the chunked prefill" if args.cache_fill == "prefill" else
+                                  "synthetic: K/V pools filled with a pseudo-random pattern at the prompt lengths, no prefill"),
+                   "kv_dtype": "bf16", "page_tokens": 256,
                    "parallelism": "single GPU" if world == 1 else (f"tp{tp} (sums after O and down: {r['tp_exchange']})"
                                                                    if tp > 1 else f"{world} independent replicas"),
                    "l2": "per-step inputs (weights + KV) exceed the 126 MB L2; no flush",

@@ -237,6 +237,12 @@ int32_t oxg4_profile_count(const oxg4_model* model, const char* kind);
 int32_t oxg4_debug_wait_timeout(oxg4_model* model, oxg4_cache* cache, int32_t kind, uint32_t spin_limit);
 void oxg4_debug_fail_alloc_after(int32_t n);
 
+/* Measurement aid (no counterpart in the reference): marks lens[b] positions of every sequence of an EMPTY cache
+ * table as cached and fills the K/V pools with a fixed pseudo-random pattern, so that decode steps at a long
+ * context can be timed without ingesting the prompts first. The pool contents are not the K/V of any prompt:
+ * only timing, never parity, may be taken from a table filled this way. */
+int32_t oxg4_debug_fill_cache(oxg4_model* model, oxg4_cache* cache, const int32_t* lens);
+
 /* Top-k selection that allocates nothing (no counterpart in the reference). It is meant for callers
  * that are not allowed to allocate device memory at the moment they need a top-k: code running
  * between cudaStreamBeginCapture and cudaStreamEndCapture on a stream, where cudaMalloc is illegal;

@@ -329,6 +329,28 @@ __global__ void wait_probe_kernel(int kind, unsigned int limit, const unsigned i
     }
 }
 
+// Measurement aid: fills a K/V pool with a fixed pseudo-random pattern (values in [-1, 1)), 16 bytes per thread and
+// pass, so that decode steps at a long context can be timed without ingesting the prompts first.
+template <typename KT>
+__global__ void pool_fill_kernel(uint4* __restrict__ pool, size_t n16, uint32_t salt) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x) {
+        uint32_t h = (uint32_t)i * 2654435761u ^ (uint32_t)(i >> 32) ^ salt;
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            h ^= h >> 15; h *= 0x2c1b3c6du; h ^= h >> 12; h *= 0x297a2d39u; h ^= h >> 15;
+            if (sizeof(KT) == 2) {
+                const float a = (float)(int)(h & 0xffu) * (1.0f / 128.0f) - 1.0f;
+                const float b = (float)(int)((h >> 8) & 0xffu) * (1.0f / 128.0f) - 1.0f;
+                w[j] = (uint32_t)f32_to_bf16_bits(a) | ((uint32_t)f32_to_bf16_bits(b) << 16);
+            } else {
+                w[j] = __float_as_uint((float)(int)(h & 0xffffu) * (1.0f / 32768.0f) - 1.0f);
+            }
+        }
+        pool[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
 // x[b, i] = bf16(gelu_tanh(sum_s gu[s, b, i]) * sum_s gu[s, b, I + i]); grid (ceil(I / 256), B)
 __global__ void __launch_bounds__(kRowsThreads)
 geglu_rows_kernel(int B, int I, const float* gu, int splits, uint16_t* x) {

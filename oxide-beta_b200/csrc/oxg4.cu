@@ -666,6 +666,7 @@ struct oxg4_cache {
     int physical_caches = 0;
     bool attn_cluster = true;     // merge split-KV partials through a thread-block cluster's shared memory
     std::vector<void*> kpool, vpool;          // per layer
+    std::vector<size_t> pool_bytes;           // per layer, 0 for a KV-shared layer
     int64_t kv_bytes = 0;
     int32_t *pt_full = nullptr, *pt_slide = nullptr, *cap_full = nullptr, *cap_slide = nullptr;
     uint32_t* tokens = nullptr;
@@ -793,6 +794,7 @@ static int32_t cache_build(oxg4_cache* c) {
     c->mma_attn = c->kv_dtype == OXG4_BF16 && PT % kAmTile == 0 && getenv("OXG4_DISABLE_MMA_ATTN") == nullptr;
     c->kpool.assign(L, nullptr);
     c->vpool.assign(L, nullptr);
+    c->pool_bytes.assign(L, 0);
     c->kmap.resize(L);
     c->vmap.resize(L);
     c->attn_splits.assign(L, 1);
@@ -815,6 +817,7 @@ static int32_t cache_build(oxg4_cache* c) {
             TRY(dalloc(c, &v, bytes));
             c->kpool[l] = k;
             c->vpool[l] = v;
+            c->pool_bytes[l] = bytes;
             c->kv_bytes += 2 * (int64_t)bytes;
             ++c->physical_caches;
             if (c->mma_attn) {
@@ -2579,6 +2582,36 @@ extern "C" int32_t oxg4_generate(oxg4_model* m, const uint32_t* prompt, int64_t 
 
 // Failure-path probe: runs a bounded device-side wait that nothing will ever satisfy, with a polling budget
 // of `spin_limit`, then reports through the same status word and check as every step does.
+// Measurement aid (no counterpart in the reference): an empty cache table is marked as holding lens[b] positions of
+// every sequence and its K/V pools are filled with a fixed pseudo-random pattern, so that decode steps at a long
+// context can be timed without ingesting the prompts. The contents are not the K/V of any prompt.
+extern "C" int32_t oxg4_debug_fill_cache(oxg4_model* m, oxg4_cache* c, const int32_t* lens) {
+    if (!m || !c || !lens || c->m != m) return fail(OXG4_INVALID_ARGUMENT, "null or mismatched handle");
+    for (int b = 0; b < c->B; ++b) {
+        if (c->pos_host[b] != 0) return fail(OXG4_INVALID_ARGUMENT, "synthetic fill requires an empty cache table");
+        if (lens[b] <= 0 || lens[b] > c->max_seq[b]) return fail(OXG4_INVALID_SHAPE, "length does not fit the cache table");
+    }
+    TRY(bind_device(m));
+    const int L = m->cfg.num_hidden_layers;
+    for (int l = 0; l < L; ++l) {
+        const size_t n16 = c->pool_bytes[l] / 16;
+        if (n16 == 0) continue;
+        const int grid = (int)std::min<size_t>((n16 + 255) / 256, (size_t)m->num_sms * 16);
+        if (c->kv_dtype == OXG4_BF16) {
+            pool_fill_kernel<uint16_t><<<grid, 256, 0, m->stream>>>((uint4*)c->kpool[l], n16, 2u * l + 1u);
+            pool_fill_kernel<uint16_t><<<grid, 256, 0, m->stream>>>((uint4*)c->vpool[l], n16, 2u * l + 2u);
+        } else {
+            pool_fill_kernel<float><<<grid, 256, 0, m->stream>>>((uint4*)c->kpool[l], n16, 2u * l + 1u);
+            pool_fill_kernel<float><<<grid, 256, 0, m->stream>>>((uint4*)c->vpool[l], n16, 2u * l + 2u);
+        }
+    }
+    CK(cudaGetLastError());
+    CK(cudaMemcpyAsync(c->pos, lens, sizeof(int32_t) * c->B, cudaMemcpyHostToDevice, m->stream));
+    CK(cudaStreamSynchronize(m->stream));
+    for (int b = 0; b < c->B; ++b) c->pos_host[b] = lens[b];
+    return OXG4_OK;
+}
+
 extern "C" int32_t oxg4_debug_wait_timeout(oxg4_model* m, oxg4_cache* c, int32_t kind, uint32_t spin_limit) {
     if (!m || !c || c->m != m) return fail(OXG4_INVALID_ARGUMENT, "null or mismatched handle");
     if (kind != 1 && kind != 2) return fail(OXG4_INVALID_ARGUMENT, "kind must be 1 (mbarrier) or 2 (peer flag)");

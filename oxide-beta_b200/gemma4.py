@@ -198,6 +198,12 @@ class Gemma4CudaCacheTable:
     def reset(self):
         N.check(N.lib().oxg4_cache_reset(self._h))
 
+    def fill_synthetic(self, lens: Sequence[int]):
+        """Measurement aid: marks lens[b] positions per sequence as cached and fills the K/V pools with a fixed
+        pseudo-random pattern (timing only; the contents are not the K/V of any prompt)."""
+        a = np.ascontiguousarray(lens, dtype=np.int32)
+        N.check(N.lib().oxg4_debug_fill_cache(self._state._h, self._h, a.ctypes.data_as(C.POINTER(C.c_int32))))
+
     def tp_export(self) -> bytes:
         """64-byte CUDA IPC handle of this table's tensor-parallel exchange block."""
         buf = C.create_string_buffer(64)

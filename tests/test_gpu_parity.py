@@ -475,6 +475,29 @@ def test_bounded_wait_runs_out_and_reports_timeout(c1, kind):
     assert N.lib().oxg4_debug_wait_timeout(gpu._h, table._h, 3, 2000) == 2      # INVALID_ARGUMENT
 
 
+def test_synthetic_cache_fill_sets_positions_and_decodes(c1):
+    """The measurement aid behind `bench.py --cache-fill synthetic`: positions advance to the given lengths, the
+    pools hold finite values (decode steps return finite logits, twice the same on two tables), and a table
+    that already holds tokens is refused."""
+    cfg, gpu, oracle = c1
+    outs = []
+    for kv in (pkg.F32, pkg.BF16):
+        for _ in range(2):
+            table = gpu.new_cache_table([40, 24], batch=2, kv_dtype=kv)
+            table.fill_synthetic([33, 7])
+            assert [table.position(0), table.position(1)] == [33, 7]
+            logits = gpu.decode_token(np.array([3, 9], dtype=np.uint32), table)
+            assert np.isfinite(logits).all()
+            assert [table.position(0), table.position(1)] == [34, 8]
+            outs.append(logits)
+        assert np.array_equal(outs[-1], outs[-2])
+    with pytest.raises(pkg.Oxg4Error, match="empty cache table"):
+        table.fill_synthetic([1, 1])
+    fresh = gpu.new_cache_table([8, 8], batch=2, kv_dtype=pkg.F32)
+    with pytest.raises(pkg.Oxg4Error, match="does not fit"):
+        fresh.fill_synthetic([9, 1])
+
+
 def test_cache_create_out_of_memory_leaks_nothing(c1):
     """An allocation that fails in the middle of oxg4_cache_create (injected on the host): OXG4_OOM comes
     back, no handle is produced and the driver's free-memory figure returns to what it was."""
