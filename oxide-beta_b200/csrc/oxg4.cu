@@ -752,19 +752,6 @@ constexpr int kPrefillRows = 256;             // most prompt tokens one pass ove
 
 static int32_t tc_gemm_setup();
 static int32_t attn_mma_setup();
-// Shared-memory carve-out (percent of the SM's L1 + shared memory array) asked for with EVERY launch of a step.
-// Consecutive kernels of a step need anything between a few and 223 KiB of shared memory; left to itself the
-// driver picks the smallest configuration that fits each kernel, and an SM can only be reconfigured once it is
-// idle, which delays the first CTAs of the next kernel by microseconds and keeps it from becoming co-resident
-// with the tail of its predecessor. One configuration for the whole step avoids both; none of the kernels
-// depends on L1 capacity (weights and K/V are streamed past L1).
-static int smem_carveout() {
-    static const int v = [] {
-        const char* e = getenv("OXG4_SMEM_CARVEOUT");
-        return e ? atoi(e) : 100;
-    }();
-    return v;
-}
 static int tc_pick_splits(int tiles, int kblocks, int grid, int B, int n_total, int K, double max_extra = 0.3);
 static int32_t encode_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 
@@ -1188,20 +1175,11 @@ static int32_t tc_gemm_launch(const void* w_dev, const void* w1_dev, const void*
     cfg.gridDim = dim3(std::min(units, num_sms));
     cfg.blockDim = dim3(kTcThreads);
     cfg.stream = st;
-    cudaLaunchAttribute attr[2];
-    int na = 0;
-    if (pdl) {
-        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[na].val.programmaticStreamSerializationAllowed = 1;
-        ++na;
-    }
-    if (smem_carveout() >= 0) {
-        attr[na].id = cudaLaunchAttributePreferredSharedMemoryCarveout;
-        attr[na].val.sharedMemCarveout = (unsigned)smem_carveout();
-        ++na;
-    }
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = na;
+    cfg.numAttrs = pdl ? 1 : 0;
     cudaError_t e;
     if (bn == 16) {
         cfg.dynamicSmemBytes = tc_gemm_smem_bytes<16>();
@@ -1259,13 +1237,8 @@ struct Launcher {
         cfg.blockDim = block;
         cfg.dynamicSmemBytes = smem;
         cfg.stream = m->stream;
-        cudaLaunchAttribute attr[3];
+        cudaLaunchAttribute attr[2];
         int na = 0;
-        if (smem_carveout() >= 0) {
-            attr[na].id = cudaLaunchAttributePreferredSharedMemoryCarveout;
-            attr[na].val.sharedMemCarveout = (unsigned)smem_carveout();
-            ++na;
-        }
         if (coop) {
             attr[na].id = cudaLaunchAttributeCooperative;
             attr[na].val.cooperative = 1;
