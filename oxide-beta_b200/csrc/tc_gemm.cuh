@@ -108,10 +108,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     constexpr uint32_t A_BYTES = kTcTileM * kTcTileK * 2;     // 16 KiB
     constexpr uint32_t B_BYTES = BN * kTcTileK * 2;
     constexpr uint32_t STAGE = A_BYTES + ((B_BYTES + 1023) / 1024) * 1024;
-    constexpr uint32_t TM_COLS = BN < 32 ? 32 : BN;           // TMEM allocation: power of two >= 32
+    constexpr uint32_t ACC_COLS = BN < 32 ? 32 : BN;          // TMEM columns of one accumulator tile
+    constexpr uint32_t TM_COLS = 2 * ACC_COLS;                // two accumulators (64..512 columns, a power of two): the
+                                                              // MMAs of a unit run while the epilogue drains the previous one
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
-    __shared__ __align__(8) uint64_t full[kTcStages], empty[kTcStages], acc_full, acc_empty;
+    __shared__ __align__(8) uint64_t full[kTcStages], empty[kTcStages], acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_base;
     __shared__ volatile int failed;
 
@@ -122,11 +124,18 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // unit u -> row block u % TB, split (u / TB) % S, tile index (over both matrices) u / (TB * S)
     auto kb_begin = [&](int u) { return ((u / a.TB) % a.S) * a.kb_per_split; };
     auto kb_end = [&](int u) { return min(kblocks_all, ((u / a.TB) % a.S + 1) * a.kb_per_split); };
+    // The j-th k-block a CTA takes from a unit. Every CTA starts its walk at a different k-block: CTAs that run
+    // in step would otherwise ask L2 for the same activation tile at the same moment (measured: 11 of 66 us of
+    // the ~12B gate/up launch). The order of the f32 sums inside a unit therefore depends on the CTA (it is
+    // fixed for a given launch geometry).
+    auto kb_at = [&](int u, int j) {
+        const int k0 = kb_begin(u), nk = kb_end(u) - k0;
+        return k0 + (j + (int)blockIdx.x) % nk;
+    };
 
     if (tid == 0) {
         for (int s = 0; s < kTcStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        mbar_init(&acc_full, 1);
-        mbar_init(&acc_empty, 128);
+        for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 128); }
         failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -146,11 +155,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // programmatic: this CTA may be resident while the preceding kernel still runs) and only the
         // activation tiles of those stages wait for it.
         int t = blockIdx.x;
-        int kb = t < n_tiles ? kb_begin(t) : 0;
+        int j = 0;                                   // position in unit t's (rotated) walk over its k-blocks
         auto advance = [&]() {
-            if (++kb >= kb_end(t)) {
+            if (++j >= kb_end(t) - kb_begin(t)) {
                 t += gridDim.x;
-                if (t < n_tiles) kb = kb_begin(t);
+                j = 0;
             }
         };
         auto load_w = [&](int tt, int kk, int s) {
@@ -166,6 +175,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         int n_pre = 0;
         while (n_pre < kTcStages && t < n_tiles) {
             mbar_expect_tx(&full[n_pre], A_BYTES + B_BYTES);
+            const int kb = kb_at(t, j);
             load_w(t, kb, n_pre);
             pre_t[n_pre] = t;
             pre_kb[n_pre] = kb;
@@ -180,6 +190,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const uint32_t ph = (it / kTcStages) & 1;
             if (!mbar_wait(&empty[s], ph ^ 1)) { failed = 1; atomicExch(a.err, 1); break; }
             mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+            const int kb = kb_at(t, j);
             load_w(t, kb, s);
             load_x(t, kb, s);
             advance();
@@ -193,10 +204,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const uint32_t idesc = umma_idesc_bf16(kTcTileM, BN);
         uint32_t it = 0, tile_i = 0;
         for (int t = blockIdx.x; t < n_tiles && !failed; t += gridDim.x, ++tile_i) {
-            if (tile_i > 0 && !mbar_wait(&acc_empty, (tile_i - 1) & 1)) { failed = 1; atomicExch(a.err, 2); break; }
+            // accumulator tile_i % 2; its previous user (unit tile_i - 2) must have been drained by the epilogue
+            const uint32_t ab = tile_i & 1, use = tile_i >> 1;
+            if (use > 0 && !mbar_wait(&acc_empty[ab], (use - 1) & 1)) { failed = 1; atomicExch(a.err, 2); break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int kb0 = kb_begin(t);
-            for (int kb = kb0; kb < kb_end(t); ++kb, ++it) {
+            const uint32_t acc = tmem + ab * ACC_COLS;
+            const int nk = kb_end(t) - kb_begin(t);
+            for (int j = 0; j < nk; ++j, ++it) {
                 const int s = it % kTcStages;
                 const uint32_t ph = (it / kTcStages) & 1;
                 if (!mbar_wait(&full[s], ph)) { failed = 1; atomicExch(a.err, 3); break; }
@@ -205,19 +219,19 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const uint64_t da = umma_smem_desc(sa), db = umma_smem_desc(sa + A_BYTES);
 #pragma unroll
                 for (int k = 0; k < kTcTileK / 16; ++k) {
-                    const uint32_t accumulate = (kb > kb0 || k > 0) ? 1u : 0u;
+                    const uint32_t accumulate = (j > 0 || k > 0) ? 1u : 0u;
                     // advance 16 BF16 = 32 bytes inside the swizzle atom: +2 in units of 16 bytes
                     asm volatile(
                         "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
                         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                        ::"r"(tmem), "l"(da + (uint64_t)(2 * k)), "l"(db + (uint64_t)(2 * k)), "r"(idesc), "r"(accumulate)
+                        ::"r"(acc), "l"(da + (uint64_t)(2 * k)), "l"(db + (uint64_t)(2 * k)), "r"(idesc), "r"(accumulate)
                         : "memory");
                 }
                 // the stage may be refilled once these MMAs have read it
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&empty[s])) : "memory");
             }
             if (failed) break;
-            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&acc_full)) : "memory");
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&acc_full[ab])) : "memory");
         }
     }
     __syncwarp();
@@ -227,7 +241,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int quad = warp & 3;
         uint32_t tile_i = 0;
         for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++tile_i) {
-            if (!mbar_wait(&acc_full, tile_i & 1)) { if (lane == 0) atomicExch(a.err, 4); break; }
+            const uint32_t ab = tile_i & 1, use = tile_i >> 1;
+            if (!mbar_wait(&acc_full[ab], use & 1)) { if (lane == 0) atomicExch(a.err, 4); break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int tg = t / (a.S * a.TB), sp = (t / a.TB) % a.S, b0 = (t % a.TB) * BN;
             const bool second = tg >= tiles_per_mat;
@@ -236,7 +251,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 uint32_t v[16];
-                const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0;
+                const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + ab * ACC_COLS + (uint32_t)c0;
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
                     : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
@@ -250,7 +265,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty)) : "memory");
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[ab])) : "memory");
         }
     }
 
