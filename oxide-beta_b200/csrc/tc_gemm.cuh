@@ -124,15 +124,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // unit u -> row block u % TB, split (u / TB) % S, tile index (over both matrices) u / (TB * S)
     auto kb_begin = [&](int u) { return ((u / a.TB) % a.S) * a.kb_per_split; };
     auto kb_end = [&](int u) { return min(kblocks_all, ((u / a.TB) % a.S + 1) * a.kb_per_split); };
-    // The j-th k-block a CTA takes from a unit. Every CTA starts its walk at a different k-block: CTAs that run
-    // in step would otherwise ask L2 for the same activation tile at the same moment (measured: 11 of 66 us of
-    // the ~12B gate/up launch). The order of the f32 sums inside a unit therefore depends on the CTA (it is
-    // fixed for a given launch geometry).
-    auto kb_at = [&](int u, int j) {
-        const int k0 = kb_begin(u), nk = kb_end(u) - k0;
-        return k0 + (j + (int)blockIdx.x) % nk;
-    };
-
     if (tid == 0) {
         for (int s = 0; s < kTcStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 128); }
@@ -154,45 +145,56 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // kernel writes, so the first ring of them is requested BEFORE the dependency wait (the launch is
         // programmatic: this CTA may be resident while the preceding kernel still runs) and only the
         // activation tiles of those stages wait for it.
+        // Everything that is constant over a unit (and needs an integer division) is computed once per unit: this
+        // thread has to request a 16 KiB tile every ~350 ns for the CTA to get its share of the HBM bandwidth.
+        // Every CTA starts its walk over a unit's k-blocks at a different block (jr), so that CTAs running in
+        // step do not all ask L2 for the same activation tile at the same moment; the order of the f32 sums
+        // inside a unit therefore depends on the CTA (fixed for a given launch geometry).
         int t = blockIdx.x;
-        int j = 0;                                   // position in unit t's (rotated) walk over its k-blocks
+        int k0 = 0, nk = 1, jr = 0, left = 0, trow = 0, xrow = 0;
+        const CUtensorMap* wmap = &map_w;
+        auto enter_unit = [&]() {
+            const int sp = (t / a.TB) % a.S;
+            k0 = sp * a.kb_per_split;
+            nk = min(kblocks_all, k0 + a.kb_per_split) - k0;
+            jr = (int)blockIdx.x % nk;
+            left = nk;
+            const int tg = t / (a.S * a.TB);
+            const bool second = tg >= tiles_per_mat;
+            wmap = second ? &map_w1 : &map_w;
+            trow = (second ? tg - tiles_per_mat : tg) * kTcTileM;
+            xrow = (t % a.TB) * BN;
+        };
         auto advance = [&]() {
-            if (++j >= kb_end(t) - kb_begin(t)) {
+            if (++jr == nk) jr = 0;
+            if (--left == 0) {
                 t += gridDim.x;
-                j = 0;
+                if (t < n_tiles) enter_unit();
             }
         };
-        auto load_w = [&](int tt, int kk, int s) {
-            const int tg = tt / (a.S * a.TB);
-            const bool second = tg >= tiles_per_mat;
-            const int trow = (second ? tg - tiles_per_mat : tg) * kTcTileM;
-            tma_load_2d(tiles + (size_t)s * STAGE, second ? &map_w1 : &map_w, kk * kTcTileK, trow, &full[s]);
-        };
-        auto load_x = [&](int tt, int kk, int s) {
-            tma_load_2d(tiles + (size_t)s * STAGE + A_BYTES, &map_x, kk * kTcTileK, (tt % a.TB) * BN, &full[s]);
-        };
-        int pre_t[kTcStages], pre_kb[kTcStages];
+        if (t < n_tiles) enter_unit();
+        int pre_x[kTcStages], pre_row[kTcStages];
         int n_pre = 0;
         while (n_pre < kTcStages && t < n_tiles) {
             mbar_expect_tx(&full[n_pre], A_BYTES + B_BYTES);
-            const int kb = kb_at(t, j);
-            load_w(t, kb, n_pre);
-            pre_t[n_pre] = t;
-            pre_kb[n_pre] = kb;
+            const int kx = (k0 + jr) * kTcTileK;
+            tma_load_2d(tiles + (size_t)n_pre * STAGE, wmap, kx, trow, &full[n_pre]);
+            pre_x[n_pre] = kx;
+            pre_row[n_pre] = xrow;
             ++n_pre;
             advance();
         }
         pdl_wait();
         pdl_launch();
-        for (int i = 0; i < n_pre; ++i) load_x(pre_t[i], pre_kb[i], i);
+        for (int i = 0; i < n_pre; ++i) tma_load_2d(tiles + (size_t)i * STAGE + A_BYTES, &map_x, pre_x[i], pre_row[i], &full[i]);
         for (uint32_t it = (uint32_t)n_pre; t < n_tiles && !failed; ++it) {
             const int s = it % kTcStages;
             const uint32_t ph = (it / kTcStages) & 1;
             if (!mbar_wait(&empty[s], ph ^ 1)) { failed = 1; atomicExch(a.err, 1); break; }
             mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-            const int kb = kb_at(t, j);
-            load_w(t, kb, s);
-            load_x(t, kb, s);
+            const int kx = (k0 + jr) * kTcTileK;
+            tma_load_2d(tiles + (size_t)s * STAGE, wmap, kx, trow, &full[s]);
+            tma_load_2d(tiles + (size_t)s * STAGE + A_BYTES, &map_x, kx, xrow, &full[s]);
             advance();
         }
     } else {
