@@ -227,6 +227,25 @@ int32_t oxg4_profile_step(oxg4_model* model, oxg4_cache* cache, const uint32_t* 
 float oxg4_profile_ms(const oxg4_model* model, const char* kind);
 int32_t oxg4_profile_count(const oxg4_model* model, const char* kind);
 
+/* Diagnostic entry points: the reference's smoke functions (crates/oxide-torch-models/src/gemma4_cuda/smoke.rs),
+ * one token through one block of one layer, on a single-GPU model.
+ *   oxg4_smoke_embedding_logits   embedding_logits (smoke.rs:8-30): embedding row * sqrt(hidden) -> BF16 -> tied LM
+ *                                 head; logits[vocab_size], no final norm, no soft cap
+ *   oxg4_smoke_decoder_mlp        decoder_mlp_smoke (smoke.rs:32-59): out[hidden_size]
+ *   oxg4_smoke_decoder_attention  decoder_attention_smoke (smoke.rs:61-126), one token at position 0: out[hidden_size]
+ *   oxg4_smoke_cached_attention   cached_attention_smoke (smoke.rs:128-204): appends the token to `layer`'s K/V ring of
+ *                                 a ONE-sequence cache table and returns the attention output
+ *                                 attended[num_attention_heads * head_dim of the layer]; the table's position
+ *                                 advances by one. A one-sequence table created with oxg4_cache_create stands in
+ *                                 for new_kv_cache (cache.rs:5-29); use it for nothing but these calls.
+ * hidden_size / heads / epsilon / window, which the reference takes as arguments, come from the model's config.
+ * The layer's own RoPE parameters are used where the reference passes theta 10000, factor 1 and the full head
+ * (the sliding layers' values; identical at position 0). KV-shared layers are refused by the attention calls. */
+int32_t oxg4_smoke_embedding_logits(oxg4_model* model, uint32_t token, float* logits);
+int32_t oxg4_smoke_decoder_mlp(oxg4_model* model, uint32_t token, int32_t layer, float* out);
+int32_t oxg4_smoke_decoder_attention(oxg4_model* model, uint32_t token, int32_t layer, float* out);
+int32_t oxg4_smoke_cached_attention(oxg4_model* model, oxg4_cache* cache, uint32_t token, int32_t layer, float* attended);
+
 /* Failure-path test hooks (no counterpart in the reference, whose errors are Result values and whose
  * capture always ends, crates/oxide-torch-cuda/src/cuda_graph.rs:84-97). Neither faults or hangs a GPU.
  * oxg4_debug_wait_timeout runs one of the library's bounded device-side waits (kind 1: mbarrier phase,

@@ -767,6 +767,126 @@ int orc_decode_logits(void* model, void* cache, uint32_t token, float* logits) {
     return 0;
 }
 
+// ---- the diagnostic entry points of gemma4_cuda/smoke.rs, restated ---------------------------------------
+// embedding() (attention.rs:4-35): the token's embedding row widened to f32, times sqrt(hidden)
+static void embed_row(const Model& m, uint32_t token, std::vector<float>& hidden) {
+    const int H = m.c.hidden;
+    hidden.resize(H);
+    const float scale = sqrtf((float)H);
+    for (int i = 0; i < H; ++i) {
+        float e = m.embed.is_bf16 ? bf16_bits_to_f32(m.embed.h[(int64_t)token * H + i]) : m.embed.f[(int64_t)token * H + i];
+        hidden[i] = e * scale;
+    }
+}
+
+// embedding_logits (smoke.rs:8-30): embedding -> bf16 -> tied LM head; no final norm, no soft cap
+int orc_smoke_embedding_logits(void* model, uint32_t token, float* logits) {
+    Model* m = (Model*)model;
+    if ((int64_t)token >= m->c.vocab) return -1;
+    std::vector<float> hidden;
+    embed_row(*m, token, hidden);
+    if (m->c.mode == 1) for (auto& v : hidden) v = round_bf16(v);
+    gemv(m->embed, hidden.data(), logits);
+    return 0;
+}
+
+// decoder_mlp_smoke (smoke.rs:32-59): the dense MLP residual branch of one layer on the embedding of one token
+int orc_smoke_decoder_mlp(void* model, uint32_t token, int layer, float* out) {
+    Model* m = (Model*)model;
+    const Config& c = m->c;
+    if ((int64_t)token >= c.vocab || layer < 0 || layer >= c.layers) return -1;
+    const bool bf = c.mode == 1;
+    const int H = c.hidden;
+    const LayerW& w = m->L[layer];
+    std::vector<float> hidden, x(H), tmp(H);
+    embed_row(*m, token, hidden);
+    rms_norm_rows(hidden.data(), w.pre_ff_ln.v.data(), x.data(), 1, H, c.eps, bf);
+    const int I = (int)w.gate.rows;
+    std::vector<float> gate(I), up(I), act(I), down(H);
+    gemv(w.gate, x.data(), gate.data());
+    gemv(w.up, x.data(), up.data());
+    for (int i = 0; i < I; ++i) {
+        float a = gelu_mul(gate[i], up[i]);
+        act[i] = bf ? round_bf16(a) : a;
+    }
+    gemv(w.down, act.data(), down.data());
+    rms_norm_rows(down.data(), w.post_ff_ln.v.data(), tmp.data(), 1, H, c.eps, false);
+    for (int i = 0; i < H; ++i) out[i] = hidden[i] + tmp[i];
+    return 0;
+}
+
+// q / k / v of one token for one layer at `pos`: norms and RoPE as in the decode step (decode.rs:82-116). The
+// reference's smoke entry points pass theta 10000, factor 1 and the full head to rope(); the layer's own
+// parameters are used here, which is the same thing for sliding layers (and for any layer at position 0).
+static void smoke_qkv(const Model& m, const LayerW& w, const std::vector<float>& hidden, int64_t pos, std::vector<float>& q,
+                      std::vector<float>& k, std::vector<float>& vn) {
+    const Config& c = m.c;
+    const int H = c.hidden, D = w.head_dim, QW = c.heads * D, KW = w.kv_heads * D;
+    std::vector<float> x(H), qn(QW), kn(KW), v(KW);
+    rms_norm_rows(hidden.data(), w.input_ln.v.data(), x.data(), 1, H, c.eps, c.mode == 1);
+    q.resize(QW); k.resize(KW); vn.resize(KW);
+    gemv(w.q, x.data(), q.data());
+    rms_norm_rows(q.data(), w.q_norm.v.data(), qn.data(), c.heads, D, c.eps, false);
+    rope_rows(qn.data(), q.data(), c.heads, D, w.rotary_dim, w.theta, w.factor, pos);
+    gemv(w.k, x.data(), k.data());
+    gemv(w.v, x.data(), v.data());
+    rms_norm_rows(k.data(), w.k_norm.v.data(), kn.data(), w.kv_heads, D, c.eps, false);
+    rope_rows(kn.data(), k.data(), w.kv_heads, D, w.rotary_dim, w.theta, w.factor, pos);
+    rms_norm_rows(v.data(), nullptr, vn.data(), w.kv_heads, D, c.eps, false);
+}
+
+static void smoke_append(bool kv_bf16, LayerCache& lc, int64_t pos, const std::vector<float>& k, const std::vector<float>& vn) {
+    const int64_t KW = (int64_t)k.size(), slot = pos % lc.capacity;
+    for (int64_t i = 0; i < KW; ++i) {
+        float kk = k[i], vv = vn[i];
+        if (kv_bf16) { kk = round_bf16(kk); vv = round_bf16(vv); }
+        lc.k[slot * KW + i] = kk;
+        lc.v[slot * KW + i] = vv;
+    }
+}
+
+// decoder_attention_smoke (smoke.rs:61-126): the attention residual branch of one layer for one token at position 0
+int orc_smoke_decoder_attention(void* model, uint32_t token, int layer, float* out) {
+    Model* m = (Model*)model;
+    const Config& c = m->c;
+    if ((int64_t)token >= c.vocab || layer < 0 || layer >= c.layers || m->L[layer].source != layer) return -1;
+    const LayerW& w = m->L[layer];
+    const int H = c.hidden, D = w.head_dim;
+    std::vector<float> hidden, q, k, vn, att((size_t)c.heads * D), proj(H), tmp(H);
+    embed_row(*m, token, hidden);
+    smoke_qkv(*m, w, hidden, 0, q, k, vn);
+    LayerCache lc;
+    lc.capacity = 1; lc.kv_heads = w.kv_heads; lc.head_dim = D;
+    lc.k.assign((size_t)w.kv_heads * D, 0.0f);
+    lc.v.assign((size_t)w.kv_heads * D, 0.0f);
+    smoke_append(false, lc, 0, k, vn);          // no cache here: K and V stay in an f32 workspace
+    gqa_decode_ring(q.data(), lc, c.heads, 0, 0, att.data());
+    if (c.mode == 1) for (auto& a : att) a = round_bf16(a);
+    gemv(w.o, att.data(), proj.data());
+    rms_norm_rows(proj.data(), w.post_attn_ln.v.data(), tmp.data(), 1, H, c.eps, false);
+    for (int i = 0; i < H; ++i) out[i] = hidden[i] + tmp[i];
+    return 0;
+}
+
+// cached_attention_smoke (smoke.rs:128-204): appends one token to the layer's ring of `cache` and returns the
+// attention output [heads * head_dim] against it; the cache's position advances by one
+int orc_smoke_cached_attention(void* model, void* cache, uint32_t token, int layer, float* attended) {
+    Model* m = (Model*)model;
+    Cache* ch = (Cache*)cache;
+    const Config& c = m->c;
+    if ((int64_t)token >= c.vocab || layer < 0 || layer >= c.layers || m->L[layer].source != layer) return -1;
+    const LayerW& w = m->L[layer];
+    LayerCache& lc = ch->L[layer];
+    const int64_t pos = ch->position;
+    std::vector<float> hidden, q, k, vn;
+    embed_row(*m, token, hidden);
+    smoke_qkv(*m, w, hidden, pos, q, k, vn);
+    smoke_append(c.kv_bf16, lc, pos, k, vn);
+    gqa_decode_ring(q.data(), lc, c.heads, w.sliding ? c.sliding_window : 0, pos, attended);
+    ch->position += 1;
+    return 0;
+}
+
 // decode_topk (decode.rs:666-783): mark_seen, step, two-stage top-k with penalty.
 // logits_out may be null. top_k is clamped to 1..=64 and to the vocabulary.
 int orc_decode_topk(void* model, void* cache, uint32_t token, int top_k, float penalty,

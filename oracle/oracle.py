@@ -231,6 +231,25 @@ class OracleModel:
     def new_cache(self, max_sequence: int):
         return OracleCache(self, max_sequence)
 
+    # ---- gemma4_cuda/smoke.rs restated (one token through one block of one layer) ----
+    def embedding_logits(self, token: int) -> np.ndarray:
+        out = np.empty(self.cfg["vocab_size"], dtype=np.float32)
+        if lib().orc_smoke_embedding_logits(self._h, C.c_uint32(token), _fp(out)) != 0:
+            raise ValueError("token id exceeds vocabulary")
+        return out
+
+    def decoder_mlp_smoke(self, token: int, layer: int) -> np.ndarray:
+        out = np.empty(self.cfg["hidden_size"], dtype=np.float32)
+        if lib().orc_smoke_decoder_mlp(self._h, C.c_uint32(token), C.c_int(layer), _fp(out)) != 0:
+            raise ValueError("invalid token or layer")
+        return out
+
+    def decoder_attention_smoke(self, token: int, layer: int) -> np.ndarray:
+        out = np.empty(self.cfg["hidden_size"], dtype=np.float32)
+        if lib().orc_smoke_decoder_attention(self._h, C.c_uint32(token), C.c_int(layer), _fp(out)) != 0:
+            raise ValueError("invalid token or layer")
+        return out
+
     def generate(self, prompt, max_new_tokens, temperature=1.0, top_k=1, top_p=0.95,
                  repetition_penalty=1.0, seed=0x4D595DF4D0F33173, eos=(), want_first_logits=False):
         prompt = np.ascontiguousarray(prompt, dtype=np.uint32)
@@ -270,6 +289,16 @@ class OracleCache:
         if cap:
             lib().orc_softcap(_fp(values), C.c_int64(values.size), C.c_float(cap))
         return values
+
+    def cached_attention_smoke(self, token: int, layer: int) -> np.ndarray:
+        """gemma4_cuda/smoke.rs:128-204 on this cache: append the token to the layer's ring, attend, advance."""
+        cfg = self.model.cfg
+        sliding = cfg["layer_types"][layer] == "sliding_attention"
+        d = cfg["head_dim"] if sliding else cfg.get("global_head_dim", cfg["head_dim"])
+        out = np.empty(cfg["num_attention_heads"] * d, dtype=np.float32)
+        if lib().orc_smoke_cached_attention(self.model._h, self._h, C.c_uint32(token), C.c_int(layer), _fp(out)) != 0:
+            raise ValueError("invalid token or layer")
+        return out
 
     def decode_logits(self, token: int) -> np.ndarray:
         logits = np.empty(self.model.cfg["vocab_size"], dtype=np.float32)

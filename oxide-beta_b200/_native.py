@@ -100,6 +100,10 @@ SYMBOLS = {
     "oxg4_profile_count": (C.c_int32, [C.c_void_p, C.c_char_p]),
     "oxg4_debug_wait_timeout": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_uint32]),
     "oxg4_debug_fail_alloc_after": (None, [C.c_int32]),
+    "oxg4_smoke_embedding_logits": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_void_p]),
+    "oxg4_smoke_decoder_mlp": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_int32, C.c_void_p]),
+    "oxg4_smoke_decoder_attention": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_int32, C.c_void_p]),
+    "oxg4_smoke_cached_attention": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_int32, C.c_void_p]),
     "oxg4_debug_fill_cache": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]),
     "oxg4_topk_noalloc": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_float, C.c_int32, C.c_void_p,
                                       C.c_void_p, C.c_void_p]),

@@ -2260,6 +2260,201 @@ extern "C" int32_t oxg4_decode_trace(oxg4_model* m, oxg4_cache* c, const uint32_
     return s;
 }
 
+// ------------------------------------------------------------------------------------------------
+// Diagnostic entry points: the counterparts of the reference's smoke functions (gemma4_cuda/smoke.rs:8-204), one
+// token through one block of one layer, built from the kernels of the one-sequence decode step. Single-GPU models.
+// ------------------------------------------------------------------------------------------------
+struct ScratchTable {      // a one-sequence cache table for entry points that take none (workspace + a 16-token ring)
+    oxg4_cache* c = nullptr;
+    ~ScratchTable() { if (c) oxg4_cache_destroy(c); }
+    int32_t open(oxg4_model* m) {
+        const int32_t max_seq = 16;
+        return oxg4_cache_create(m, 1, &max_seq, 16, OXG4_F32, &c);
+    }
+};
+
+static int32_t smoke_check(oxg4_model* m, uint32_t token, int32_t layer, bool need_layer, bool own_kv) {
+    if (!m) return fail(OXG4_INVALID_ARGUMENT, "null argument");
+    if (!m->finalized) return fail(OXG4_INVALID_ARGUMENT, "model is not finalized");
+    if (m->tp > 1) return fail(OXG4_UNSUPPORTED, "the diagnostic entry points run on a single-GPU model");
+    if (token >= (uint32_t)m->V) return fail(OXG4_INVALID_ARGUMENT, "token id exceeds CUDA embedding table");   // attention.rs:13-17
+    if (need_layer && (layer < 0 || layer >= m->cfg.num_hidden_layers)) return fail(OXG4_INVALID_ARGUMENT, "layer out of range");
+    if (own_kv && m->layers[layer].shared) return fail(OXG4_UNSUPPORTED, "layer %d shares the K/V of layer %d", layer, m->layers[layer].source);
+    return OXG4_OK;
+}
+
+static int32_t smoke_stage(oxg4_cache* c, uint32_t token) {
+    c->h_tokens[0] = token;
+    CK(cudaMemcpyAsync(c->tokens, c->h_tokens, sizeof(uint32_t), cudaMemcpyHostToDevice, c->m->stream));
+    return OXG4_OK;
+}
+
+static int32_t smoke_finish(oxg4_cache* c, Launcher& ln, const float* dev, float* host, size_t n) {
+    oxg4_model* m = c->m;
+    TRY(ln.status);
+    m->launches += ln.kernels;
+    CK(cudaMemcpyAsync(host, dev, sizeof(float) * n, cudaMemcpyDeviceToHost, m->stream));
+    CK(cudaStreamSynchronize(m->stream));
+    return OXG4_OK;
+}
+
+// input norm + fused QKV projection of `layer` on the embedding of the staged token: layer input -> c->hB, qkv -> c->qkv_raw
+static void smoke_qkv(oxg4_cache* c, Launcher& ln, int layer) {
+    oxg4_model* m = c->m;
+    const LayerPlan& p = m->layers[layer];
+    GemvArgs a{};
+    a.W0 = p.wqkv;
+    a.embed = m->embed;
+    a.tokens = c->tokens;
+    a.embed_scale = sqrtf((float)m->H);
+    a.h_out = c->hB;
+    a.w_norm = p.input_ln;
+    a.scalar = 1.0f;
+    a.out = c->qkv_raw;
+    launch_gemv(ln, "qkv", c, 1, a, p.p_qkv, PRO_NORM, EPI_STORE);
+}
+
+static RowSet smoke_rows(oxg4_cache* c) {
+    RowSet rs;
+    rs.R = 1;
+    rs.tok = c->tokens;
+    rs.pos = c->pos;
+    for (int k = 0; k < 2; ++k) {
+        rs.grp_row0[k] = c->dec_grp_row0;
+        rs.grp_n[k] = c->dec_grp_n;
+        rs.NG[k] = 1;
+    }
+    return rs;
+}
+
+// embedding_logits (smoke.rs:8-30): embedding row * sqrt(hidden) -> BF16 -> tied LM head; no final norm, no soft cap
+extern "C" int32_t oxg4_smoke_embedding_logits(oxg4_model* m, uint32_t token, float* logits) {
+    if (!logits) return fail(OXG4_INVALID_ARGUMENT, "null argument");
+    TRY(smoke_check(m, token, 0, false, false));
+    TRY(bind_device(m));
+    ScratchTable t;
+    TRY(t.open(m));
+    oxg4_cache* c = t.c;
+    TRY(smoke_stage(c, token));
+    Launcher ln{m};
+    if (m->es == 2)
+        ln.go("embed", ple_embed_rows_kernel<uint16_t>, dim3(1), dim3(256), 0, m->H, (const uint16_t*)m->embed,
+              (const uint32_t*)c->tokens, sqrtf((float)m->H), c->hA);
+    else
+        ln.go("embed", ple_embed_rows_kernel<float>, dim3(1), dim3(256), 0, m->H, (const float*)m->embed,
+              (const uint32_t*)c->tokens, sqrtf((float)m->H), c->hA);
+    GemvArgs a{};
+    a.W0 = m->embed;
+    a.in = c->hA;
+    a.out = c->logits;
+    launch_gemv(ln, "lmhead", c, 1, a, m->p_lm, PRO_PLAIN, EPI_STORE);
+    return smoke_finish(c, ln, c->logits, logits, (size_t)m->V);
+}
+
+// decoder_mlp_smoke (smoke.rs:32-59): hidden + rmsnorm(down(gelu(gate x) * up x), post_ff_ln), x = rmsnorm(hidden, pre_ff_ln)
+extern "C" int32_t oxg4_smoke_decoder_mlp(oxg4_model* m, uint32_t token, int32_t layer, float* out) {
+    if (!out) return fail(OXG4_INVALID_ARGUMENT, "null argument");
+    TRY(smoke_check(m, token, layer, true, false));
+    TRY(bind_device(m));
+    ScratchTable t;
+    TRY(t.open(m));
+    oxg4_cache* c = t.c;
+    TRY(smoke_stage(c, token));
+    const LayerPlan& p = m->layers[layer];
+    Launcher ln{m};
+    {
+        GemvArgs a{};
+        a.W0 = p.wgate;
+        a.W1 = p.wup;
+        a.embed = m->embed;
+        a.tokens = c->tokens;
+        a.embed_scale = sqrtf((float)m->H);
+        a.h_out = c->hA;
+        a.w_norm = p.pre_ff_ln;
+        a.scalar = 1.0f;
+        a.out = c->gu_raw;
+        launch_gemv(ln, "gateup", c, 1, a, m->p_gateup, PRO_NORM, EPI_GATEUP);
+    }
+    {
+        GemvArgs a{};
+        a.W0 = p.wdown;
+        a.in = c->gu_raw;
+        a.out = c->down_raw;
+        launch_gemv(ln, "down", c, 1, a, m->p_down, PRO_PLAIN, EPI_STORE);
+    }
+    {   // the residual update is the prologue of the projection that would follow: hB = hA + rmsnorm(down, post_ff_ln)
+        GemvArgs a{};
+        a.W0 = p.wqkv;
+        a.h_in = c->hA;
+        a.h_out = c->hB;
+        a.raw = c->down_raw;
+        a.w_post = p.post_ff_ln;
+        a.scalar = 1.0f;
+        a.w_norm = p.input_ln;
+        a.out = c->qkv_raw;
+        launch_gemv(ln, "qkv", c, 1, a, p.p_qkv, PRO_NORM, EPI_STORE);
+    }
+    return smoke_finish(c, ln, c->hB, out, (size_t)m->H);
+}
+
+// decoder_attention_smoke (smoke.rs:61-126): the attention residual branch of one layer for one token at position 0
+// (a single position attends to itself; the rotation at position 0 is the identity for any theta)
+extern "C" int32_t oxg4_smoke_decoder_attention(oxg4_model* m, uint32_t token, int32_t layer, float* out) {
+    if (!out) return fail(OXG4_INVALID_ARGUMENT, "null argument");
+    TRY(smoke_check(m, token, layer, true, true));
+    TRY(bind_device(m));
+    ScratchTable t;
+    TRY(t.open(m));
+    oxg4_cache* c = t.c;
+    TRY(smoke_stage(c, token));
+    const LayerPlan& p = m->layers[layer];
+    Launcher ln{m};
+    smoke_qkv(c, ln, layer);
+    launch_attention(ln, c, smoke_rows(c), layer, c->qkv_raw, 1, nullptr, false);
+    {
+        GemvArgs a{};
+        a.W0 = p.wo;
+        a.in = c->attn_out;
+        a.out = c->o_raw;
+        launch_gemv(ln, "o", c, 1, a, p.p_o, PRO_PLAIN, EPI_STORE);
+    }
+    {   // hA = hB + rmsnorm(o, post_attn_ln): the prologue of the gate/up projection
+        GemvArgs a{};
+        a.W0 = p.wgate;
+        a.W1 = p.wup;
+        a.h_in = c->hB;
+        a.h_out = c->hA;
+        a.raw = c->o_raw;
+        a.w_post = p.post_attn_ln;
+        a.scalar = 1.0f;
+        a.w_norm = p.pre_ff_ln;
+        a.out = c->gu_raw;
+        launch_gemv(ln, "gateup", c, 1, a, m->p_gateup, PRO_NORM, EPI_GATEUP);
+    }
+    return smoke_finish(c, ln, c->hA, out, (size_t)m->H);
+}
+
+// cached_attention_smoke (smoke.rs:128-204): one token appended to the layer's K/V ring of a one-sequence cache
+// table (the counterpart of new_kv_cache, cache.rs:5-29) and attended against it; returns [heads * head_dim] and
+// advances the table's position. The layer's own RoPE parameters are used (the reference passes theta 10000,
+// factor 1, full rotary: the sliding layers' values). Use such a table for nothing but these calls.
+extern "C" int32_t oxg4_smoke_cached_attention(oxg4_model* m, oxg4_cache* c, uint32_t token, int32_t layer, float* attended) {
+    if (!c || !attended || c->m != m) return fail(OXG4_INVALID_ARGUMENT, "null or mismatched handle");
+    TRY(smoke_check(m, token, layer, true, true));
+    if (c->B != 1) return fail(OXG4_INVALID_SHAPE, "cached attention smoke takes a one-sequence cache table");
+    TRY(bind_device(m));
+    TRY(check_tokens(c, &token, false));
+    TRY(smoke_stage(c, token));
+    Launcher ln{m};
+    smoke_qkv(c, ln, layer);
+    launch_attention(ln, c, smoke_rows(c), layer, c->qkv_raw, 1, nullptr, false);
+    TRY(smoke_finish(c, ln, c->attn_out, attended, (size_t)m->layers[layer].qw));
+    c->pos_host[0] += 1;
+    CK(cudaMemcpyAsync(c->pos, c->pos_host.data(), sizeof(int32_t), cudaMemcpyHostToDevice, m->stream));
+    CK(cudaStreamSynchronize(m->stream));
+    return OXG4_OK;
+}
+
 extern "C" int32_t oxg4_debug_timeline(oxg4_cache* c, unsigned long long* out, int32_t max_entries) {
     if (!c || !out) return fail(OXG4_INVALID_ARGUMENT, "null argument");
     if (!c->ts_buf) return fail(OXG4_UNSUPPORTED, "timeline recording is off (set OXG4_TIMELINE before creating the model)");

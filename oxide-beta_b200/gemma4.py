@@ -343,6 +343,29 @@ class Gemma4CudaState:
                                           _ptr(trace), None if logits is None else _ptr(logits)))
         return trace, logits
 
+    # ---- the reference's diagnostic entry points (gemma4_cuda/smoke.rs) ----
+    def embedding_logits(self, token: int) -> np.ndarray:
+        out = np.empty(self.config.vocab_size, dtype=np.float32)
+        N.check(N.lib().oxg4_smoke_embedding_logits(self._h, int(token), out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def decoder_mlp_smoke(self, token: int, layer: int) -> np.ndarray:
+        out = np.empty(self.config.hidden_size, dtype=np.float32)
+        N.check(N.lib().oxg4_smoke_decoder_mlp(self._h, int(token), int(layer), out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def decoder_attention_smoke(self, token: int, layer: int) -> np.ndarray:
+        out = np.empty(self.config.hidden_size, dtype=np.float32)
+        N.check(N.lib().oxg4_smoke_decoder_attention(self._h, int(token), int(layer), out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def cached_attention_smoke(self, token: int, layer: int, table: Gemma4CudaCacheTable) -> np.ndarray:
+        sliding = self.config.layer_types[layer] == "sliding_attention"
+        d = self.config.head_dim if sliding else self.config.global_head_dim
+        out = np.empty(self.config.num_attention_heads * d, dtype=np.float32)
+        N.check(N.lib().oxg4_smoke_cached_attention(self._h, table._h, int(token), int(layer), out.ctypes.data_as(C.c_void_p)))
+        return out
+
     def decode_greedy(self, first_tokens, table: Gemma4CudaCacheTable, steps: int):
         """Device-resident greedy loop: returns (ids [steps, batch], mean device ms per step)."""
         t = _as_u32(np.atleast_1d(first_tokens))

@@ -318,3 +318,41 @@ def test_shared_layer_without_source_is_rejected():
     cfg["num_kv_shared_layers"] = 1          # the only full_attention layer is shared: no earlier source
     with pytest.raises(ValueError):
         orc.OracleModel(cfg, orc.F32)
+
+
+def test_smoke_restatements_match_numpy():
+    """The oracle's restatement of gemma4_cuda/smoke.rs (embedding_logits :8-30, decoder_mlp_smoke :32-59,
+    decoder_attention_smoke :61-126, cached_attention_smoke :128-204) against the same blocks written with numpy
+    in float64 (f32 recipe, tiny model), and cached attention at position 0 against the attention block."""
+    cfg = syn._cfg(300, 64, 2, 4, 2, 16, 96, 8, ["sliding_attention", "full_attention"])
+    weights = dict(syn.generate_weights(cfg, seed=3, dtype="f32", norm_jitter=0.1))
+    o = orc.OracleModel(cfg, orc.F32)
+    o.load(weights)
+    W = {k: np.asarray(v, dtype=np.float64) for k, v in weights.items()}
+    H, eps, token = cfg["hidden_size"], cfg["rms_norm_eps"], 17
+
+    def rms(x, w=None):
+        y = x / np.sqrt((x * x).mean(-1, keepdims=True) + eps)
+        return y if w is None else y * w
+
+    hidden = W["embed_tokens.weight"][token] * np.sqrt(np.float32(H))
+    assert np.abs(o.embedding_logits(token) - W["embed_tokens.weight"] @ hidden).max() < 1e-4
+    for l in range(2):
+        p = f"layers.{l}."
+        x = rms(hidden, W[p + "pre_feedforward_layernorm.weight"])
+        g, u = W[p + "mlp.gate_proj.weight"] @ x, W[p + "mlp.up_proj.weight"] @ x
+        act = 0.5 * g * (1.0 + np.tanh(0.7978846 * (g + 0.044715 * g ** 3))) * u
+        want = hidden + rms(W[p + "mlp.down_proj.weight"] @ act, W[p + "post_feedforward_layernorm.weight"])
+        assert np.abs(o.decoder_mlp_smoke(token, l) - want).max() < 1e-4
+        # one position attends to itself: the output of every query head is its KV head's unit-normed value row
+        D, Nq, Nkv = cfg["head_dim"], cfg["num_attention_heads"], cfg["num_key_value_heads"]
+        x = rms(hidden, W[p + "input_layernorm.weight"])
+        vn = rms((W[p + "self_attn.v_proj.weight"] @ x).reshape(Nkv, D))
+        att = np.repeat(vn, Nq // Nkv, axis=0).reshape(-1)
+        want = hidden + rms(W[p + "self_attn.o_proj.weight"] @ att, W[p + "post_attention_layernorm.weight"])
+        assert np.abs(o.decoder_attention_smoke(token, l) - want).max() < 1e-4
+        cache = o.new_cache(8)
+        assert np.abs(cache.cached_attention_smoke(token, l) - att).max() < 1e-5
+        assert cache.position == 1
+    with pytest.raises(ValueError):
+        o.decoder_mlp_smoke(token, 2)
