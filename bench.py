@@ -325,6 +325,11 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
     torch.cuda.set_device(local_rank)
     dist = None
+    # The one JSON line is the only thing this program writes to its standard output: libraries that print
+    # there (NCCL announces its version on stdout) are sent to stderr for the length of the run.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
@@ -407,7 +412,8 @@ def main():
         out["cpu_baseline"] = {"value": tps, "unit": UNIT, "cores": cores, "kind": "port",
                                "sample": f"{cpu_steps} greedy decode steps at batch 1 after a {sample_prompt}-token "
                                          f"prompt, full {args.workload} weights, BF16 recipe"}
-    print(json.dumps(out))
+    sys.stdout.flush()
+    os.write(json_fd, (json.dumps(out) + "\n").encode())
     if dist:
         dist.destroy_process_group()
 
