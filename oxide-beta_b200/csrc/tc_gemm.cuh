@@ -1,19 +1,20 @@
 // Batched projection on the 5th-generation tensor cores (tcgen05 + TMEM), fed by TMA.
 //
 // out[b, n] = sum_k x[b, k] * W[n, k]   (the reference's cuBLAS contract, crates/oxide-torch-cuda/src/
-// cublas.rs:101-153: BF16 operands, f32 accumulate, f32 output) for 1..64 activation rows per block (up to
-// 256 rows in four blocks for prompt chunks), where the weight matrix is streamed from HBM exactly once.
+// cublas.rs:101-153: BF16 operands, f32 accumulate, f32 output) for 1..256 activation rows (one block of 16 / 32 /
+// 64 / 128 / 256 rows per weight tile), where the weight matrix is streamed from HBM exactly once.
 //
 // Roles are swapped with respect to a textbook GEMM because the batch is the small dimension: the
 // 128-row weight tile is the MMA's M operand (A, K-major in shared memory), the activations are
-// the N operand (B, K-major), the accumulator lives in TMEM as 128 lanes x N columns of f32.
+// the N operand (B, K-major), the accumulator lives in TMEM as 128 lanes x N columns of f32. Two accumulators
+// are allocated: the MMAs of a CTA's next work unit run while the epilogue warps drain the previous one.
 //
 //   warp 0, one lane : TMA producer  (cp.async.bulk.tensor.2d, 128-byte swizzle, NS-stage ring)
 //   warp 1, one lane : MMA issuer    (tcgen05.mma.cta_group::1.kind::f16, 4 x K=16 per 64-wide stage)
 //   warps 2..5       : epilogue      (tcgen05.ld 32x32b, one TMEM lane = one output row per thread;
 //                                     a warp may only touch TMEM lanes 32 * (warp % 4) .. + 31)
 //
-// A CTA walks the 128-row tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... Rows past the end of the
+// A CTA walks the work units (tile, K-split, row block) u = blockIdx.x, blockIdx.x + gridDim.x, ... Rows past the end of the
 // matrix and batch rows past B are zero-filled by TMA (tensor-map bounds) and masked at the store.
 // Every mbarrier wait is bounded: when a wait runs out the kernel raises `*err`, stops issuing work,
 // still frees its TMEM columns and returns, so a protocol bug cannot hang the GPU.
