@@ -481,6 +481,38 @@ struct QkvPostArgs {
     int write_kv;                // 0: a KV-shared layer (its source layer has appended K/V; the projection holds q only)
 };
 
+// EPT (2, 4 or 8) consecutive f32 / 16-bit values per lane, moved with the widest aligned access
+template <int EPT> DEVINL void ld_f32_vec(const float* p, float (&v)[EPT]) {
+    if constexpr (EPT == 8) {
+        const float4 a = __ldcg(reinterpret_cast<const float4*>(p)), b = __ldcg(reinterpret_cast<const float4*>(p) + 1);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else if constexpr (EPT == 4) {
+        const float4 a = __ldcg(reinterpret_cast<const float4*>(p));
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    } else {
+        const float2 a = __ldcg(reinterpret_cast<const float2*>(p));
+        v[0] = a.x; v[1] = a.y;
+    }
+}
+template <int EPT> DEVINL void st_f32_vec(float* p, const float (&v)[EPT]) {
+    if constexpr (EPT == 8) {
+        reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+        reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+    } else if constexpr (EPT == 4) {
+        reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+        reinterpret_cast<float2*>(p)[0] = make_float2(v[0], v[1]);
+    }
+}
+template <int EPT> DEVINL void st_u16_vec(uint16_t* p, const uint32_t (&bits)[EPT]) {      // low 16 bits of every entry
+    uint32_t w[EPT / 2];
+#pragma unroll
+    for (int i = 0; i < EPT / 2; ++i) w[i] = (bits[2 * i] & 0xffffu) | (bits[2 * i + 1] << 16);
+    if constexpr (EPT == 8) *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    else if constexpr (EPT == 4) *reinterpret_cast<uint2*>(p) = make_uint2(w[0], w[1]);
+    else *reinterpret_cast<uint32_t*>(p) = w[0];
+}
+
 template <typename KT, int D>
 __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostArgs a) {
     constexpr int EPT = D / 32;
@@ -497,23 +529,28 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostArgs a) {
     const int pos = a.row_pos[row];
     const int col = task * D;                                  // q heads, then k heads, then v heads
     float t[EPT];
+#pragma unroll
+    for (int e = 0; e < EPT; ++e) t[e] = 0.0f;
+    for (int sp = 0; sp < a.splits; ++sp) {                    // K-split partials, in split order
+        float v[EPT];
+        ld_f32_vec<EPT>(a.qkv + ((size_t)sp * a.R + row) * a.qkv_n + col + lane * EPT, v);
+#pragma unroll
+        for (int e = 0; e < EPT; ++e) t[e] += v[e];
+    }
     float ss = 0.0f;
 #pragma unroll
-    for (int e = 0; e < EPT; ++e) {
-        float v = 0.0f;
-        for (int sp = 0; sp < a.splits; ++sp) v += __ldcg(a.qkv + ((size_t)sp * a.R + row) * a.qkv_n + col + lane * EPT + e);
-        t[e] = v;
-        ss += v * v;
-    }
+    for (int e = 0; e < EPT; ++e) ss += t[e] * t[e];
     ss = warp_sum(ss);
     const float r = 1.0f / sqrtf(ss / (float)D + a.eps);
     const bool is_v = task >= a.Nq + a.Nkv;
     float o[EPT];
     if (!is_v) {
-        const float* w = task < a.Nq ? a.q_norm : a.k_norm;
         constexpr int half = D / 2;
+        float w[EPT], fr[EPT];
+        ld_f32_vec<EPT>((task < a.Nq ? a.q_norm : a.k_norm) + lane * EPT, w);
+        ld_f32_vec<EPT>(a.inv_freq + (lane * EPT) % half, fr);               // a lane's elements lie in one half
 #pragma unroll
-        for (int e = 0; e < EPT; ++e) t[e] = t[e] * r * w[lane * EPT + e];
+        for (int e = 0; e < EPT; ++e) t[e] = t[e] * r * w[e];
 #pragma unroll
         for (int e = 0; e < EPT; ++e) {
             const int d = lane * EPT + e;
@@ -521,9 +558,10 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostArgs a) {
             const float partner = __shfl_xor_sync(0xffffffffu, t[e], 16);      // element d +- D/2 lives 16 lanes away
             float v = t[e];
             if (fi < a.rotary_half) {
-                const float angle = (float)pos * a.inv_freq[fi];
+                float sn, cs;
+                sincosf((float)pos * fr[e], &sn, &cs);
                 const float rotated = d < half ? -partner : partner;
-                v = v * cosf(angle) + rotated * sinf(angle);
+                v = v * cs + rotated * sn;
             }
             o[e] = v;
         }
@@ -533,12 +571,14 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostArgs a) {
     }
     if (task < a.Nq) {
         uint16_t* dst = a.q_hl + ((size_t)row * a.Nq + task) * 2 * D + lane * EPT;
+        uint32_t hi[EPT], lo[EPT];
 #pragma unroll
         for (int e = 0; e < EPT; ++e) {
-            const uint32_t hi = f32_to_bf16_bits(o[e]);
-            dst[e] = (uint16_t)hi;
-            dst[D + e] = (uint16_t)f32_to_bf16_bits(o[e] - __uint_as_float(hi << 16));
+            hi[e] = f32_to_bf16_bits(o[e]);
+            lo[e] = f32_to_bf16_bits(o[e] - __uint_as_float(hi[e] << 16));
         }
+        st_u16_vec<EPT>(dst, hi);
+        st_u16_vec<EPT>(dst + D, lo);
         return;
     }
     const int kvh = (task - a.Nq) % a.Nkv;
@@ -547,10 +587,13 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const QkvPostArgs a) {
     const size_t off = (((size_t)a.page_table[(size_t)seq * a.pages_per_seq + slot / a.page_tokens] * a.Nkv + kvh) *
                             a.page_tokens + slot % a.page_tokens) * (size_t)D + lane * EPT;
     KT* pool = (KT*)(is_v ? a.vpool : a.kpool);
+    if constexpr (sizeof(KT) == 2) {
+        uint32_t bits[EPT];
 #pragma unroll
-    for (int e = 0; e < EPT; ++e) {
-        if constexpr (sizeof(KT) == 2) pool[off + e] = (uint16_t)f32_to_bf16_bits(o[e]);
-        else pool[off + e] = o[e];
+        for (int e = 0; e < EPT; ++e) bits[e] = f32_to_bf16_bits(o[e]);
+        st_u16_vec<EPT>((uint16_t*)pool + off, bits);
+    } else {
+        st_f32_vec<EPT>((float*)pool + off, o);
     }
 }
 
