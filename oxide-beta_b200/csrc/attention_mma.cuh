@@ -58,6 +58,7 @@ struct AttnMmaArgs {
     int part_rows;               // rows per partial slot (tokens per group * G <= 8)
     float* part;                 // [NG * Nkv + total consumer warps][part_rows][D + 2]
     int* err;                    // device flag, raised when a bounded wait ran out
+    int* pre_out;                // [NG + 1] tile prefix of the groups, written by the attention kernel for the merge
     // merge only
     int total_warps;
     float* out;                  // [R, Nq * D]
@@ -172,6 +173,8 @@ attn_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant
     am_prefix(a, pre);                                         // contains the CTA-wide barriers
     const int T = pre[a.NG] * a.Nkv;
     const int W = (int)gridDim.x * NCW;
+    if (blockIdx.x == 0)                                       // the merge kernel reads the prefix instead of redoing it
+        for (int g = tid; g <= a.NG; g += (int)blockDim.x) a.pre_out[g] = pre[g];
 
     if (warp == NCW) {
         // ---- producer: lane w streams the tiles of consumer warp w ----
@@ -366,16 +369,16 @@ inline size_t attn_mma_smem_bytes() {
 template <int D, int G>
 __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnMmaArgs a) {
     constexpr int CH = 64;                                     // partials handled per round
-    __shared__ int pre[kAmMaxGroups + 1];
     __shared__ float s_m[kAmRows][CH], s_e[kAmRows][CH], s_l[kAmRows][CH], s_L[kAmRows], s_M[kAmRows];
     pdl_wait();
     pdl_launch();
-    am_prefix(a, pre);
     const int u = blockIdx.x, g = u / a.Nkv, kvh = u % a.Nkv;
-    const int nt = pre[g + 1] - pre[g];
+    // tile prefix of the groups as the attention kernel computed it (one round of loads instead of a CTA-wide scan)
+    const int pre_g = __ldcg(a.pre_out + g), pre_g1 = __ldcg(a.pre_out + g + 1), pre_all = __ldcg(a.pre_out + a.NG);
+    const int nt = pre_g1 - pre_g;
     if (nt == 0) return;
-    const int T = pre[a.NG] * a.Nkv, W = a.total_warps;
-    const int ub = pre[g] * a.Nkv + kvh * nt;
+    const int T = pre_all * a.Nkv, W = a.total_warps;
+    const int ub = pre_g * a.Nkv + kvh * nt;
     const int w0 = am_warp_of(T, W, ub), w1 = am_warp_of(T, W, ub + nt - 1);
     const int nrows = a.grp_n[g] * G, row0 = a.grp_row0[g];
     const int tid = threadIdx.x;

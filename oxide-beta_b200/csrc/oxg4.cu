@@ -712,6 +712,7 @@ struct oxg4_cache {
     bool mma_attn = false;
     uint16_t* q_hl = nullptr;
     float* am_part = nullptr;
+    int* am_pre = nullptr;                    // tile prefix of the attention groups, attention kernel -> merge kernel
     std::vector<CUtensorMap> kmap, vmap;
     // tcgen05 path (decode with eight or more sequences, and every prompt chunk of a BF16 model): BF16
     // activations, K-split partial outputs, error flag
@@ -901,6 +902,7 @@ static int32_t cache_build(oxg4_cache* c) {
         TRY(dalloc(c, &c->q_hl, (size_t)R * 2 * m->qw_max));
         const int warps = m->num_sms * 4;                       // upper bound of the consumer warps of a launch
         TRY(dalloc(c, &c->am_part, ((size_t)std::min(R, kAmMaxGroups) * kvh_max + warps) * kAmRows * (m->Dmax + 2)));
+        TRY(dalloc(c, &c->am_pre, (size_t)kAmMaxGroups + 1));
     }
     // models with per-layer embeddings run through the small-batch kernels only (the extra projections per layer
     // are tiny and have no tcgen05 variant)
@@ -1498,6 +1500,7 @@ static void launch_attention(Launcher& ln, oxg4_cache* c, const RowSet& rs, int 
         a.window = window;
         a.part_rows = rs.chunk ? kAmRows : p.G;
         a.part = c->am_part;
+        a.pre_out = c->am_pre;
         a.err = c->tc_err;
         a.out = c->attn_out;
         a.out_bf16 = out_bf16;
