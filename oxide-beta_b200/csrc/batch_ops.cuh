@@ -199,8 +199,9 @@ sum_splits_kernel(const float* part, int splits, size_t n, float* out, const Pee
         }
     }
     if (px.tp > 1) {
-        // the last CTA to finish publishes the exchange to every rank (its own flag array included)
-        __threadfence();
+        // the last CTA to finish publishes the exchange to every rank (its own flag array included); every thread
+        // orders its own peer stores at system scope before its CTA reports in
+        __threadfence_system();
         __syncthreads();
         if (threadIdx.x == 0) s_last = (atomicAdd(px.ticket, 1u) == gridDim.x - 1) ? 1u : 0u;
         __syncthreads();
