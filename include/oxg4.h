@@ -298,7 +298,7 @@ int32_t oxg4_decode_trace(oxg4_model* model, oxg4_cache* cache, const uint32_t* 
 /* Stand-alone run of the tcgen05/TMEM batched projection kernel (csrc/tc_gemm.cuh) for its parity
  * tests: out[B, N] = x[B, K] . W[N, K]^T with BF16 inputs given as bit patterns, f32 output, the
  * contract of Cublas::linear_bf16_f32 (crates/oxide-torch-cuda/src/cublas.rs:101-153). 1 <= B <= 256,
- * K a multiple of 8. ms (may be NULL) receives the device time of one launch. Returns OXG4_TIMEOUT
+ * K a multiple of 8. ms (may be NULL) receives the mean device time of ten back-to-back launches. Returns OXG4_TIMEOUT
  * if one of the kernel's bounded barrier waits ran out. */
 int32_t oxg4_debug_tc_gemm(const uint16_t* w_host, const uint16_t* x_host, int32_t N, int32_t K, int32_t B,
                            float* out_host, float* ms);
