@@ -41,7 +41,9 @@ sys.path.insert(0, ROOT)
 METRIC = "decode_tokens_per_s"
 UNIT = "tok/s"
 DEFAULT_WORKLOAD = "c3"          # ~4B-class, batch 1: the configuration the 70%-of-HBM target is quoted on
-NCU_TRAFFIC_BYTES = {"c3": 108442368}   # gate/up launch: dram read + write bytes from the ncu capture in profiles/
+# gate/up launch: dram read + write bytes per launch from the ncu captures summarised in profiles/ (the one-row
+# kernel on the ~4B widths; the tcgen05 kernel on the ~12B widths, single GPU)
+NCU_TRAFFIC_BYTES = {"c3": 108442368, "c4": 246000000}
 TP_RECORD_PROMPT = 8192          # prompt length of the tensor-parallel (~12B) record that accompanies the default run
 
 
@@ -353,7 +355,7 @@ def main():
                            "tc_gemm_kernel (tcgen05, gate and up maps)" if B <= 64 else
                            "gemv_mma_kernel<PRO_NORM, EPI_GATEUP>") + " (gate/up projection)",
                 "achieved": achieved, "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
-                "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload) if tp == 1 else None,
                 "bytes_per_launch": r["parts"]["gateup_launch"], "ms_per_launch": gu_ms,
                 "step_bytes": r["step_bytes"], "step_achieved": r["step_bytes"] / (ms_step * 1e-3) / 1e9,
                 "step_frac": r["step_bytes"] / (ms_step * 1e-3) / 1e9 / (peak * tp),
